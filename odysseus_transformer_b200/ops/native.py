@@ -1,0 +1,86 @@
+"""Loader for the in-tree sm_100a extension (``odysseus_transformer_b200/_C*.so``).
+
+The reference has no native code of its own; every kernel it runs belongs to a dependency
+(cuBLAS, flash-attn, Triton, NCCL).  Here the hot ops are hand-written CUDA in ``csrc/`` and are
+built in-tree by ``build_ext.py``.  On a CUDA device with the ``fused`` backend selected a missing
+extension is an error - there is no silent fallback to library kernels.
+"""
+from __future__ import annotations
+
+import importlib
+import os
+import threading
+from typing import Optional
+
+_lock = threading.Lock()
+_lib = None
+_err: Optional[BaseException] = None
+_backend = os.environ.get("ODY_BACKEND", "auto")  # "fused" | "library" | "auto"
+
+# number of launches of kernels from this package since the last reset (bench.py reports it)
+_launches = 0
+
+
+def set_backend(name: str) -> None:
+    """Select ``fused`` (own sm_100a kernels), ``library`` (torch / cuBLAS / NCCL), or ``auto``."""
+    global _backend
+    if name not in ("fused", "library", "auto"):
+        raise ValueError(name)
+    _backend = name
+
+
+def get_backend() -> str:
+    return _backend
+
+
+def lib():
+    """Import the extension (once). Raises if it is missing or fails to load."""
+    global _lib, _err
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if _err is not None:
+                raise RuntimeError(f"odysseus_transformer_b200._C failed to load earlier: {_err!r}")
+            try:
+                import torch  # noqa: F401  (libtorch symbols must be loaded first)
+                _lib = importlib.import_module("odysseus_transformer_b200._C")
+            except BaseException as e:  # noqa: BLE001
+                _err = e
+                raise RuntimeError(
+                    "the sm_100a extension odysseus_transformer_b200._C is not built or failed to load; "
+                    "run `python -m odysseus_transformer_b200.build_ext` (or __graft_entry__.build())"
+                ) from e
+    return _lib
+
+
+def available() -> bool:
+    try:
+        lib()
+        return True
+    except RuntimeError:
+        return False
+
+
+def use_native(t) -> bool:
+    """True when tensor ``t`` should go through the sm_100a kernels."""
+    if not t.is_cuda or _backend == "library":
+        return False
+    if _backend == "fused":
+        lib()          # raises loudly when the extension is missing
+        return True
+    return available()
+
+
+def count_launch(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def launch_count() -> int:
+    return _launches

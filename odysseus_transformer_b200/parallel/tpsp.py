@@ -1,0 +1,98 @@
+"""TP-SP (Megatron tensor parallel + sequence parallel) attention and MLP blocks.
+
+``TPSPAttention`` is the attention block of both the ``tpsp`` and ``odysseus`` modes
+(reference ``decoder/odysseus.py:45-271``): packed QKV projection as all-gather -> GEMM over the
+inner group, RoPE on the gathered sequence, causal attention over the whole (ring-block) sequence
+on ``H/U`` heads, output projection as GEMM -> reduce-scatter.  With a ring group of size R > 1 the
+attention itself becomes zigzag ring attention across ring blocks (the Odysseus x ring hybrid the
+reference README only claims, reference ``README.md:14``).
+
+``TPSPMLP`` is the Megatron MLP (reference ``decoder/tensor_parallel.py:14-85``): packed
+``w1w3`` column-parallel with a *local* ``[gate_u ; up_u]`` layout, ``w2`` row-parallel.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict
+
+import torch
+import torch.nn as nn
+
+from ..comm import torch_backend as C
+from ..ops import functional as F
+from .attention import packed_rope_attention
+from .linear import ColumnParallelLinearAG, RowParallelLinearRS
+
+
+class TPSPAttention(nn.Module):
+    def __init__(self, cfg, ctx, layer_idx: int = 0, dtype=None, device=None):
+        super().__init__()
+        U = ctx.inner_size
+        self.cfg, self.pctx, self.layer_idx = cfg, ctx, layer_idx
+        self.n_local_heads = cfg.num_attention_heads // U
+        self.n_local_kv_heads = cfg.num_key_value_heads // U
+        hd = cfg.head_dim
+        self.head_dim = hd
+        self.qkv_proj = ColumnParallelLinearAG(
+            cfg.hidden_size, (self.n_local_heads + 2 * self.n_local_kv_heads) * hd, ctx.inner_group,
+            dtype=dtype, device=device)
+        self.o_proj = RowParallelLinearRS(self.n_local_heads * hd, cfg.hidden_size, ctx.inner_group,
+                                          dtype=dtype, device=device)
+        if ctx.ring_size > 1:
+            # replicated across ring blocks: their gradients are summed over the ring group
+            for p in self.parameters():
+                p.grad_sync_group = ctx.ring_group
+
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        """x [T/N, d] local shard; cos/sin for the positions of this rank's ring block [T/R, hd/2]."""
+        qkv = self.qkv_proj(x)                                   # [Tb, (hq + 2 hkv) * hd]
+        o = packed_rope_attention(qkv, cos, sin, self.n_local_heads, self.n_local_kv_heads,
+                                  self.pctx.ring_group)          # [Tb, hq * hd]
+        return self.o_proj(o)                                    # [T/N, d]
+
+    # -- HF state-dict <-> shard
+    def hf_load(self, get: Callable[[str], torch.Tensor], prefix: str) -> None:
+        u, hd = self.pctx.inner_rank, self.head_dim
+        hq, hkv = self.n_local_heads, self.n_local_kv_heads
+        wq = get(prefix + "q_proj.weight")[u * hq * hd:(u + 1) * hq * hd]
+        wk = get(prefix + "k_proj.weight")[u * hkv * hd:(u + 1) * hkv * hd]
+        wv = get(prefix + "v_proj.weight")[u * hkv * hd:(u + 1) * hkv * hd]
+        with torch.no_grad():
+            self.qkv_proj.weight.copy_(torch.cat([wq, wk, wv], 0))
+            self.o_proj.weight.copy_(get(prefix + "o_proj.weight")[:, u * hq * hd:(u + 1) * hq * hd])
+
+    def hf_export(self, prefix: str, out: Dict[str, torch.Tensor]) -> None:
+        g, U, hd = self.pctx.inner_group, self.pctx.inner_size, self.head_dim
+        hq, hkv = self.n_local_heads, self.n_local_kv_heads
+        packed = C.all_gather_rows(self.qkv_proj.weight.detach(), g).view(U, (hq + 2 * hkv) * hd, -1)
+        out[prefix + "q_proj.weight"] = packed[:, :hq * hd].reshape(U * hq * hd, -1).clone()
+        out[prefix + "k_proj.weight"] = packed[:, hq * hd:(hq + hkv) * hd].reshape(U * hkv * hd, -1).clone()
+        out[prefix + "v_proj.weight"] = packed[:, (hq + hkv) * hd:].reshape(U * hkv * hd, -1).clone()
+        out[prefix + "o_proj.weight"] = self.o_proj.get_master_weight()
+
+
+class TPSPMLP(nn.Module):
+    def __init__(self, cfg, ctx, dtype=None, device=None):
+        super().__init__()
+        U = ctx.inner_size
+        self.cfg, self.pctx = cfg, ctx
+        self.i_local = cfg.intermediate_size // U
+        self.w1w3 = ColumnParallelLinearAG(cfg.hidden_size, 2 * self.i_local, ctx.inner_group,
+                                           dtype=dtype, device=device)
+        self.w2 = RowParallelLinearRS(self.i_local, cfg.hidden_size, ctx.inner_group, dtype=dtype, device=device)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.w2(F.swiglu(self.w1w3(x)))
+
+    def hf_load(self, get, prefix: str) -> None:
+        u, il = self.pctx.inner_rank, self.i_local
+        with torch.no_grad():
+            self.w1w3.weight.copy_(torch.cat([get(prefix + "gate_proj.weight")[u * il:(u + 1) * il],
+                                              get(prefix + "up_proj.weight")[u * il:(u + 1) * il]], 0))
+            self.w2.weight.copy_(get(prefix + "down_proj.weight")[:, u * il:(u + 1) * il])
+
+    def hf_export(self, prefix: str, out) -> None:
+        U, il = self.pctx.inner_size, self.i_local
+        packed = C.all_gather_rows(self.w1w3.weight.detach(), self.pctx.inner_group).view(U, 2 * il, -1)
+        out[prefix + "gate_proj.weight"] = packed[:, :il].reshape(U * il, -1).clone()
+        out[prefix + "up_proj.weight"] = packed[:, il:].reshape(U * il, -1).clone()
+        out[prefix + "down_proj.weight"] = self.w2.get_master_weight()
