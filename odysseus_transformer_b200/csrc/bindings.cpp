@@ -1,0 +1,270 @@
+// Python bindings (torch tensors -> raw-pointer launchers of ody_kernels.h).
+// All kernels run on the current CUDA stream of the tensors' device.  A per-device status word
+// receives the error code of any bounded in-kernel wait that gave up; `check_status()` reads it.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <mutex>
+
+#include "ody_kernels.h"
+
+namespace {
+
+int64_t g_launches = 0;
+std::map<int, at::Tensor> g_status;
+std::mutex g_mu;
+
+#define ODY_CHECK(call, what)                                                                        \
+  do {                                                                                               \
+    int rc__ = (call);                                                                               \
+    TORCH_CHECK(rc__ == 0, "odysseus_transformer_b200: ", what, " failed with code ", rc__, " (",    \
+                (rc__ > 0 && rc__ < 1000 ? cudaGetErrorString((cudaError_t)rc__) : "see ody_kernels.h"), ")"); \
+  } while (0)
+
+inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int* status_ptr(const at::Tensor& like) {
+  std::lock_guard<std::mutex> g(g_mu);
+  const int dev = like.get_device();
+  auto it = g_status.find(dev);
+  if (it == g_status.end()) {
+    auto t = torch::zeros({16}, torch::dtype(torch::kInt32).device(like.device()));
+    it = g_status.emplace(dev, t).first;
+  }
+  return it->second.data_ptr<int>();
+}
+
+void check_bf16(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+}
+
+// ------------------------------------------------------------------------------------------- GEMM
+at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& out, int64_t layout,
+                bool accumulate) {
+  check_bf16(a, "a");
+  check_bf16(b, "b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm expects 2-D operands");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm operands must be row-major (last stride 1)");
+  c10::cuda::CUDAGuard guard(a.device());
+  int64_t M, N, K;
+  if (layout == 0) { M = a.size(0); K = a.size(1); N = b.size(0); TORCH_CHECK(b.size(1) == K, "K mismatch"); }
+  else if (layout == 1) { M = a.size(0); K = a.size(1); N = b.size(1); TORCH_CHECK(b.size(0) == K, "K mismatch"); }
+  else { K = a.size(0); M = a.size(1); N = b.size(1); TORCH_CHECK(b.size(0) == K, "K mismatch"); }
+  at::Tensor c = out.has_value() ? out.value() : at::empty({M, N}, a.options());
+  check_bf16(c, "out");
+  TORCH_CHECK(c.dim() == 2 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1, "bad out shape");
+  TORCH_CHECK(!accumulate || out.has_value(), "accumulate needs out");
+  if (M == 0 || N == 0) return c;
+  if (K == 0) { if (!accumulate) c.zero_(); return c; }
+  ODY_CHECK(ody_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                          c.stride(0), (int)layout, accumulate ? 1 : 0, status_ptr(a), cur_stream()),
+            "gemm");
+  ++g_launches;
+  return c;
+}
+
+// ------------------------------------------------------------------------------------------- RMSNorm
+std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps) {
+  check_bf16(x, "x"); check_bf16(w, "w");
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous(), "rmsnorm: contiguous inputs required");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  auto y = at::empty_like(x);
+  auto rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  ODY_CHECK(ody_rmsnorm_fwd(x.data_ptr(), nullptr, w.data_ptr(), nullptr, y.data_ptr(), rstd.data_ptr<float>(), rows,
+                            (int)dim, (float)eps, cur_stream()), "rmsnorm_fwd");
+  ++g_launches;
+  return {y, rstd};
+}
+
+std::vector<at::Tensor> add_rmsnorm_fwd(const at::Tensor& x, const at::Tensor& delta, const at::Tensor& w, double eps) {
+  check_bf16(x, "x"); check_bf16(delta, "delta"); check_bf16(w, "w");
+  TORCH_CHECK(x.is_contiguous() && delta.is_contiguous() && w.is_contiguous(), "add_rmsnorm: contiguous inputs required");
+  TORCH_CHECK(x.sizes() == delta.sizes(), "add_rmsnorm: shape mismatch");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  auto s = at::empty_like(x);
+  auto y = at::empty_like(x);
+  auto rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  ODY_CHECK(ody_rmsnorm_fwd(x.data_ptr(), delta.data_ptr(), w.data_ptr(), s.data_ptr(), y.data_ptr(),
+                            rstd.data_ptr<float>(), rows, (int)dim, (float)eps, cur_stream()), "add_rmsnorm_fwd");
+  ++g_launches;
+  return {s, y, rstd};
+}
+
+std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w,
+                                    const at::Tensor& rstd, const c10::optional<at::Tensor>& ds) {
+  check_bf16(dy, "dy"); check_bf16(x, "x"); check_bf16(w, "w");
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous(), "rmsnorm_bwd: contiguous inputs required");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  auto dx = at::empty_like(x);
+  auto dw = at::empty({dim}, x.options().dtype(at::kFloat));
+  const int nb = ody_rmsnorm_bwd_blocks(rows, (int)dim);
+  auto partial = at::empty({nb, dim}, x.options().dtype(at::kFloat));
+  const void* dsp = nullptr;
+  if (ds.has_value()) { check_bf16(ds.value(), "ds"); TORCH_CHECK(ds.value().is_contiguous()); dsp = ds.value().data_ptr(); }
+  ODY_CHECK(ody_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dsp, dx.data_ptr(),
+                            dw.data_ptr<float>(), partial.data_ptr<float>(), rows, (int)dim, cur_stream()), "rmsnorm_bwd");
+  g_launches += 2;
+  return {dx, dw};
+}
+
+// ------------------------------------------------------------------------------------------- RoPE
+std::vector<at::Tensor> rope_tables(const at::Tensor& pos, int64_t head_dim, double theta) {
+  TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == at::kLong && pos.is_contiguous(), "positions: contiguous int64 CUDA");
+  c10::cuda::CUDAGuard guard(pos.device());
+  const int64_t T = pos.numel();
+  auto opt = pos.options().dtype(at::kFloat);
+  auto c = at::empty({T, head_dim / 2}, opt), s = at::empty({T, head_dim / 2}, opt);
+  ODY_CHECK(ody_rope_tables(pos.data_ptr<int64_t>(), c.data_ptr<float>(), s.data_ptr<float>(), T, (int)head_dim,
+                            (float)theta, cur_stream()), "rope_tables");
+  ++g_launches;
+  return {c, s};
+}
+
+void rope_inplace_(at::Tensor x, int64_t n_rot, const at::Tensor& cos, const at::Tensor& sin, bool inverse) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2), "rope: x must be [T, heads, hd] with packed heads");
+  TORCH_CHECK(cos.is_contiguous() && sin.is_contiguous() && cos.scalar_type() == at::kFloat, "rope tables: fp32 contiguous");
+  TORCH_CHECK(cos.size(0) == x.size(0) && cos.size(1) * 2 == x.size(2), "rope tables shape");
+  TORCH_CHECK(n_rot <= x.size(1));
+  c10::cuda::CUDAGuard guard(x.device());
+  ODY_CHECK(ody_rope_inplace(x.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), x.size(0), (int)n_rot,
+                             (int)x.size(2), x.stride(0), inverse ? 1 : 0, cur_stream()), "rope_inplace");
+  ++g_launches;
+}
+
+at::Tensor rope_apply(const at::Tensor& x, const at::Tensor& cos, const at::Tensor& sin, bool inverse) {
+  auto y = x.contiguous().clone();
+  rope_inplace_(y, y.size(1), cos, sin, inverse);
+  return y;
+}
+
+// ------------------------------------------------------------------------------------------- SwiGLU
+at::Tensor swiglu_fwd(const at::Tensor& gu) {
+  check_bf16(gu, "gate_up");
+  TORCH_CHECK(gu.is_contiguous() && gu.dim() == 2);
+  c10::cuda::CUDAGuard guard(gu.device());
+  const int64_t T = gu.size(0), I = gu.size(1) / 2;
+  auto h = at::empty({T, I}, gu.options());
+  ODY_CHECK(ody_swiglu_fwd(gu.data_ptr(), h.data_ptr(), T, I, cur_stream()), "swiglu_fwd");
+  ++g_launches;
+  return h;
+}
+
+at::Tensor swiglu_bwd(const at::Tensor& dh, const at::Tensor& gu) {
+  check_bf16(gu, "gate_up"); check_bf16(dh, "dh");
+  TORCH_CHECK(gu.is_contiguous() && dh.is_contiguous());
+  c10::cuda::CUDAGuard guard(gu.device());
+  const int64_t T = gu.size(0), I = gu.size(1) / 2;
+  auto dgu = at::empty_like(gu);
+  ODY_CHECK(ody_swiglu_bwd(dh.data_ptr(), gu.data_ptr(), dgu.data_ptr(), T, I, cur_stream()), "swiglu_bwd");
+  ++g_launches;
+  return dgu;
+}
+
+// ------------------------------------------------------------------------------------------- cross-entropy
+std::vector<at::Tensor> ce_fwd(const at::Tensor& logits, const at::Tensor& targets, int64_t ignore_index) {
+  check_bf16(logits, "logits");
+  TORCH_CHECK(logits.is_contiguous() && logits.dim() == 2 && targets.scalar_type() == at::kLong && targets.is_contiguous());
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0), V = logits.size(1);
+  auto opt = logits.options().dtype(at::kFloat);
+  auto loss = at::empty({T}, opt), lse = at::empty({T}, opt);
+  ODY_CHECK(ody_ce_fwd(logits.data_ptr(), targets.data_ptr<int64_t>(), loss.data_ptr<float>(), lse.data_ptr<float>(), T, V,
+                       ignore_index, cur_stream()), "ce_fwd");
+  ++g_launches;
+  return {loss, lse};
+}
+
+void ce_bwd_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse, const at::Tensor& scale,
+             int64_t ignore_index) {
+  check_bf16(logits, "logits");
+  TORCH_CHECK(logits.is_contiguous() && scale.is_cuda() && scale.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0), V = logits.size(1);
+  for (int64_t r0 = 0; r0 < T; r0 += 32768) {   // grid.y limit
+    const int64_t n = std::min<int64_t>(32768, T - r0);
+    ODY_CHECK(ody_ce_bwd((char*)logits.data_ptr() + r0 * V * 2, targets.data_ptr<int64_t>() + r0,
+                         lse.data_ptr<float>() + r0, scale.data_ptr<float>(), n, V, ignore_index, cur_stream()), "ce_bwd");
+    ++g_launches;
+  }
+}
+
+// ------------------------------------------------------------------------------------------- AdamW
+void adamw_step(at::Tensor master, at::Tensor m, at::Tensor v, const at::Tensor& grad, at::Tensor param, double lr,
+                double beta1, double beta2, double eps, double weight_decay, int64_t step, double grad_scale) {
+  check_bf16(grad, "grad"); check_bf16(param, "param");
+  TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  TORCH_CHECK(master.is_contiguous() && m.is_contiguous() && v.is_contiguous() && grad.is_contiguous() && param.is_contiguous());
+  c10::cuda::CUDAGuard guard(master.device());
+  ODY_CHECK(ody_adamw(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr(), param.data_ptr(),
+                      master.numel(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)weight_decay, (int)step,
+                      (float)grad_scale, cur_stream()), "adamw");
+  ++g_launches;
+}
+
+// ------------------------------------------------------------------------------------------- attention merge
+void attn_merge_(at::Tensor out, at::Tensor lse, const at::Tensor& o, const at::Tensor& l, int64_t row0) {
+  check_bf16(o, "o");
+  TORCH_CHECK(out.scalar_type() == at::kFloat && lse.scalar_type() == at::kFloat && l.scalar_type() == at::kFloat);
+  TORCH_CHECK(out.is_contiguous() && lse.is_contiguous() && o.is_contiguous() && l.is_contiguous());
+  c10::cuda::CUDAGuard guard(out.device());
+  ODY_CHECK(ody_attn_merge(out.data_ptr<float>(), lse.data_ptr<float>(), o.data_ptr(), l.data_ptr<float>(), o.size(0),
+                           (int)o.size(1), (int)o.size(2), row0, out.size(0), cur_stream()), "attn_merge");
+  ++g_launches;
+}
+
+// ------------------------------------------------------------------------------------------- status
+int64_t status(int64_t device) {
+  at::Tensor t;
+  {
+    std::lock_guard<std::mutex> g(g_mu);
+    auto it = g_status.find((int)device);
+    if (it == g_status.end()) return 0;
+    t = it->second;
+  }
+  return t.cpu().data_ptr<int>()[0];
+}
+
+void clear_status(int64_t device) {
+  std::lock_guard<std::mutex> g(g_mu);
+  auto it = g_status.find((int)device);
+  if (it != g_status.end()) it->second.zero_();
+}
+
+int64_t launch_count() { return g_launches; }
+void reset_launch_count() { g_launches = 0; }
+void add_launches(int64_t n) { g_launches += n; }
+
+}  // namespace
+
+// attention (defined in attn_bindings.cpp)
+void ody_register_attention(pybind11::module& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out") = py::none(), py::arg("layout") = 0,
+        py::arg("accumulate") = false);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope_tables", &rope_tables);
+  m.def("rope_inplace_", &rope_inplace_);
+  m.def("rope_apply", &rope_apply);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("ce_fwd", &ce_fwd);
+  m.def("ce_bwd_", &ce_bwd_);
+  m.def("adamw_step", &adamw_step);
+  m.def("attn_merge_", &attn_merge_);
+  m.def("status", &status);
+  m.def("clear_status", &clear_status);
+  m.def("launch_count", &launch_count);
+  m.def("reset_launch_count", &reset_launch_count);
+  m.def("add_launches", &add_launches);
+  ody_register_attention(m);
+}

@@ -1,0 +1,443 @@
+// Memory-bound hot ops for sm_100a: RMSNorm(+residual) fwd/bwd, RoPE, SwiGLU fwd/bwd, cross-entropy
+// fwd / in-place bwd, fused AdamW over flat shards, attention partial-result merge.
+//
+// The reference gets these from unfused ATen elementwise kernels inside HF Llama, a Triton loss from
+// flash-attn and torch.optim.AdamW (reference train.py:167,173; decoder/odysseus.py:210-213,293-295).
+// Every kernel here moves 16 bytes per thread per access and touches each operand once.
+#include "common.cuh"
+#include "ody_kernels.h"
+
+namespace ody {
+
+// ------------------------------------------------------------------------------------------- RMSNorm
+
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_k(const bf16* __restrict__ x, const bf16* __restrict__ delta,
+                                                     const bf16* __restrict__ w, bf16* __restrict__ sum_out,
+                                                     bf16* __restrict__ y, float* __restrict__ rstd, int dim,
+                                                     float eps) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const bf16* xr = x + row * dim;
+  float vals[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (threadIdx.x + i * blockDim.x) * 8;
+    if (c < dim) {
+      bf16x8 p = ld8(xr + c);
+      if (delta != nullptr) {
+        float a[8], b[8];
+        unpack8(p, a);
+        unpack8(ld8(delta + row * dim + c), b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] += b[j];
+        p = pack8(a);  // the residual stream is stored in bf16; the norm sees the stored value
+        st8(sum_out + row * dim + c, p);
+      }
+      unpack8(p, vals[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rs = rsqrtf(ss / (float)dim + eps);
+  if (threadIdx.x == 0) rstd[row] = rs;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (threadIdx.x + i * blockDim.x) * 8;
+    if (c < dim) {
+      float wv[8], o[8];
+      unpack8(ld8(w + c), wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rs * wv[j];
+      st8(y + row * dim + c, pack8(o));
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_k(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                     const bf16* __restrict__ w, const float* __restrict__ rstd,
+                                                     const bf16* __restrict__ ds, bf16* __restrict__ dx,
+                                                     float* __restrict__ dw_partial, int64_t rows, int dim) {
+  __shared__ float red[33];
+  float wv[NV][8], acc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (threadIdx.x + i * blockDim.x) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    if (c < dim) unpack8(ld8(w + c), wv[i]);
+  }
+  const float inv_dim = 1.f / (float)dim;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float rs = rstd[row];
+    float g[NV][8], xh[NV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (threadIdx.x + i * blockDim.x) * 8;
+      if (c < dim) {
+        float a[8];
+        unpack8(ld8(dy + row * dim + c), a);
+        unpack8(ld8(x + row * dim + c), xh[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] *= rs;
+          acc[i][j] += a[j] * xh[i][j];
+          g[i][j] = a[j] * wv[i][j];
+          dot += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    dot = block_sum(dot, red) * inv_dim;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (threadIdx.x + i * blockDim.x) * 8;
+      if (c < dim) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (g[i][j] - xh[i][j] * dot) * rs;
+        if (ds != nullptr) {
+          float s[8];
+          unpack8(ld8(ds + row * dim + c), s);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += s[j];
+        }
+        st8(dx + row * dim + c, pack8(o));
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = (threadIdx.x + i * blockDim.x) * 8;
+    if (c < dim) {
+      float* p = dw_partial + (int64_t)blockIdx.x * dim + c;
+      *reinterpret_cast<float4*>(p) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+      *reinterpret_cast<float4*>(p + 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+    }
+  }
+}
+
+__global__ void colsum_k(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int dim) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= dim) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(int64_t)b * dim + c];
+  out[c] = s;
+}
+
+// ------------------------------------------------------------------------------------------- RoPE
+
+__global__ void rope_tables_k(const int64_t* __restrict__ pos, float* __restrict__ cos_o, float* __restrict__ sin_o,
+                              int64_t T, int half, float theta) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * half) return;
+  const int k = (int)(i % half);
+  const int64_t t = i / half;
+  const float inv_freq = 1.0f / powf(theta, (float)(2 * k) / (float)(2 * half));
+  const float ang = (float)pos[t] * inv_freq;
+  float s, c;
+  sincosf(ang, &s, &c);
+  cos_o[i] = c;
+  sin_o[i] = s;
+}
+
+__global__ void rope_inplace_k(bf16* __restrict__ x, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                               int64_t T, int n_rot, int head_dim, int64_t row_stride, int inverse) {
+  const int half = head_dim >> 1;
+  const int vec_per_head = half >> 3;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = T * n_rot * vec_per_head;
+  if (i >= total) return;
+  const int kv = (int)(i % vec_per_head);
+  const int h = (int)((i / vec_per_head) % n_rot);
+  const int64_t t = i / ((int64_t)vec_per_head * n_rot);
+  bf16* p1 = x + t * row_stride + (int64_t)h * head_dim + kv * 8;
+  bf16* p2 = p1 + half;
+  float a[8], b[8], o1[8], o2[8];
+  unpack8(ld8(p1), a);
+  unpack8(ld8(p2), b);
+  const float* cp = cos_t + t * half + kv * 8;
+  const float* sp = sin_t + t * half + kv * 8;
+  const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+  const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float sj = inverse ? -s[j] : s[j];
+    o1[j] = a[j] * c[j] - b[j] * sj;
+    o2[j] = b[j] * c[j] + a[j] * sj;
+  }
+  st8(p1, pack8(o1));
+  st8(p2, pack8(o2));
+}
+
+// ------------------------------------------------------------------------------------------- SwiGLU
+
+__global__ void swiglu_fwd_k(const bf16* __restrict__ gu, bf16* __restrict__ h, int64_t T, int64_t I) {
+  const int64_t vpr = I >> 3;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * vpr) return;
+  const int64_t t = i / vpr, c = (i % vpr) * 8;
+  float g[8], u[8], o[8];
+  unpack8(ld8(gu + t * 2 * I + c), g);
+  unpack8(ld8(gu + t * 2 * I + I + c), u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+  st8(h + t * I + c, pack8(o));
+}
+
+__global__ void swiglu_bwd_k(const bf16* __restrict__ dh, const bf16* __restrict__ gu, bf16* __restrict__ dgu,
+                             int64_t T, int64_t I) {
+  const int64_t vpr = I >> 3;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * vpr) return;
+  const int64_t t = i / vpr, c = (i % vpr) * 8;
+  float g[8], u[8], d[8], dg[8], du[8];
+  unpack8(ld8(gu + t * 2 * I + c), g);
+  unpack8(ld8(gu + t * 2 * I + I + c), u);
+  unpack8(ld8(dh + t * I + c), d);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float sig = 1.f / (1.f + __expf(-g[j]));
+    dg[j] = d[j] * u[j] * sig * (1.f + g[j] * (1.f - sig));
+    du[j] = d[j] * g[j] * sig;
+  }
+  st8(dgu + t * 2 * I + c, pack8(dg));
+  st8(dgu + t * 2 * I + I + c, pack8(du));
+}
+
+// ------------------------------------------------------------------------------------------- cross-entropy
+
+__global__ void __launch_bounds__(512) ce_fwd_k(const bf16* __restrict__ logits, const int64_t* __restrict__ targets,
+                                                float* __restrict__ loss, float* __restrict__ lse, int64_t V,
+                                                int64_t ignore_index) {
+  __shared__ float red[33];
+  const int64_t row = blockIdx.x;
+  const bf16* lr = logits + row * V;
+  float m = -INFINITY, s = 0.f;
+  for (int64_t c = (int64_t)threadIdx.x * 8; c < V; c += (int64_t)blockDim.x * 8) {
+    float f[8];
+    unpack8(ld8(lr + c), f);
+    float mx = f[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mx = fmaxf(mx, f[j]);
+    const float mn = fmaxf(m, mx);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += __expf(f[j] - mn);
+    s = s * __expf(m - mn) + acc;
+    m = mn;
+  }
+  const float M = block_max(m, red);
+  const float S = block_sum(s * __expf(m - M), red);
+  if (threadIdx.x == 0) {
+    const float l = M + logf(S);
+    lse[row] = l;
+    const int64_t tg = targets[row];
+    loss[row] = (tg == ignore_index) ? 0.f : l - __bfloat162float(lr[tg]);
+  }
+}
+
+__global__ void ce_bwd_k(bf16* __restrict__ logits, const int64_t* __restrict__ targets, const float* __restrict__ lse,
+                         const float* __restrict__ scale, int64_t V, int64_t ignore_index) {
+  const int64_t row = blockIdx.y;
+  const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= V) return;
+  const int64_t tg = targets[row];
+  const float sc = (tg == ignore_index) ? 0.f : scale[0];
+  const float l = lse[row];
+  bf16* p = logits + row * V + c;
+  float f[8];
+  unpack8(ld8(p), f);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float pr = __expf(f[j] - l);
+    if (c + j == tg) pr -= 1.f;
+    f[j] = pr * sc;
+  }
+  st8(p, pack8(f));
+}
+
+// ------------------------------------------------------------------------------------------- AdamW
+
+__global__ void adamw_k(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+                        const bf16* __restrict__ grad, bf16* __restrict__ param, int64_t n, float decay, float beta1,
+                        float beta2, float step_size, float inv_sqrt_bc2, float eps, float grad_scale) {
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  float g[8];
+  unpack8(ld8(grad + i), g);
+  float4 w0 = *reinterpret_cast<float4*>(master + i), w1 = *reinterpret_cast<float4*>(master + i + 4);
+  float4 m0 = *reinterpret_cast<float4*>(m + i), m1 = *reinterpret_cast<float4*>(m + i + 4);
+  float4 v0 = *reinterpret_cast<float4*>(v + i), v1 = *reinterpret_cast<float4*>(v + i + 4);
+  float W[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+  float M[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+  float Vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float gj = g[j] * grad_scale;
+    M[j] = beta1 * M[j] + (1.f - beta1) * gj;
+    Vv[j] = beta2 * Vv[j] + (1.f - beta2) * gj * gj;
+    const float denom = sqrtf(Vv[j]) * inv_sqrt_bc2 + eps;
+    W[j] = W[j] * decay - step_size * M[j] / denom;
+  }
+  *reinterpret_cast<float4*>(master + i) = make_float4(W[0], W[1], W[2], W[3]);
+  *reinterpret_cast<float4*>(master + i + 4) = make_float4(W[4], W[5], W[6], W[7]);
+  *reinterpret_cast<float4*>(m + i) = make_float4(M[0], M[1], M[2], M[3]);
+  *reinterpret_cast<float4*>(m + i + 4) = make_float4(M[4], M[5], M[6], M[7]);
+  *reinterpret_cast<float4*>(v + i) = make_float4(Vv[0], Vv[1], Vv[2], Vv[3]);
+  *reinterpret_cast<float4*>(v + i + 4) = make_float4(Vv[4], Vv[5], Vv[6], Vv[7]);
+  st8(param + i, pack8(W));
+}
+
+// ------------------------------------------------------------------------------------------- attention merge
+
+// out [T_total, H, hd] fp32 and lse [H, T_total] fp32 are the running result; (o [T, H, hd] bf16,
+// l [H, T] fp32) is a partial over a disjoint key set for rows [row0, row0 + T).
+__global__ void attn_merge_k(float* __restrict__ out, float* __restrict__ lse, const bf16* __restrict__ o,
+                             const float* __restrict__ l, int64_t T, int H, int hd, int64_t row0, int64_t T_total) {
+  const int vph = hd >> 3;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = i < T * H * vph;
+  float la = 0.f, lb = 0.f;
+  int64_t t = 0;
+  int h = 0, kv = 0;
+  if (live) {
+    kv = (int)(i % vph);
+    h = (int)((i / vph) % H);
+    t = i / ((int64_t)vph * H);
+    la = lse[(int64_t)h * T_total + row0 + t];
+    lb = l[(int64_t)h * T + t];
+  }
+  __syncwarp();  // every lane of a (t, h) group has read the old lse before its leader overwrites it
+  if (!live) return;
+  const float mx = fmaxf(la, lb);
+  const float ln = mx + logf(__expf(la - mx) + __expf(lb - mx));
+  const float wa = __expf(la - ln), wb = __expf(lb - ln);
+  float* po = out + ((row0 + t) * H + h) * hd + kv * 8;
+  float b[8];
+  unpack8(ld8(o + (t * H + h) * hd + kv * 8), b);
+  float4 a0 = *reinterpret_cast<float4*>(po), a1 = *reinterpret_cast<float4*>(po + 4);
+  a0 = make_float4(a0.x * wa + b[0] * wb, a0.y * wa + b[1] * wb, a0.z * wa + b[2] * wb, a0.w * wa + b[3] * wb);
+  a1 = make_float4(a1.x * wa + b[4] * wb, a1.y * wa + b[5] * wb, a1.z * wa + b[6] * wb, a1.w * wa + b[7] * wb);
+  *reinterpret_cast<float4*>(po) = a0;
+  *reinterpret_cast<float4*>(po + 4) = a1;
+  if (kv == 0) lse[(int64_t)h * T_total + row0 + t] = ln;
+}
+
+}  // namespace ody
+
+// =========================================================================================== launchers
+
+using namespace ody;
+
+static inline int last_err() { return (int)cudaGetLastError(); }
+static inline unsigned blocks_for(int64_t n, int per) { return (unsigned)((n + per - 1) / per); }
+
+extern "C" int ody_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* sum_out, void* y, float* rstd,
+                               int64_t rows, int dim, float eps, cudaStream_t st) {
+  if (dim % 8 != 0 || dim > 256 * 8 * 8) return (int)cudaErrorInvalidValue;
+  if (rows == 0) return 0;
+  const int nv = (dim + 2047) / 2048;
+#define L(NV)                                                                                               \
+  rmsnorm_fwd_k<NV><<<(unsigned)rows, 256, 0, st>>>((const bf16*)x, (const bf16*)delta, (const bf16*)w,    \
+                                                    (bf16*)sum_out, (bf16*)y, rstd, dim, eps)
+  if (nv <= 1) L(1); else if (nv <= 2) L(2); else if (nv <= 4) L(4); else L(8);
+#undef L
+  return last_err();
+}
+
+extern "C" int ody_rmsnorm_bwd_blocks(int64_t rows, int dim) {
+  (void)dim;
+  int64_t b = 148 * 4;
+  return (int)(rows < b ? (rows > 0 ? rows : 1) : b);
+}
+
+extern "C" int ody_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* ds,
+                               void* dx, float* dw, float* dw_partial, int64_t rows, int dim, cudaStream_t st) {
+  if (dim % 8 != 0 || dim > 256 * 8 * 8) return (int)cudaErrorInvalidValue;
+  const int nb = ody_rmsnorm_bwd_blocks(rows, dim);
+  const int nv = (dim + 2047) / 2048;
+#define L(NV)                                                                                                  \
+  rmsnorm_bwd_k<NV><<<nb, 256, 0, st>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)ds, \
+                                        (bf16*)dx, dw_partial, rows, dim)
+  if (nv <= 1) L(1); else if (nv <= 2) L(2); else if (nv <= 4) L(4); else L(8);
+#undef L
+  colsum_k<<<blocks_for(dim, 256), 256, 0, st>>>(dw_partial, dw, nb, dim);
+  return last_err();
+}
+
+extern "C" int ody_rope_tables(const int64_t* positions, float* cos_out, float* sin_out, int64_t T, int head_dim,
+                               float theta, cudaStream_t st) {
+  const int half = head_dim / 2;
+  if (T == 0) return 0;
+  rope_tables_k<<<blocks_for(T * half, 256), 256, 0, st>>>(positions, cos_out, sin_out, T, half, theta);
+  return last_err();
+}
+
+extern "C" int ody_rope_inplace(void* x, const float* cos_t, const float* sin_t, int64_t T, int n_rot, int head_dim,
+                                int64_t row_stride, int inverse, cudaStream_t st) {
+  if (head_dim % 16 != 0 || row_stride % 8 != 0) return (int)cudaErrorInvalidValue;
+  const int64_t total = T * n_rot * (head_dim / 16);
+  if (total == 0) return 0;
+  rope_inplace_k<<<blocks_for(total, 256), 256, 0, st>>>((bf16*)x, cos_t, sin_t, T, n_rot, head_dim, row_stride,
+                                                         inverse);
+  return last_err();
+}
+
+extern "C" int ody_swiglu_fwd(const void* gu, void* h, int64_t T, int64_t I, cudaStream_t st) {
+  if (I % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (T * I == 0) return 0;
+  swiglu_fwd_k<<<blocks_for(T * (I / 8), 256), 256, 0, st>>>((const bf16*)gu, (bf16*)h, T, I);
+  return last_err();
+}
+
+extern "C" int ody_swiglu_bwd(const void* dh, const void* gu, void* dgu, int64_t T, int64_t I, cudaStream_t st) {
+  if (I % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (T * I == 0) return 0;
+  swiglu_bwd_k<<<blocks_for(T * (I / 8), 256), 256, 0, st>>>((const bf16*)dh, (const bf16*)gu, (bf16*)dgu, T, I);
+  return last_err();
+}
+
+extern "C" int ody_ce_fwd(const void* logits, const int64_t* targets, float* loss, float* lse, int64_t T, int64_t V,
+                          int64_t ignore_index, cudaStream_t st) {
+  if (V % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (T == 0) return 0;
+  ce_fwd_k<<<(unsigned)T, 512, 0, st>>>((const bf16*)logits, targets, loss, lse, V, ignore_index);
+  return last_err();
+}
+
+extern "C" int ody_ce_bwd(void* logits, const int64_t* targets, const float* lse, const float* scale, int64_t T,
+                          int64_t V, int64_t ignore_index, cudaStream_t st) {
+  if (V % 8 != 0 || T > 65535) return (int)cudaErrorInvalidValue;
+  if (T == 0) return 0;
+  dim3 grid(blocks_for(V / 8, 256), (unsigned)T);
+  ce_bwd_k<<<grid, 256, 0, st>>>((bf16*)logits, targets, lse, scale, V, ignore_index);
+  return last_err();
+}
+
+extern "C" int ody_adamw(float* master, float* m, float* v, const void* grad, void* param, int64_t n, float lr,
+                         float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale,
+                         cudaStream_t st) {
+  if (n % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (n == 0) return 0;
+  const double bc1 = 1.0 - pow((double)beta1, (double)step);
+  const double bc2 = 1.0 - pow((double)beta2, (double)step);
+  adamw_k<<<blocks_for(n / 8, 256), 256, 0, st>>>(master, m, v, (const bf16*)grad, (bf16*)param, n,
+                                                  1.f - lr * weight_decay, beta1, beta2, (float)(lr / bc1),
+                                                  (float)(1.0 / sqrt(bc2)), eps, grad_scale);
+  return last_err();
+}
+
+extern "C" int ody_attn_merge(float* out, float* lse, const void* o, const float* l, int64_t T, int H, int hd,
+                              int64_t row0, int64_t T_total, cudaStream_t st) {
+  if (hd % 8 != 0 || 32 % (hd / 8) != 0) return (int)cudaErrorInvalidValue;
+  const int64_t total = T * H * (hd / 8);
+  if (total == 0) return 0;
+  attn_merge_k<<<blocks_for(total, 256), 256, 0, st>>>(out, lse, (const bf16*)o, l, T, H, hd, row0, T_total);
+  return last_err();
+}

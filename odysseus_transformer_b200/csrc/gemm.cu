@@ -1,0 +1,303 @@
+// bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM -> epilogue -> TMA store.
+//
+// This is the GEMM core behind every linear layer of the model (the reference reaches cuBLAS through
+// torch.matmul / F.linear: reference utils/linear_tpsp.py:173,217,291,588; utils/linear_zero3.py:44,68,74).
+//
+//   layout 0 (NT): C[M,N] = A[M,K] * B[N,K]^T      forward   y  = x  W^T     (A, B K-major)
+//   layout 1 (NN): C[M,N] = A[M,K] * B[K,N]        dgrad     dx = dy W       (B MN-major)
+//   layout 2 (TN): C[M,N] = A[K,M]^T * B[K,N]      wgrad     dW = dy^T x     (A, B MN-major)
+//
+// One persistent CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (one elected
+// thread) and TMEM owner, warps 2-5 = epilogue.  Tile 128 x 256 x 64, 4-stage smem ring (48 KB / stage),
+// two 256-column fp32 accumulators in TMEM (all 512 columns) so the epilogue of tile i overlaps the
+// main loop of tile i+1.  The epilogue converts to bf16, stages 128 x 64 blocks in swizzled smem and
+// writes them with TMA stores (edges are clipped by the tensor map).  No cluster multicast anywhere.
+#include "ody_kernels.h"
+#include "sm100.cuh"
+
+namespace ody {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;             // 16 KB
+constexpr int B_BYTES = BN * BK * 2;             // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 48 KB
+constexpr int EPI_COLS = 64;
+constexpr int EPI_BYTES = BM * EPI_COLS * 2;     // 16 KB
+constexpr int SMEM_TILES = STAGES * STAGE_BYTES + 2 * EPI_BYTES;
+constexpr int SMEM_TOTAL = SMEM_TILES + 256 + 1024;   // + barriers + alignment slack
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 16;
+
+struct GemmBars {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = GROUP_M * tiles_n;
+  const int g = tile / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsize = min(GROUP_M, tiles_m - first_m);
+  const int local = tile - g * per_group;
+  tm = first_m + local % gsize;
+  tn = local / gsize;
+}
+
+__device__ __forceinline__ bool epi_all_ok(bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(r)
+      : "r"((uint32_t)ok)
+      : "memory");
+  return r != 0;
+}
+
+template <int LAYOUT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const __nv_bfloat16* __restrict__ c_in, int M, int N, int K,
+                 int64_t ldc, int accumulate, int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  GemmBars* bars = (GemmBars*)(smem + SMEM_TILES);
+  uint8_t* epi = smem + STAGES * STAGE_BYTES;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int kblocks = (K + BK - 1) / BK;
+  constexpr bool A_MN = (LAYOUT == 2), B_MN = (LAYOUT != 0);
+  constexpr uint32_t IDESC = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->tmem_full[b], 1);
+      mbar_init(&bars->tmem_empty[b], 128);
+    }
+    mbar_init(&bars->drain, 1);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+    prefetch_tmap(&tmC);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          mbar_expect_tx(&bars->full[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sA, &tmA, k0, m0, &bars->full[stage]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sA + j * 8192, &tmA, m0 + 64 * j, k0, &bars->full[stage]);
+          }
+          if (!B_MN) {
+            tma_load_2d(sB, &tmB, k0, n0, &bars->full[stage]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &tmB, n0 + 64 * j, k0, &bars->full[stage]);
+          }
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // give copies still in flight a bounded chance to land before the CTA retires
+        int n = issued < STAGES ? issued : STAGES;
+        for (int i = 0; i < n; ++i) {
+          if (--stage < 0) { stage = STAGES - 1; phase ^= 1; }
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&bars->full[stage], phase) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const int buf = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!mbar_wait(&bars->tmem_empty[buf], acc_phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&bars->full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t adesc = A_MN ? make_smem_desc(sA + kk * 2048, 8192, 1024) : make_smem_desc(sA + kk * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(sB + kk * 2048, 8192, 1024) : make_smem_desc(sB + kk * 32, 16, 1024);
+            umma_ss(d_tmem, adesc, bdesc, IDESC, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&bars->empty[stage]);        // frees the smem stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&bars->tmem_full[buf]);  // accumulator complete
+      }
+      if (!ok || *abort_flag) {
+        umma_commit(&bars->drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    const int r = q * 32 + lane;                 // row inside the tile
+    const bool store_thread = (warp == 2 && lane == 0);
+    int local_tile = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int m0 = tm * BM, n0 = tn * BN;
+      const int buf = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      bool ok = mbar_wait(&bars->tmem_full[buf], acc_phase, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL);
+      if (!epi_all_ok(ok)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < BN / EPI_COLS; ++c) {
+        uint8_t* sbuf = epi + (c & 1) * EPI_BYTES;
+        if (store_thread) tma_store_wait_read<1>();
+        named_barrier(1, 128);
+        const uint32_t taddr = tmem_base + buf * BN + c * EPI_COLS + ((uint32_t)(q * 32) << 16);
+        uint32_t v[64];
+        tmem_ld_32x32(taddr, v);
+        tmem_ld_32x32(taddr + 32, v + 32);
+        tmem_ld_wait();
+        if (c == BN / EPI_COLS - 1) {
+          tc_fence_before();
+          mbar_arrive(&bars->tmem_empty[buf]);
+        }
+        const int row = m0 + r, col0 = n0 + c * EPI_COLS;
+        if (accumulate && row < M) {
+          const __nv_bfloat16* cp = c_in + (int64_t)row * ldc + col0;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (col0 + j * 8 < N) {   // N is a multiple of 8
+              const uint4 old = *reinterpret_cast<const uint4*>(cp + j * 8);
+              const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const float2 f = __bfloat1622float2(o2[t]);
+                v[j * 8 + 2 * t] = __float_as_uint(__uint_as_float(v[j * 8 + 2 * t]) + f.x);
+                v[j * 8 + 2 * t + 1] = __float_as_uint(__uint_as_float(v[j * 8 + 2 * t + 1]) + f.y);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 pk;
+          __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int t = 0; t < 4; ++t)
+            p2[t] = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * t]), __uint_as_float(v[j * 8 + 2 * t + 1]));
+          *reinterpret_cast<uint4*>(sbuf + r * 128 + ((j ^ (r & 7)) << 4)) = pk;
+        }
+        fence_proxy_async_smem();
+        named_barrier(1, 128);
+        if (store_thread && col0 < N) {
+          tma_store_2d(&tmC, sbuf, col0, m0);
+          tma_store_commit();
+        }
+      }
+    }
+    if (store_thread) tma_store_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+static int g_num_sms = 0;
+
+template <int LAYOUT>
+static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                       int64_t ldc, int accumulate, int* err, cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<LAYOUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  CUtensorMap tA, tB, tC;
+  int r;
+  if (LAYOUT == 2) r = make_tmap_2d_bf16(&tA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
+  else r = make_tmap_2d_bf16(&tA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, BM);
+  if (r) return 700000 + r;
+  if (LAYOUT == 0) r = make_tmap_2d_bf16(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, BN);
+  else r = make_tmap_2d_bf16(&tB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
+  if (r) return 710000 + r;
+  r = make_tmap_2d_bf16(&tC, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, EPI_COLS, BM);
+  if (r) return 720000 + r;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < g_num_sms ? tiles : g_num_sms;
+  gemm_bf16_kernel<LAYOUT><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tA, tB, tC, (const __nv_bfloat16*)C, M, N, K, ldc,
+                                                                  accumulate, err);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace ody
+
+extern "C" int ody_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                             int64_t ldc, int layout, int accumulate, int* err, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return (int)cudaErrorInvalidValue;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15))
+    return (int)cudaErrorInvalidValue;
+  switch (layout) {
+    case 0: return ody::launch_gemm<0>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, err, st);
+    case 1: return ody::launch_gemm<1>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, err, st);
+    case 2: return ody::launch_gemm<2>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, err, st);
+  }
+  return (int)cudaErrorInvalidValue;
+}

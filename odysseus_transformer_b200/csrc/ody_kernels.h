@@ -1,0 +1,55 @@
+// Host-callable launchers of the sm_100a kernels.  Plain pointers and a stream: no torch types, so
+// the .cu files build in seconds and can be called from any host runtime.  Every launcher returns a
+// cudaError_t-compatible int (0 = success) and never allocates device memory; workspaces are passed in.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- RMSNorm (bf16 activations, fp32 statistics). delta may be null (no residual add).
+int ody_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* sum_out, void* y, float* rstd,
+                    int64_t rows, int dim, float eps, cudaStream_t stream);
+// dx = d(rmsnorm)/dx * dy (+ ds when non-null); dw_partial [ody_rmsnorm_bwd_blocks(), dim] fp32 workspace,
+// reduced into dw [dim] fp32 by the same call.
+int ody_rmsnorm_bwd_blocks(int64_t rows, int dim);
+int ody_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* ds, void* dx,
+                    float* dw, float* dw_partial, int64_t rows, int dim, cudaStream_t stream);
+
+// ---- RoPE (rotate-half).  positions int64 [T]; tables fp32 [T, hd/2].
+int ody_rope_tables(const int64_t* positions, float* cos_out, float* sin_out, int64_t T, int head_dim, float theta,
+                    cudaStream_t stream);
+// rotates heads [0, n_rot) of x [T, heads, hd] (row stride in elements) in place; inverse = transpose rotation
+int ody_rope_inplace(void* x, const float* cos_t, const float* sin_t, int64_t T, int n_rot, int head_dim,
+                     int64_t row_stride, int inverse, cudaStream_t stream);
+
+// ---- SwiGLU: gu [T, 2I] = [gate | up]  ->  h [T, I] ; bwd writes dgu [T, 2I]
+int ody_swiglu_fwd(const void* gu, void* h, int64_t T, int64_t I, cudaStream_t stream);
+int ody_swiglu_bwd(const void* dh, const void* gu, void* dgu, int64_t T, int64_t I, cudaStream_t stream);
+
+// ---- cross-entropy over bf16 logits [T, V]: per-row loss and lse (fp32); bwd overwrites logits with
+// (softmax - onehot) * scale[0]  (scale on device), rows with target == ignore_index get 0.
+int ody_ce_fwd(const void* logits, const int64_t* targets, float* loss, float* lse, int64_t T, int64_t V,
+               int64_t ignore_index, cudaStream_t stream);
+int ody_ce_bwd(void* logits, const int64_t* targets, const float* lse, const float* scale, int64_t T, int64_t V,
+               int64_t ignore_index, cudaStream_t stream);
+
+// ---- AdamW on flat shards: fp32 master / m / v, bf16 grad in, bf16 param out.
+int ody_adamw(float* master, float* m, float* v, const void* grad, void* param, int64_t n, float lr, float beta1,
+              float beta2, float eps, float weight_decay, int step, float grad_scale, cudaStream_t stream);
+
+// ---- merge of two partial attention results (ring attention): out/lse fp32 running, o bf16 / l fp32 partial
+int ody_attn_merge(float* out, float* lse, const void* o, const float* l, int64_t T, int H, int hd, int64_t row0,
+                   int64_t T_total, cudaStream_t stream);
+
+// ---- bf16 GEMM on tcgen05 (fp32 accumulate in TMEM).  layout 0: C = A[M,K] B[N,K]^T ; 1: C = A[M,K] B[K,N] ;
+// 2: C = A[K,M]^T B[K,N].  ld* are row pitches in elements (multiples of 8).  accumulate: C += result.
+// err: device int that receives a non-zero code if a bounded wait inside the kernel gave up.
+int ody_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                  int layout, int accumulate, int* err, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

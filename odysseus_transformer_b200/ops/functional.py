@@ -24,7 +24,7 @@ from . import native, torch_ref as R
 
 def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C[M,N] = A[M,K] @ B[N,K]^T  (the forward of a linear layer: x @ W^T)."""
-    if native.use_native(a) and a.dtype == torch.bfloat16:
+    if native.use_native(a):
         return native.lib().gemm(a, b, out, 0, False)
     if out is None:
         return a @ b.t()
@@ -33,7 +33,7 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
 
 def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C[M,N] = A[M,K] @ B[K,N]  (dgrad: dy @ W)."""
-    if native.use_native(a) and a.dtype == torch.bfloat16:
+    if native.use_native(a):
         return native.lib().gemm(a, b, out, 1, False)
     if out is None:
         return a @ b
@@ -43,7 +43,7 @@ def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
 def gemm_tn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
             accumulate: bool = False) -> torch.Tensor:
     """C[M,N] (+)= A[K,M]^T @ B[K,N]  (wgrad: dy^T @ x)."""
-    if native.use_native(a) and a.dtype == torch.bfloat16:
+    if native.use_native(a):
         return native.lib().gemm(a, b, out, 2, accumulate)
     if out is None:
         return a.t() @ b
@@ -225,7 +225,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 def attn_block_fwd(q, k, v, causal: bool, scale: Optional[float] = None):
     """One attention block -> (out [Tq,H,hd], lse [H,Tq] fp32)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if native.use_native(q):
+    if native.use_native(q) and native.has_native_attention():
         return native.lib().attn_fwd(q, k, v, causal, scale)
     if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
         return _aten_flash_fwd(q, k, v, causal, scale)
@@ -235,7 +235,7 @@ def attn_block_fwd(q, k, v, causal: bool, scale: Optional[float] = None):
 def attn_block_bwd(do, q, k, v, o, lse, causal: bool, scale: Optional[float] = None):
     """Backward of one block given the final (o, lse) of q's rows -> (dq, dk, dv)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if native.use_native(q):
+    if native.use_native(q) and native.has_native_attention():
         return native.lib().attn_bwd(do, q, k, v, o, lse, causal, scale)
     if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
         return _aten_flash_bwd(do, q, k, v, o, lse, causal, scale)

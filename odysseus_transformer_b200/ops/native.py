@@ -17,8 +17,6 @@ _lib = None
 _err: Optional[BaseException] = None
 _backend = os.environ.get("ODY_BACKEND", "auto")  # "fused" | "library" | "auto"
 
-# number of launches of kernels from this package since the last reset (bench.py reports it)
-_launches = 0
 
 
 def set_backend(name: str) -> None:
@@ -63,8 +61,10 @@ def available() -> bool:
 
 
 def use_native(t) -> bool:
-    """True when tensor ``t`` should go through the sm_100a kernels."""
+    """True when tensor ``t`` should go through the sm_100a kernels (CUDA, bf16 or integer)."""
     if not t.is_cuda or _backend == "library":
+        return False
+    if t.is_floating_point() and str(t.dtype) != "torch.bfloat16":
         return False
     if _backend == "fused":
         lib()          # raises loudly when the extension is missing
@@ -72,15 +72,25 @@ def use_native(t) -> bool:
     return available()
 
 
-def count_launch(n: int = 1) -> None:
-    global _launches
-    _launches += n
+def has_native_attention() -> bool:
+    return available() and hasattr(lib(), "attn_fwd")
 
 
 def reset_launch_count() -> None:
-    global _launches
-    _launches = 0
+    if available():
+        lib().reset_launch_count()
 
 
 def launch_count() -> int:
-    return _launches
+    """Launches of this package's own kernels since the last reset."""
+    return int(lib().launch_count()) if available() else 0
+
+
+def check_status(device_index: int = 0) -> None:
+    """Raise if a bounded in-kernel wait gave up since the last check (codes in csrc/sm100.cuh)."""
+    if not available():
+        return
+    st = int(lib().status(device_index))
+    if st != 0:
+        lib().clear_status(device_index)
+        raise RuntimeError(f"odysseus_transformer_b200 kernel reported status {st} (a bounded device-side wait expired)")

@@ -1,0 +1,204 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same op (needs a B200)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from odysseus_transformer_b200.ops import native
+    native.set_backend("fused")
+    return native.lib()
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+
+def _check_status(lib):
+    torch.cuda.synchronize()
+    assert lib.status(0) == 0, f"kernel status {lib.status(0)}"
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (300, 264, 200), (1000, 72, 136),
+               (2048, 4096, 1024), (8, 8, 8)]
+
+
+@pytest.mark.parametrize("layout", [0, 1, 2])
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm(lib, layout, M, N, K):
+    torch.manual_seed(M * 7 + N * 3 + K + layout)
+    if layout == 0:
+        a, b = _rand(M, K), _rand(N, K)
+        ref = a.float() @ b.float().t()
+    elif layout == 1:
+        a, b = _rand(M, K), _rand(K, N)
+        ref = a.float() @ b.float()
+    else:
+        a, b = _rand(K, M), _rand(K, N)
+        ref = a.float().t() @ b.float()
+    c = lib.gemm(a, b, None, layout, False)
+    _check_status(lib)
+    err = (c.float() - ref).abs().max().item()
+    tol = 0.02 * math.sqrt(K) + 1e-2 * ref.abs().max().item()
+    assert err <= tol, f"layout {layout} {M}x{N}x{K}: max err {err} > {tol}"
+    # relative Frobenius error is the sharper check (catches a wrong k-slice or swizzle)
+    rel = (c.float() - ref).norm() / ref.norm()
+    assert rel < 5e-3, f"layout {layout} {M}x{N}x{K}: rel err {rel}"
+
+
+def test_gemm_accumulate_and_strided_out(lib):
+    M, N, K = 512, 384, 256
+    a, b = _rand(K, M), _rand(K, N)
+    base = _rand(M, N)
+    out = base.clone()
+    lib.gemm(a, b, out, 2, True)
+    _check_status(lib)
+    ref = base.float() + a.float().t() @ b.float()
+    assert ((out.float() - ref).norm() / ref.norm()) < 5e-3
+    # strided A (a column slice of a wider matrix) and strided out
+    wide = _rand(M, 2 * K)
+    w = _rand(N, K)
+    big = torch.zeros(M, 2 * N, device="cuda", dtype=torch.bfloat16)
+    lib.gemm(wide[:, K:], w, big[:, :N], 0, False)
+    _check_status(lib)
+    ref = wide[:, K:].float() @ w.float().t()
+    assert ((big[:, :N].float() - ref).norm() / ref.norm()) < 5e-3
+    assert big[:, N:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("rows,dim", [(64, 256), (1000, 4096), (33, 1024), (17, 8192)])
+def test_rmsnorm(lib, rows, dim):
+    from odysseus_transformer_b200.ops import torch_ref as R
+    x, d, w = _rand(rows, dim), _rand(rows, dim), _rand(dim) + 1
+    y, rstd = lib.rmsnorm_fwd(x, w, 1e-5)
+    yr, rr = R.rmsnorm_fwd(x, w, 1e-5)
+    torch.testing.assert_close(y.float(), yr.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(rstd, rr, rtol=1e-4, atol=1e-5)
+    s, y2, rstd2 = lib.add_rmsnorm_fwd(x, d, w, 1e-5)
+    sr, y2r, r2r = R.add_rmsnorm_fwd(x, d, w, 1e-5)
+    torch.testing.assert_close(s.float(), sr.float(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(y2.float(), y2r.float(), rtol=2e-2, atol=2e-2)
+    dy, ds = _rand(rows, dim), _rand(rows, dim)
+    dx, dw = lib.rmsnorm_bwd(dy, x, w, rstd, None)
+    dxr, dwr = R.rmsnorm_bwd(dy, x, w, rr)
+    torch.testing.assert_close(dx.float(), dxr.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(dw, dwr, rtol=1e-3, atol=1e-2 * math.sqrt(rows))
+    dx2, _ = lib.rmsnorm_bwd(dy, x, w, rstd, ds)
+    torch.testing.assert_close(dx2.float(), dxr.float() + ds.float(), rtol=2e-2, atol=4e-2)
+
+
+def test_rope(lib):
+    from odysseus_transformer_b200.ops import torch_ref as R
+    T, H, hd = 777, 6, 128
+    pos = torch.randint(0, 200000, (T,), device="cuda")
+    cos, sin = lib.rope_tables(pos, hd, 10000.0)
+    cr, sr = R.rope_tables(pos, hd, 10000.0)
+    torch.testing.assert_close(cos, cr, rtol=0, atol=2e-3)   # fp32 angles of ~2e5 rad carry ~1e-2 rad of rounding
+    torch.testing.assert_close(sin, sr, rtol=0, atol=2e-3)
+    x = _rand(T, H, hd)
+    want = x.clone()
+    want[:, :4] = R.rope_apply(x[:, :4], cr, sr, False)
+    got = x.clone()
+    lib.rope_inplace_(got, 4, cr, sr, False)
+    torch.testing.assert_close(got.float(), want.float(), rtol=1e-2, atol=1e-2)
+    back = got.clone()
+    lib.rope_inplace_(back, 4, cr, sr, True)
+    torch.testing.assert_close(back.float(), x.float(), rtol=2e-2, atol=3e-2)
+    # strided rows: rotate a slice of a wider packed tensor
+    wide = _rand(T, 2 * H * hd)
+    view = wide[:, :H * hd].view(T, H, hd) if False else wide.view(T, 2 * H, hd)
+    ref = view.clone()
+    ref[:, :3] = R.rope_apply(view[:, :3], cr, sr, False)
+    lib.rope_inplace_(view, 3, cr, sr, False)
+    torch.testing.assert_close(view.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_swiglu(lib):
+    from odysseus_transformer_b200.ops import torch_ref as R
+    T, I = 300, 2816
+    gu, dh = _rand(T, 2 * I), _rand(T, I)
+    torch.testing.assert_close(lib.swiglu_fwd(gu).float(), R.swiglu_fwd(gu).float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(lib.swiglu_bwd(dh, gu).float(), R.swiglu_bwd(dh, gu).float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("T,V", [(64, 32000), (513, 128256), (7, 1000)])
+def test_cross_entropy(lib, T, V):
+    from odysseus_transformer_b200.ops import torch_ref as R
+    logits = _rand(T, V, scale=3.0)
+    tg = torch.randint(0, V, (T,), device="cuda")
+    tg[::5] = -100
+    loss, lse = lib.ce_fwd(logits, tg, -100)
+    lr, lser = R.cross_entropy_fwd(logits, tg, -100)
+    torch.testing.assert_close(lse, lser, rtol=1e-4, atol=1e-3)
+    torch.testing.assert_close(loss, lr, rtol=1e-4, atol=1e-3)
+    scale = torch.tensor([1.0 / T], device="cuda")
+    a, b = logits.clone(), logits.clone()
+    lib.ce_bwd_(a, tg, lse, scale, -100)
+    R.cross_entropy_bwd_(b, tg, lser, scale, -100)
+    torch.testing.assert_close(a.float(), b.float(), rtol=2e-2, atol=1e-5)
+
+
+def test_adamw(lib):
+    from odysseus_transformer_b200.ops import torch_ref as R
+    n = 8 * 100003
+    master = torch.randn(n, device="cuda")
+    m, v = torch.randn(n, device="cuda") * 0.01, torch.rand(n, device="cuda") * 1e-4
+    g = _rand(n, scale=0.01)
+    p = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    m2, v2, master2, p2 = m.clone(), v.clone(), master.clone(), p.clone()
+    lib.adamw_step(master, m, v, g, p, 1e-3, 0.9, 0.999, 1e-8, 0.01, 3, 1.0)
+    R.adamw_step_(master2, m2, v2, g, p2, 1e-3, 0.9, 0.999, 1e-8, 0.01, 3, 1.0)
+    torch.testing.assert_close(master, master2, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(m, m2, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(v, v2, rtol=1e-5, atol=1e-9)
+    torch.testing.assert_close(p.float(), p2.float(), rtol=1e-2, atol=1e-3)
+
+
+def test_attn_merge(lib):
+    from odysseus_transformer_b200.ops import torch_ref as R
+    Tt, T, H, hd, row0 = 96, 48, 3, 128, 48
+    out = torch.randn(Tt, H, hd, device="cuda")
+    lse = torch.randn(H, Tt, device="cuda")
+    o = _rand(T, H, hd)
+    l = torch.randn(H, T, device="cuda")
+    want_o, want_l = R.merge_attn(out[row0:], lse[:, row0:], o.float(), l)
+    got_o, got_l = out.clone(), lse.clone()
+    lib.attn_merge_(got_o, got_l, o, l, row0)
+    torch.testing.assert_close(got_o[row0:], want_o, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(got_l[:, row0:], want_l, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(got_o[:row0], out[:row0])
+
+
+def test_model_step_fused_vs_library():
+    """One fwd+bwd of the small model: own kernels vs the torch/cuBLAS/flash path, same weights."""
+    from odysseus_transformer_b200.config import get_model_config
+    from odysseus_transformer_b200.mesh import ParallelContext
+    from odysseus_transformer_b200.ops import native
+    from odysseus_transformer_b200.parallel.apply import build_model
+    from odysseus_transformer_b200.utils.debug import export_hf_grads
+    cfg = get_model_config("small")
+    L = 512
+    dev = torch.device("cuda", 0)
+    ctx = ParallelContext(device=dev)
+    g = torch.Generator().manual_seed(0)
+    batch = torch.randint(cfg.vocab_size, (1, L + 1), generator=g).to(dev)
+    pos = torch.arange(L, device=dev).unsqueeze(0)
+    res = {}
+    for be in ("library", "fused"):
+        native.set_backend(be)
+        model = build_model(cfg, "odysseus", ctx, dtype=torch.bfloat16, device=dev, seed=0)
+        loss = model(batch[:, :-1], pos, labels=batch[:, 1:])
+        loss.backward()
+        res[be] = (loss.detach().float().item(), export_hf_grads(model))
+    native.set_backend("fused")
+    native.check_status(0)
+    assert abs(res["fused"][0] - res["library"][0]) < 2e-2, (res["fused"][0], res["library"][0])
+    for k, gl in res["library"][1].items():
+        gf = res["fused"][1][k]
+        denom = gl.float().norm().item() + 1e-6
+        rel = (gf.float() - gl.float()).norm().item() / denom
+        assert rel < 0.08, f"{k}: rel grad diff {rel}"
