@@ -6,6 +6,9 @@
 #include <torch/extension.h>
 
 #include <map>
+#include <sstream>
+#include <stdexcept>
+#include <string>
 #include <mutex>
 
 #include "ody_kernels.h"
@@ -16,12 +19,28 @@ int64_t g_launches = 0;
 std::map<int, at::Tensor> g_status;
 std::mutex g_mu;
 
-#define ODY_CHECK(call, what)                                                                        \
-  do {                                                                                               \
-    int rc__ = (call);                                                                               \
-    TORCH_CHECK(rc__ == 0, "odysseus_transformer_b200: ", what, " failed with code ", rc__, " (",    \
-                (rc__ > 0 && rc__ < 1000 ? cudaGetErrorString((cudaError_t)rc__) : "see ody_kernels.h"), ")"); \
+// Failures are reported with std::runtime_error (pybind11 maps it to RuntimeError) rather than
+// c10::Error, whose backtrace capture crashed on the B200 hosts when raised from this module.
+[[noreturn]] inline void ody_fail(const std::string& msg) { throw std::runtime_error("odysseus_transformer_b200: " + msg); }
+
+#define ODY_CHECK(call, what)                                                                         \
+  do {                                                                                                \
+    int rc__ = (call);                                                                                \
+    if (rc__ != 0) {                                                                                  \
+      std::string m__ = std::string(what) + " failed with code " + std::to_string(rc__);              \
+      if (rc__ > 0 && rc__ < 1000) m__ += std::string(" (") + cudaGetErrorString((cudaError_t)rc__) + ")"; \
+      ody_fail(m__);                                                                                  \
+    }                                                                                                 \
   } while (0)
+
+template <class... A>
+inline void ody_req(bool cond, const A&... parts) {
+  if (!cond) {
+    std::ostringstream o;
+    (o << ... << parts);
+    ody_fail(o.str());
+  }
+}
 
 inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
@@ -37,8 +56,8 @@ int* status_ptr(const at::Tensor& like) {
 }
 
 void check_bf16(const at::Tensor& t, const char* name) {
-  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
-  TORCH_CHECK(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
+  ody_req(t.is_cuda(), name, " must be a CUDA tensor");
+  ody_req(t.scalar_type() == at::kBFloat16, name, " must be bfloat16");
 }
 
 // ------------------------------------------------------------------------------------------- GEMM
@@ -46,17 +65,17 @@ at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at
                 bool accumulate) {
   check_bf16(a, "a");
   check_bf16(b, "b");
-  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm expects 2-D operands");
-  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm operands must be row-major (last stride 1)");
+  ody_req(a.dim() == 2 && b.dim() == 2, "gemm expects 2-D operands");
+  ody_req(a.stride(1) == 1 && b.stride(1) == 1, "gemm operands must be row-major (last stride 1)");
   c10::cuda::CUDAGuard guard(a.device());
   int64_t M, N, K;
-  if (layout == 0) { M = a.size(0); K = a.size(1); N = b.size(0); TORCH_CHECK(b.size(1) == K, "K mismatch"); }
-  else if (layout == 1) { M = a.size(0); K = a.size(1); N = b.size(1); TORCH_CHECK(b.size(0) == K, "K mismatch"); }
-  else { K = a.size(0); M = a.size(1); N = b.size(1); TORCH_CHECK(b.size(0) == K, "K mismatch"); }
+  if (layout == 0) { M = a.size(0); K = a.size(1); N = b.size(0); ody_req(b.size(1) == K, "K mismatch"); }
+  else if (layout == 1) { M = a.size(0); K = a.size(1); N = b.size(1); ody_req(b.size(0) == K, "K mismatch"); }
+  else { K = a.size(0); M = a.size(1); N = b.size(1); ody_req(b.size(0) == K, "K mismatch"); }
   at::Tensor c = out.has_value() ? out.value() : at::empty({M, N}, a.options());
   check_bf16(c, "out");
-  TORCH_CHECK(c.dim() == 2 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1, "bad out shape");
-  TORCH_CHECK(!accumulate || out.has_value(), "accumulate needs out");
+  ody_req(c.dim() == 2 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1, "bad out shape");
+  ody_req(!accumulate || out.has_value(), "accumulate needs out");
   if (M == 0 || N == 0) return c;
   if (K == 0) { if (!accumulate) c.zero_(); return c; }
   ODY_CHECK(ody_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
@@ -69,7 +88,7 @@ at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at
 // ------------------------------------------------------------------------------------------- RMSNorm
 std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps) {
   check_bf16(x, "x"); check_bf16(w, "w");
-  TORCH_CHECK(x.is_contiguous() && w.is_contiguous(), "rmsnorm: contiguous inputs required");
+  ody_req(x.is_contiguous() && w.is_contiguous(), "rmsnorm: contiguous inputs required");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t dim = x.size(-1), rows = x.numel() / dim;
   auto y = at::empty_like(x);
@@ -82,8 +101,8 @@ std::vector<at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, do
 
 std::vector<at::Tensor> add_rmsnorm_fwd(const at::Tensor& x, const at::Tensor& delta, const at::Tensor& w, double eps) {
   check_bf16(x, "x"); check_bf16(delta, "delta"); check_bf16(w, "w");
-  TORCH_CHECK(x.is_contiguous() && delta.is_contiguous() && w.is_contiguous(), "add_rmsnorm: contiguous inputs required");
-  TORCH_CHECK(x.sizes() == delta.sizes(), "add_rmsnorm: shape mismatch");
+  ody_req(x.is_contiguous() && delta.is_contiguous() && w.is_contiguous(), "add_rmsnorm: contiguous inputs required");
+  ody_req(x.sizes() == delta.sizes(), "add_rmsnorm: shape mismatch");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t dim = x.size(-1), rows = x.numel() / dim;
   auto s = at::empty_like(x);
@@ -98,7 +117,7 @@ std::vector<at::Tensor> add_rmsnorm_fwd(const at::Tensor& x, const at::Tensor& d
 std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w,
                                     const at::Tensor& rstd, const c10::optional<at::Tensor>& ds) {
   check_bf16(dy, "dy"); check_bf16(x, "x"); check_bf16(w, "w");
-  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous(), "rmsnorm_bwd: contiguous inputs required");
+  ody_req(dy.is_contiguous() && x.is_contiguous(), "rmsnorm_bwd: contiguous inputs required");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t dim = x.size(-1), rows = x.numel() / dim;
   auto dx = at::empty_like(x);
@@ -106,7 +125,7 @@ std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, c
   const int nb = ody_rmsnorm_bwd_blocks(rows, (int)dim);
   auto partial = at::empty({nb, dim}, x.options().dtype(at::kFloat));
   const void* dsp = nullptr;
-  if (ds.has_value()) { check_bf16(ds.value(), "ds"); TORCH_CHECK(ds.value().is_contiguous()); dsp = ds.value().data_ptr(); }
+  if (ds.has_value()) { check_bf16(ds.value(), "ds"); ody_req(ds.value().is_contiguous()); dsp = ds.value().data_ptr(); }
   ODY_CHECK(ody_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dsp, dx.data_ptr(),
                             dw.data_ptr<float>(), partial.data_ptr<float>(), rows, (int)dim, cur_stream()), "rmsnorm_bwd");
   g_launches += 2;
@@ -115,7 +134,7 @@ std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, c
 
 // ------------------------------------------------------------------------------------------- RoPE
 std::vector<at::Tensor> rope_tables(const at::Tensor& pos, int64_t head_dim, double theta) {
-  TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == at::kLong && pos.is_contiguous(), "positions: contiguous int64 CUDA");
+  ody_req(pos.is_cuda() && pos.scalar_type() == at::kLong && pos.is_contiguous(), "positions: contiguous int64 CUDA");
   c10::cuda::CUDAGuard guard(pos.device());
   const int64_t T = pos.numel();
   auto opt = pos.options().dtype(at::kFloat);
@@ -128,10 +147,10 @@ std::vector<at::Tensor> rope_tables(const at::Tensor& pos, int64_t head_dim, dou
 
 void rope_inplace_(at::Tensor x, int64_t n_rot, const at::Tensor& cos, const at::Tensor& sin, bool inverse) {
   check_bf16(x, "x");
-  TORCH_CHECK(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2), "rope: x must be [T, heads, hd] with packed heads");
-  TORCH_CHECK(cos.is_contiguous() && sin.is_contiguous() && cos.scalar_type() == at::kFloat, "rope tables: fp32 contiguous");
-  TORCH_CHECK(cos.size(0) == x.size(0) && cos.size(1) * 2 == x.size(2), "rope tables shape");
-  TORCH_CHECK(n_rot <= x.size(1));
+  ody_req(x.dim() == 3 && x.stride(2) == 1 && x.stride(1) == x.size(2), "rope: x must be [T, heads, hd] with packed heads");
+  ody_req(cos.is_contiguous() && sin.is_contiguous() && cos.scalar_type() == at::kFloat, "rope tables: fp32 contiguous");
+  ody_req(cos.size(0) == x.size(0) && cos.size(1) * 2 == x.size(2), "rope tables shape");
+  ody_req(n_rot <= x.size(1));
   c10::cuda::CUDAGuard guard(x.device());
   ODY_CHECK(ody_rope_inplace(x.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), x.size(0), (int)n_rot,
                              (int)x.size(2), x.stride(0), inverse ? 1 : 0, cur_stream()), "rope_inplace");
@@ -147,7 +166,7 @@ at::Tensor rope_apply(const at::Tensor& x, const at::Tensor& cos, const at::Tens
 // ------------------------------------------------------------------------------------------- SwiGLU
 at::Tensor swiglu_fwd(const at::Tensor& gu) {
   check_bf16(gu, "gate_up");
-  TORCH_CHECK(gu.is_contiguous() && gu.dim() == 2);
+  ody_req(gu.is_contiguous() && gu.dim() == 2);
   c10::cuda::CUDAGuard guard(gu.device());
   const int64_t T = gu.size(0), I = gu.size(1) / 2;
   auto h = at::empty({T, I}, gu.options());
@@ -158,7 +177,7 @@ at::Tensor swiglu_fwd(const at::Tensor& gu) {
 
 at::Tensor swiglu_bwd(const at::Tensor& dh, const at::Tensor& gu) {
   check_bf16(gu, "gate_up"); check_bf16(dh, "dh");
-  TORCH_CHECK(gu.is_contiguous() && dh.is_contiguous());
+  ody_req(gu.is_contiguous() && dh.is_contiguous());
   c10::cuda::CUDAGuard guard(gu.device());
   const int64_t T = gu.size(0), I = gu.size(1) / 2;
   auto dgu = at::empty_like(gu);
@@ -170,7 +189,7 @@ at::Tensor swiglu_bwd(const at::Tensor& dh, const at::Tensor& gu) {
 // ------------------------------------------------------------------------------------------- cross-entropy
 std::vector<at::Tensor> ce_fwd(const at::Tensor& logits, const at::Tensor& targets, int64_t ignore_index) {
   check_bf16(logits, "logits");
-  TORCH_CHECK(logits.is_contiguous() && logits.dim() == 2 && targets.scalar_type() == at::kLong && targets.is_contiguous());
+  ody_req(logits.is_contiguous() && logits.dim() == 2 && targets.scalar_type() == at::kLong && targets.is_contiguous());
   c10::cuda::CUDAGuard guard(logits.device());
   const int64_t T = logits.size(0), V = logits.size(1);
   auto opt = logits.options().dtype(at::kFloat);
@@ -184,7 +203,7 @@ std::vector<at::Tensor> ce_fwd(const at::Tensor& logits, const at::Tensor& targe
 void ce_bwd_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse, const at::Tensor& scale,
              int64_t ignore_index) {
   check_bf16(logits, "logits");
-  TORCH_CHECK(logits.is_contiguous() && scale.is_cuda() && scale.scalar_type() == at::kFloat);
+  ody_req(logits.is_contiguous() && scale.is_cuda() && scale.scalar_type() == at::kFloat);
   c10::cuda::CUDAGuard guard(logits.device());
   const int64_t T = logits.size(0), V = logits.size(1);
   for (int64_t r0 = 0; r0 < T; r0 += 32768) {   // grid.y limit
@@ -199,8 +218,8 @@ void ce_bwd_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse
 void adamw_step(at::Tensor master, at::Tensor m, at::Tensor v, const at::Tensor& grad, at::Tensor param, double lr,
                 double beta1, double beta2, double eps, double weight_decay, int64_t step, double grad_scale) {
   check_bf16(grad, "grad"); check_bf16(param, "param");
-  TORCH_CHECK(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
-  TORCH_CHECK(master.is_contiguous() && m.is_contiguous() && v.is_contiguous() && grad.is_contiguous() && param.is_contiguous());
+  ody_req(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  ody_req(master.is_contiguous() && m.is_contiguous() && v.is_contiguous() && grad.is_contiguous() && param.is_contiguous());
   c10::cuda::CUDAGuard guard(master.device());
   ODY_CHECK(ody_adamw(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr(), param.data_ptr(),
                       master.numel(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)weight_decay, (int)step,
@@ -211,8 +230,8 @@ void adamw_step(at::Tensor master, at::Tensor m, at::Tensor v, const at::Tensor&
 // ------------------------------------------------------------------------------------------- attention merge
 void attn_merge_(at::Tensor out, at::Tensor lse, const at::Tensor& o, const at::Tensor& l, int64_t row0) {
   check_bf16(o, "o");
-  TORCH_CHECK(out.scalar_type() == at::kFloat && lse.scalar_type() == at::kFloat && l.scalar_type() == at::kFloat);
-  TORCH_CHECK(out.is_contiguous() && lse.is_contiguous() && o.is_contiguous() && l.is_contiguous());
+  ody_req(out.scalar_type() == at::kFloat && lse.scalar_type() == at::kFloat && l.scalar_type() == at::kFloat);
+  ody_req(out.is_contiguous() && lse.is_contiguous() && o.is_contiguous() && l.is_contiguous());
   c10::cuda::CUDAGuard guard(out.device());
   ODY_CHECK(ody_attn_merge(out.data_ptr<float>(), lse.data_ptr<float>(), o.data_ptr(), l.data_ptr<float>(), o.size(0),
                            (int)o.size(1), (int)o.size(2), row0, out.size(0), cur_stream()), "attn_merge");
@@ -242,6 +261,9 @@ void reset_launch_count() { g_launches = 0; }
 void add_launches(int64_t n) { g_launches += n; }
 
 }  // namespace
+
+int* ody_status_ptr(const at::Tensor& like) { return status_ptr(like); }
+void ody_count_launches(int64_t n) { g_launches += n; }
 
 // attention (defined in attn_bindings.cpp)
 void ody_register_attention(pybind11::module& m);

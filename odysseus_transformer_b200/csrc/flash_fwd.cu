@@ -1,0 +1,313 @@
+// Causal / full softmax attention forward for sm_100a (head_dim 128, bf16, GQA), with log-sum-exp.
+//
+// The reference reaches FlashAttention-2 (an sm80 mma.sync design) through HF's
+// _flash_attention_forward (reference decoder/odysseus.py:256-263) and through its ring / Ulysses
+// dependencies.  This kernel is written for the Blackwell execution model instead:
+//
+//   * one CTA per (128-row query tile, head); K/V blocks of 128 rows stream through a 2-stage TMA ring;
+//   * S = Q K^T and O += P V are tcgen05.mma instructions issued by one thread; S (double buffered), the
+//     bf16 probabilities P (double buffered, fed back as the TMEM A operand) and the fp32 O accumulator
+//     live in TMEM (2*128 + 2*64 + 128 = 512 columns);
+//   * four softmax warps, one thread per query row, read S straight from TMEM (no cross-thread
+//     reductions), work in the exp2 domain and rescale O lazily: the running maximum used for
+//     exponentiation only moves when it would grow by more than 2^8, so the O read-modify-write is rare;
+//   * QK^T of block j+1 is issued before P V of block j, so the tensor core works while the softmax
+//     warps are busy.
+//
+// q [Tq, H, 128], k/v [Tk, Hkv, 128] with arbitrary row pitch; out [Tq, H, 128] bf16; lse [H, Tq] fp32
+// (natural log).  causal requires Tq == Tk (row i sees keys 0..i).
+#include "ody_kernels.h"
+#include "sm100.cuh"
+
+namespace ody {
+namespace fwd {
+
+constexpr int BM = 128, BN = 128, HD = 128;
+constexpr int TILE_BYTES = 128 * HD * 2;     // 32 KB: two 64-column halves of [128 rows x 128 B]
+constexpr int HALF_BYTES = TILE_BYTES / 2;
+constexpr int KV_STAGES = 2;
+constexpr int SMEM_TILES = TILE_BYTES * (1 + 2 * KV_STAGES);
+constexpr int SMEM_TOTAL = SMEM_TILES + 256 + 1024;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
+
+struct Bars {
+  uint64_t q_full;
+  uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
+  uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
+  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                 float* __restrict__ lse, int Tq, int Tk, int H, int Hkv, int causal, float scale,
+                 int* __restrict__ err) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TILE_BYTES;
+  uint8_t* sV = sK + KV_STAGES * TILE_BYTES;
+  Bars* bars = (Bars*)(smem + SMEM_TILES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_q_tiles = (Tq + BM - 1) / BM;
+  const int qt = causal ? (num_q_tiles - 1 - (int)blockIdx.x) : (int)blockIdx.x;   // heavy tiles first
+  const int head = blockIdx.y;
+  const int kv_head = head / (H / Hkv);
+  const int q0 = qt * BM;
+  const int nblk = causal ? (qt + 1) : (Tk + BN - 1) / BN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->s_full[b], 1);
+      mbar_init(&bars->p_full[b], 128);
+      mbar_init(&bars->pv_done[b], 1);
+    }
+    mbar_init(&bars->drain, 1);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmQ);
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmO);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(&bars->q_full, TILE_BYTES);
+      tma_load_3d(sQ, &tmQ, 0, head, q0, &bars->q_full);
+      tma_load_3d(sQ + HALF_BYTES, &tmQ, 64, head, q0, &bars->q_full);
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
+        tma_load_3d(sK + s * TILE_BYTES, &tmK, 0, kv_head, j * BN, &bars->k_full[s]);
+        tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, 64, kv_head, j * BN, &bars->k_full[s]);
+        if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
+        tma_load_3d(sV + s * TILE_BYTES, &tmV, 0, kv_head, j * BN, &bars->v_full[s]);
+        tma_load_3d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, 64, kv_head, j * BN, &bars->v_full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC_QK = make_idesc_bf16(BM, BN, 0, 0);
+      constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
+      const uint32_t aQ = smem_u32(sQ);
+      auto issue_pv = [&](int j) -> bool {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->p_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) return false;
+        if (!mbar_wait(&bars->v_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + b * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const uint64_t bdesc = make_smem_desc(aV + kk * 2048, HALF_BYTES, 1024);
+          umma_ts(tmem + COL_O, tmem + COL_P + b * 64 + kk * 8, bdesc, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&bars->v_empty[b]);
+        umma_commit(&bars->pv_done[b]);
+        return true;
+      };
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->k_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + b * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          umma_ss(tmem + COL_S + b * BN, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024),
+                  IDESC_QK, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->k_empty[b]);
+        umma_commit(&bars->s_full[b]);
+        if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
+      }
+      if (ok) ok = issue_pv(nblk - 1);
+      if (!ok) {
+        umma_commit(&bars->drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue (warps 2..5)
+    const int q = warp & 3;
+    const int r = q * 32 + lane;                       // row inside the tile == TMEM lane
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const float sl2 = scale * 1.4426950408889634f;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk; ++j) {
+      const int b = j & 1;
+      if (!mbar_wait(&bars->s_full[b], (j >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem + COL_S + b * BN + lane_off + c * 32, sv + 32 * c);
+      tmem_ld_wait();
+      const int kv0 = j * BN;
+      if (causal && j == qt) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (c > r) sv[c] = 0xff800000u;   // -inf
+      }
+      if (kv0 + BN > Tk) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (kv0 + c >= Tk) sv[c] = 0xff800000u;
+      }
+      float mx = __uint_as_float(sv[0]);
+#pragma unroll
+      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+      const float m_new = fmaxf(m_used, mx * sl2);
+      const bool need = (m_new - m_used) > 8.f;      // true on the first block (m_used = -inf)
+      if (j == 0) {
+        m_used = m_new;
+      } else if (__any_sync(0xffffffffu, need)) {
+        // the running maximum moved by more than 2^8 for some row of this warp: rescale O and l
+        if (!mbar_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC)) { ok = false; break; }
+        tc_fence_after();
+        const float alpha = need ? fast_exp2(m_used - m_new) : 1.f;
+        if (need) m_used = m_new;
+        l *= alpha;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[16];
+          tmem_ld_32x16(tmem + COL_O + lane_off + c * 16, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 16; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * alpha);
+          tmem_st_32x16(tmem + COL_O + lane_off + c * 16, o);
+        }
+        tmem_st_wait();
+      }
+      float rowsum = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - m_used);
+        const float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - m_used);
+        rowsum += p0 + p1;
+        pk[c] = pack_bf16(p0, p1);
+      }
+      l += rowsum;
+      if (j >= 2) {   // P buffer b was last read by P V of block j-2
+        if (!mbar_wait(&bars->pv_done[b], ((j - 2) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_st_32x16(tmem + COL_P + b * 64 + lane_off + c * 16, pk + 16 * c);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[b]);
+    }
+    // epilogue: O / l -> bf16 -> swizzled smem (the Q tile is dead by now) -> TMA store; lse
+    if (ok) ok = mbar_wait(&bars->pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC);
+    if (ok) {
+      tc_fence_after();
+      const float inv_l = 1.f / l;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t o[16];
+        tmem_ld_32x16(tmem + COL_O + lane_off + c * 16, o);
+        tmem_ld_wait();
+        const int half = c >> 2;                // 64 output columns per half
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          uint4 v4;
+          v4.x = pack_bf16(__uint_as_float(o[8 * t + 0]) * inv_l, __uint_as_float(o[8 * t + 1]) * inv_l);
+          v4.y = pack_bf16(__uint_as_float(o[8 * t + 2]) * inv_l, __uint_as_float(o[8 * t + 3]) * inv_l);
+          v4.z = pack_bf16(__uint_as_float(o[8 * t + 4]) * inv_l, __uint_as_float(o[8 * t + 5]) * inv_l);
+          v4.w = pack_bf16(__uint_as_float(o[8 * t + 6]) * inv_l, __uint_as_float(o[8 * t + 7]) * inv_l);
+          const int chunk = (c & 3) * 2 + t;    // 16-byte chunk inside the 128-byte row of this half
+          *reinterpret_cast<uint4*>(sQ + half * HALF_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
+        }
+      }
+      if (q0 + r < Tq) lse[(int64_t)head * Tq + q0 + r] = (m_used + log2f(l)) * 0.6931471805599453f;
+      fence_proxy_async_smem();
+    }
+    tc_fence_before();
+    named_barrier(1, 128);
+    if (ok && warp == 2 && lane == 0 && !*abort_flag) {
+      tma_store_3d(&tmO, sQ, 0, head, q0);
+      tma_store_3d(&tmO, sQ + HALF_BYTES, 64, head, q0);
+      tma_store_commit();
+      tma_store_wait<0>();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace fwd
+}  // namespace ody
+
+// q/k/v/o: bf16, head_dim 128, element strides: *_row (token pitch), heads packed (pitch 128).
+extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H,
+                             int Hkv, int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal,
+                             float scale, int* err, cudaStream_t st) {
+  using namespace ody;
+  using namespace ody::fwd;
+  if (Tq <= 0 || Tk <= 0 || H <= 0 || Hkv <= 0 || H % Hkv) return (int)cudaErrorInvalidValue;
+  if (causal && Tq != Tk) return (int)cudaErrorInvalidValue;
+  if ((q_row % 8) || (k_row % 8) || (v_row % 8) || (o_row % 8)) return (int)cudaErrorInvalidValue;
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  CUtensorMap tQ, tK, tV, tO;
+  int r;
+  if ((r = make_tmap_3d_bf16(&tQ, q, HD, H, Tq, HD * 2, q_row * 2, 64, 1, BM))) return 730000 + r;
+  if ((r = make_tmap_3d_bf16(&tK, k, HD, Hkv, Tk, HD * 2, k_row * 2, 64, 1, BN))) return 740000 + r;
+  if ((r = make_tmap_3d_bf16(&tV, v, HD, Hkv, Tk, HD * 2, v_row * 2, 64, 1, BN))) return 750000 + r;
+  if ((r = make_tmap_3d_bf16(&tO, o, HD, H, Tq, HD * 2, o_row * 2, 64, 1, BM))) return 760000 + r;
+  dim3 grid((Tq + BM - 1) / BM, H);
+  flash_fwd_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err);
+  return (int)cudaGetLastError();
+}

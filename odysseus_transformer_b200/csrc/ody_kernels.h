@@ -50,6 +50,20 @@ int ody_attn_merge(float* out, float* lse, const void* o, const float* l, int64_
 int ody_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                   int layout, int accumulate, int* err, cudaStream_t stream);
 
+// ---- attention forward (head_dim 128): q [Tq,H,128], k/v [Tk,Hkv,128], row pitches in elements; out bf16, lse [H,Tq]
+// fp32 natural log.  causal needs Tq == Tk.
+int ody_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H, int Hkv,
+                  int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal, float scale, int* err,
+                  cudaStream_t stream);
+
+// ---- attention backward.  workspace: ody_flash_bwd_workspace_bytes(Tq, H) bytes of scratch, 16-byte aligned.
+// dq/dk/dv may be row-pitched views (e.g. slices of one packed gradient tensor).
+int64_t ody_flash_bwd_workspace_bytes(int Tq, int H);
+int ody_flash_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,
+                  void* dk, void* dv, void* workspace, int Tq, int Tk, int H, int Hkv, int64_t do_row, int64_t q_row,
+                  int64_t k_row, int64_t v_row, int64_t o_row, int64_t dq_row, int64_t dk_row, int64_t dv_row, int causal,
+                  float scale, int* err, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

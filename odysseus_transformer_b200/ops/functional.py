@@ -225,7 +225,7 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 def attn_block_fwd(q, k, v, causal: bool, scale: Optional[float] = None):
     """One attention block -> (out [Tq,H,hd], lse [H,Tq] fp32)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if native.use_native(q) and native.has_native_attention():
+    if native.use_native(q) and native.has_native_attention() and q.shape[-1] == 128:
         return native.lib().attn_fwd(q, k, v, causal, scale)
     if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
         return _aten_flash_fwd(q, k, v, causal, scale)
@@ -235,8 +235,8 @@ def attn_block_fwd(q, k, v, causal: bool, scale: Optional[float] = None):
 def attn_block_bwd(do, q, k, v, o, lse, causal: bool, scale: Optional[float] = None):
     """Backward of one block given the final (o, lse) of q's rows -> (dq, dk, dv)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if native.use_native(q) and native.has_native_attention():
-        return native.lib().attn_bwd(do, q, k, v, o, lse, causal, scale)
+    if native.use_native(q) and native.has_native_attention_bwd() and q.shape[-1] == 128:
+        return native.lib().attn_bwd(do, q, k, v, o, lse, causal, scale, None, None, None)
     if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16):
         return _aten_flash_bwd(do, q, k, v, o, lse, causal, scale)
     return R.attn_bwd(do, q, k, v, o, lse, causal, scale)

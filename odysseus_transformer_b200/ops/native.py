@@ -76,6 +76,10 @@ def has_native_attention() -> bool:
     return available() and hasattr(lib(), "attn_fwd")
 
 
+def has_native_attention_bwd() -> bool:
+    return available() and hasattr(lib(), "attn_bwd")
+
+
 def reset_launch_count() -> None:
     if available():
         lib().reset_launch_count()

@@ -243,7 +243,7 @@ class _PackedRopeAttention(Function):
             dqkv[:, :hq] = dq
             dqkv[:, hq:hq + hkv] = dk
             dqkv[:, hq + hkv:] = dv
-        elif native.use_native(qkv) and native.has_native_attention():
+        elif native.use_native(qkv) and native.has_native_attention_bwd() and hd == 128:
             # the kernel writes dq/dk/dv straight into the packed gradient
             native.lib().attn_bwd(do, q, k, v, o, lse, True, scale,
                                   dqkv[:, :hq], dqkv[:, hq:hq + hkv], dqkv[:, hq + hkv:])

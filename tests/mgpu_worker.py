@@ -1,0 +1,69 @@
+"""Worker for the multi-GPU tests: run under torch.distributed.run, one rank per GPU.
+
+Usage: mgpu_worker.py MODE CONFIG SEQLEN ULYSSES RING BACKEND
+Every rank builds the model in MODE, runs one fwd+bwd on its shard, exports loss and HF-layout
+gradients; rank 0 compares them with a single-GPU run of the same weights on the library path."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    mode, cfg_name, L, U, R, backend = sys.argv[1], sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]), sys.argv[6]
+    from odysseus_transformer_b200.config import get_model_config
+    from odysseus_transformer_b200.mesh import ParallelContext, init_parallel_context
+    from odysseus_transformer_b200.ops import native
+    from odysseus_transformer_b200.parallel.apply import build_model, prepare_attn_inputs
+    from odysseus_transformer_b200.utils.debug import export_hf_grads
+    native.set_backend(backend)
+    ctx = init_parallel_context(mode, U, R, backend=backend, timeout_s=120)
+    if backend == "fused":
+        from odysseus_transformer_b200.comm import symm
+        symm.setup_fused_comm(ctx)
+    rank, world, dev = ctx.rank, ctx.world_size, ctx.device
+    cfg = get_model_config(cfg_name)
+    g = torch.Generator().manual_seed(0)
+    batch = torch.randint(cfg.vocab_size, (1, L + 1), generator=g)
+    pos = torch.arange(L).unsqueeze(0)
+    model = build_model(cfg, mode, ctx, dtype=torch.bfloat16, device=dev, seed=0)
+    s = prepare_attn_inputs(mode, batch[:, :-1], pos, batch[:, 1:], rank, world, dev, U, R)
+    gt = L * (world if mode == "dp" else 1)
+    for it in range(2):   # second iteration exercises buffer / flag reuse
+        for p in model.parameters():
+            p.grad = None
+        loss = model(s["local_input_ids"], s["local_position_ids"], labels=s["local_target_ids"], global_tokens=gt)
+        loss.backward()
+    total = loss.detach().float().clone()
+    dist.all_reduce(total)
+    grads = export_hf_grads(model)
+    torch.cuda.synchronize()
+    native.check_status(dev.index)
+    ok = True
+    if rank == 0:
+        native.set_backend("library")
+        ref = build_model(cfg, None, ParallelContext(device=dev), dtype=torch.bfloat16, device=dev, seed=0)
+        rl = ref(batch[:, :-1].to(dev), pos.to(dev), labels=batch[:, 1:].to(dev))
+        rl.backward()
+        rg = export_hf_grads(ref)
+        dl = abs(total.item() - rl.item())
+        worst, worst_k = 0.0, None
+        for k, v in rg.items():
+            rel = ((grads[k].float() - v.float()).norm() / (v.float().norm() + 1e-6)).item()
+            if rel > worst:
+                worst, worst_k = rel, k
+        print(f"RESULT mode={mode} backend={backend} loss={total.item():.5f} ref={rl.item():.5f} dloss={dl:.2e} "
+              f"worst_rel_grad={worst:.3e} ({worst_k})", flush=True)
+        ok = dl < 3e-2 and worst < 0.1
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.broadcast(flag, 0)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

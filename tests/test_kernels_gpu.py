@@ -202,3 +202,71 @@ def test_model_step_fused_vs_library():
         denom = gl.float().norm().item() + 1e-6
         rel = (gf.float() - gl.float()).norm().item() / denom
         assert rel < 0.08, f"{k}: rel grad diff {rel}"
+
+
+ATTN_CASES = [  # Tq, Tk, H, Hkv, causal
+    (128, 128, 2, 2, True), (512, 512, 4, 2, True), (1000, 1000, 2, 1, True), (2048, 2048, 8, 8, True),
+    (256, 384, 2, 2, False), (300, 200, 4, 1, False), (128, 1024, 2, 2, False),
+]
+
+
+@pytest.mark.parametrize("Tq,Tk,H,Hkv,causal", ATTN_CASES)
+def test_attention_fwd(lib, Tq, Tk, H, Hkv, causal):
+    from odysseus_transformer_b200.ops import torch_ref as R
+    torch.manual_seed(Tq + Tk + H)
+    q, k, v = _rand(Tq, H, 128), _rand(Tk, Hkv, 128), _rand(Tk, Hkv, 128)
+    scale = 1.0 / math.sqrt(128)
+    o, lse = lib.attn_fwd(q, k, v, causal, scale)
+    _check_status(lib)
+    orf, lser = R.attn_fwd(q, k, v, causal, scale)
+    torch.testing.assert_close(lse, lser, rtol=1e-3, atol=2e-3)
+    torch.testing.assert_close(o.float(), orf.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_attention_fwd_packed_views(lib):
+    """q/k/v as strided views of one packed [T, hq+2hkv, 128] tensor, peaked logits (rescale path)."""
+    from odysseus_transformer_b200.ops import torch_ref as R
+    T, hq, hkv = 640, 4, 2
+    qkv = _rand(T, hq + 2 * hkv, 128, scale=3.0)
+    q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
+    scale = 1.0 / math.sqrt(128)
+    o, lse = lib.attn_fwd(q, k, v, True, scale)
+    _check_status(lib)
+    orf, lser = R.attn_fwd(q, k, v, True, scale)
+    torch.testing.assert_close(lse, lser, rtol=1e-3, atol=5e-3)
+    torch.testing.assert_close(o.float(), orf.float(), rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("Tq,Tk,H,Hkv,causal", ATTN_CASES)
+def test_attention_bwd(lib, Tq, Tk, H, Hkv, causal):
+    from odysseus_transformer_b200.ops import torch_ref as R
+    torch.manual_seed(Tq * 3 + Tk + H)
+    q, k, v = _rand(Tq, H, 128), _rand(Tk, Hkv, 128), _rand(Tk, Hkv, 128)
+    do = _rand(Tq, H, 128)
+    scale = 1.0 / math.sqrt(128)
+    o, lse = R.attn_fwd(q, k, v, causal, scale)
+    dq, dk, dv = lib.attn_bwd(do, q, k, v, o, lse, causal, scale)
+    _check_status(lib)
+    dqr, dkr, dvr = R.attn_bwd(do, q, k, v, o, lse, causal, scale)
+    for name, a, b in (("dq", dq, dqr), ("dk", dk, dkr), ("dv", dv, dvr)):
+        rel = ((a.float() - b).norm() / b.norm()).item()
+        assert rel < 2e-2, f"{name}: rel err {rel}"
+        torch.testing.assert_close(a.float(), b, rtol=5e-2, atol=5e-2 * b.abs().max().item(), msg=lambda m: f"{name}: {m}")
+
+
+def test_attention_bwd_packed_outputs(lib):
+    """Gradients written straight into slices of one packed [T, hq+2hkv, 128] tensor."""
+    from odysseus_transformer_b200.ops import torch_ref as R
+    T, hq, hkv = 512, 4, 2
+    qkv = _rand(T, hq + 2 * hkv, 128)
+    q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
+    do = _rand(T, hq, 128)
+    scale = 1.0 / math.sqrt(128)
+    o, lse = lib.attn_fwd(q, k, v, True, scale)
+    dqkv = torch.full_like(qkv, float("nan"))
+    lib.attn_bwd(do, q, k, v, o, lse, True, scale, dqkv[:, :hq], dqkv[:, hq:hq + hkv], dqkv[:, hq + hkv:])
+    _check_status(lib)
+    dqr, dkr, dvr = R.attn_bwd(do, q, k, v, o, lse, True, scale)
+    ref = torch.cat([dqr, dkr, dvr], dim=1)
+    assert torch.isfinite(dqkv.float()).all()
+    assert ((dqkv.float() - ref).norm() / ref.norm()).item() < 2e-2

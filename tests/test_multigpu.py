@@ -1,0 +1,41 @@
+"""Multi-GPU parity: every mode on 2 (or 4) B200s against a single-GPU run of the same weights."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(n, *args, timeout=600):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", str(_port()), os.path.join(HERE, "mgpu_worker.py"), *map(str, args)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    tail = (r.stdout + r.stderr)[-3000:]
+    assert r.returncode == 0, tail
+    assert "RESULT" in r.stdout, tail
+    return r.stdout
+
+
+@pytest.mark.parametrize("backend", ["library", "fused"])
+@pytest.mark.parametrize("mode", ["odysseus", "tpsp", "ulysses", "ring"])
+def test_modes_2gpu(mode, backend):
+    _launch(2, mode, "small", 1024, 0, 1, backend)
+
+
+@pytest.mark.parametrize("mode", ["odysseus", "ulysses"])
+def test_hybrid_4gpu(mode):
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    _launch(4, mode, "small-gqa", 1024, 2, 2, "fused")
