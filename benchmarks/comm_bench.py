@@ -1,0 +1,150 @@
+#!/usr/bin/env python
+"""Fused compute+collective paths vs the NCCL + GEMM composition, on N GPUs of one node.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29520 benchmarks/comm_bench.py --tokens 16384
+
+Cases (Llama-2-7B shapes, bf16; ``tokens`` = global sequence length, sharded on sequence):
+  ag_qkv     all-gather(x [L/N,4096]) -> GEMM with W [3*4096/N, 4096]
+  oproj_rs   GEMM x [L,4096/N] W [4096,4096/N] -> reduce-scatter rows
+  wag_gateup all-gather(W [2*11008/N,4096]) -> GEMM with x [L/N,4096]
+  wag_dgrad  all-gather(W) along K -> dgrad GEMM
+  wgrad_rs   wgrad GEMM dy^T x -> reduce-scatter of [2*11008, 4096]
+
+Each case is timed with CUDA events on the launching stream after warm-up, a 256 MB write between
+iterations, and reduced as the max over ranks.  The roofline is the slower of FLOPs / measured bf16 peak
+and bytes that must cross NVLink per GPU / 770 GB/s (the measured one-direction peer-copy rate).
+Rank 0 prints one JSON line per case."""
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+NVLINK_GBS = 770.0
+
+
+def peak_tflops():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p))["bf16_tflops"], "measured"
+    return 1590.0, "fallback"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--iters", type=int, default=8)
+    ap.add_argument("--cases", type=str, default="ag_qkv,oproj_rs,wag_gateup,wag_dgrad,wgrad_rs")
+    a = ap.parse_args()
+    from odysseus_transformer_b200.comm import symm, torch_backend as C
+    from odysseus_transformer_b200.config import get_model_config
+    from odysseus_transformer_b200.mesh import init_parallel_context
+    from odysseus_transformer_b200.ops import functional as F, fused_comm, native
+    native.set_backend("fused")
+    ctx = init_parallel_context("odysseus", backend="fused")
+    n, rank, dev, g = ctx.world_size, ctx.rank, ctx.device, ctx.world_group
+    cfg = get_model_config("llama2-7b")
+    assert symm.setup_fused_comm(ctx, cfg, a.tokens // n), "peer memory unavailable"
+    heap = fused_comm.heap_for(g)
+    d, i, L, t = 4096, 11008, a.tokens, a.tokens // n
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    tf, kind = peak_tflops()
+
+    def rnd(*s):
+        return torch.randn(*s, device=dev).mul_(0.1).to(torch.bfloat16)
+
+    def timeit(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(a.iters):
+            flush.zero_()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        v = torch.tensor([ts[len(ts) // 2]], device=dev)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v.item())
+
+    def report(name, fused_ms, nccl_ms, gemm_ms, flops, link_bytes, shape):
+        if rank != 0:
+            return
+        t_comp, t_link = flops / (tf * 1e9), link_bytes / (NVLINK_GBS * 1e6)
+        roof = max(t_comp, t_link)
+        print(json.dumps({"case": name, "n_gpus": n, "tokens": L, "shape": shape, "fused_ms": round(fused_ms, 4),
+                          "nccl_plus_gemm_ms": round(nccl_ms, 4), "gemm_only_ms": round(gemm_ms, 4),
+                          "speedup_vs_nccl": round(nccl_ms / fused_ms, 3), "roofline_ms": round(roof, 4),
+                          "bound": "compute" if t_comp >= t_link else "link",
+                          f"frac_of_roofline({kind} peak, 770 GB/s)": round(roof / fused_ms, 3)}), flush=True)
+
+    def timeline(name, fn):
+        """Exposed communication of one gather launch: how long producers waited for rows, and the push span."""
+        st = heap.enable_stats()
+        fn()
+        torch.cuda.synchronize()
+        v = st.view(-1, 4).cpu()
+        v = v[v[:, 3] > 0]
+        t0 = int(v[:, 0][v[:, 0] > 0].min())
+        if rank == 0:
+            print(json.dumps({"case": name + "_timeline", "ctas": int(v.shape[0]),
+                              "push_span_us": round((int(v[:, 1].max()) - t0) / 1e3, 1),
+                              "kernel_span_us": round((int(v[:, 3].max()) - t0) / 1e3, 1),
+                              "producer_row_wait_us_mean": round(float(v[:, 2].float().mean()) / 1e3, 1),
+                              "producer_row_wait_us_max": round(int(v[:, 2].max()) / 1e3, 1)}), flush=True)
+        heap.stats = None
+
+    cases = a.cases.split(",")
+    if "ag_qkv" in cases:
+        x, w = rnd(t, d), rnd(3 * d // n, d)
+        fused = timeit(lambda: fused_comm._gather_gemm(heap, x, 1, w, 0))
+        nccl = timeit(lambda: F.gemm_nt(C.all_gather_rows(x, g), w))
+        xf = rnd(L, d)
+        gemm = timeit(lambda: F.gemm_nt(xf, w))
+        timeline("ag_qkv", lambda: fused_comm._gather_gemm(heap, x, 1, w, 0))
+        report("ag_qkv", fused, nccl, gemm, 2.0 * L * d * (3 * d // n), (n - 1) * t * d * 2, [L, 3 * d // n, d])
+    if "oproj_rs" in cases:
+        x, w = rnd(L, d // n), rnd(d, d // n)
+        fused = timeit(lambda: fused_comm._scatter_gemm(heap, x, w, 0, L, d))
+        nccl = timeit(lambda: C.reduce_scatter_rows(F.gemm_nt(x, w), g))
+        gemm = timeit(lambda: F.gemm_nt(x, w))
+        report("oproj_rs", fused, nccl, gemm, 2.0 * L * d * (d // n), (n - 1) * t * d * 2, [L, d, d // n])
+    if "wag_gateup" in cases:
+        x, w = rnd(t, d), rnd(2 * i // n, d)
+        fused = timeit(lambda: fused_comm._gather_gemm(heap, w, 2, x, 0))
+        nccl = timeit(lambda: F.gemm_nt(x, C.all_gather_rows(w, g)))
+        wf = rnd(2 * i, d)
+        gemm = timeit(lambda: F.gemm_nt(x, wf))
+        timeline("wag_gateup", lambda: fused_comm._gather_gemm(heap, w, 2, x, 0))
+        report("wag_gateup", fused, nccl, gemm, 2.0 * t * d * 2 * i, (n - 1) * (2 * i // n) * d * 2, [t, 2 * i, d])
+    if "wag_dgrad" in cases:
+        dy, w = rnd(t, 2 * i), rnd(2 * i // n, d)
+        fused = timeit(lambda: fused_comm._gather_gemm(heap, w, 2, dy, 1))
+        nccl = timeit(lambda: F.gemm_nn(dy, C.all_gather_rows(w, g)))
+        wf = rnd(2 * i, d)
+        gemm = timeit(lambda: F.gemm_nn(dy, wf))
+        timeline("wag_dgrad", lambda: fused_comm._gather_gemm(heap, w, 2, dy, 1))
+        report("wag_dgrad", fused, nccl, gemm, 2.0 * t * d * 2 * i, (n - 1) * (2 * i // n) * d * 2, [t, d, 2 * i])
+    if "wgrad_rs" in cases:
+        dy, x = rnd(t, 2 * i), rnd(t, d)
+        fused = timeit(lambda: fused_comm._scatter_gemm(heap, dy, x, 2, 2 * i, d))
+        nccl = timeit(lambda: C.reduce_scatter_rows(F.gemm_tn(dy, x), g))
+        gemm = timeit(lambda: F.gemm_tn(dy, x))
+        report("wgrad_rs", fused, nccl, gemm, 2.0 * t * d * 2 * i, (n - 1) * (2 * i // n) * d * 2, [2 * i, d, t])
+    native.check_status(dev.index)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -267,6 +267,7 @@ void ody_count_launches(int64_t n) { g_launches += n; }
 
 // attention (defined in attn_bindings.cpp)
 void ody_register_attention(pybind11::module& m);
+void ody_register_comm(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out") = py::none(), py::arg("layout") = 0,
@@ -289,4 +290,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reset_launch_count", &reset_launch_count);
   m.def("add_launches", &add_launches);
   ody_register_attention(m);
+  ody_register_comm(m);
 }

@@ -63,7 +63,7 @@ template <int LAYOUT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __nv_bfloat16* __restrict__ c_in, int M, int N, int K,
-                 int64_t ldc, int accumulate, int* __restrict__ err) {
+                 int64_t ldc, int accumulate, int mn3d, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   GemmBars* bars = (GemmBars*)(smem + SMEM_TILES);
@@ -121,12 +121,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int k0 = kb * BK;
           if (!A_MN) {
             tma_load_2d(sA, &tmA, k0, m0, &bars->full[stage]);
+          } else if (mn3d & 1) {
+            tma_load_3d(sA, &tmA, 0, k0, m0 / 64, &bars->full[stage]);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d(sA + j * 8192, &tmA, m0 + 64 * j, k0, &bars->full[stage]);
           }
           if (!B_MN) {
             tma_load_2d(sB, &tmB, k0, n0, &bars->full[stage]);
+          } else if (mn3d & 2) {
+            tma_load_3d(sB, &tmB, 0, k0, n0 / 64, &bars->full[stage]);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &tmB, n0 + 64 * j, k0, &bars->full[stage]);
@@ -272,10 +276,13 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   }
   CUtensorMap tA, tB, tC;
   int r;
-  if (LAYOUT == 2) r = make_tmap_2d_bf16(&tA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
+  int mn3d = 0;   // bit 0: A tile is one blocked 3-D TMA load, bit 1: B tile is
+  if (LAYOUT == 2 && (M % 64) == 0) { r = make_tmap_mn_blocked_bf16(&tA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BK, BM / 64); mn3d |= 1; }
+  else if (LAYOUT == 2) r = make_tmap_2d_bf16(&tA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, 64);
   else r = make_tmap_2d_bf16(&tA, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64, BM);
   if (r) return 700000 + r;
   if (LAYOUT == 0) r = make_tmap_2d_bf16(&tB, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64, BN);
+  else if ((N % 64) == 0) { r = make_tmap_mn_blocked_bf16(&tB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, BK, BN / 64); mn3d |= 2; }
   else r = make_tmap_2d_bf16(&tB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, 64);
   if (r) return 710000 + r;
   r = make_tmap_2d_bf16(&tC, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, EPI_COLS, BM);
@@ -283,7 +290,7 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < g_num_sms ? tiles : g_num_sms;
   gemm_bf16_kernel<LAYOUT><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tA, tB, tC, (const __nv_bfloat16*)C, M, N, K, ldc,
-                                                                  accumulate, err);
+                                                                  accumulate, mn3d, err);
   return (int)cudaGetLastError();
 }
 

@@ -64,6 +64,34 @@ int ody_flash_bwd(const void* dO, const void* q, const void* k, const void* v, c
                   int64_t k_row, int64_t v_row, int64_t o_row, int64_t dq_row, int64_t dk_row, int64_t dv_row, int causal,
                   float scale, int* err, cudaStream_t stream);
 
+// ---- GEMM fused with an all-gather of one operand and/or a reduce-scatter of the result over peer memory
+// (gemm_comm.cu).  Descriptions are plain data; pointers in *_peer[p] address rank p's symmetric memory.
+typedef struct OdyGatherDesc {
+  const void* shard; int64_t shard_ld;
+  void* gathered_peer[8]; uint32_t* flags_peer[8]; uint32_t* counters_peer[8]; uint32_t* free_peer[8];
+  uint32_t* gemm_done;
+  void* stats;           /* optional [n_cta][4] uint64 ns: comm begin, comm end, producer row-wait time, CTA end */
+  int n_ranks, rank, chunk_rows, cols;
+  int n_cta;             /* CTAs of this launch = min(tiles, SMs); checked against the launcher's grid */
+  uint32_t push_total;   /* running total of CTAs that pushed into this slot (all uses, the current one included) */
+  uint32_t consume_total;/* running total of CTAs that consumed this slot (all uses, the current one included) */
+  uint32_t epoch, prev_epoch, uses;
+  int which;
+} OdyGatherDesc;
+typedef struct OdyScatterDesc {
+  void* stage_peer[8]; uint32_t* arrived_peer[8]; uint32_t* consumed_peer[8];
+  uint32_t* reduce_counter; void* out; int64_t out_ld;
+  int n_ranks, rank, chunk_rows;
+  uint32_t epoch, prev_epoch, arrived_target, uses;
+} OdyScatterDesc;
+int ody_gemm_comm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                  int layout, const OdyGatherDesc* gather, const OdyGatherDesc* push, const OdyScatterDesc* scatter, int* err,
+                  cudaStream_t stream);
+int ody_push_shard(const OdyGatherDesc* push, int* err, cudaStream_t stream);
+
+// ---- copy between (peer-mapped) device buffers with plain 16-byte loads/stores on n_ctas x threads threads
+int ody_peer_copy(void* dst, const void* src, int64_t bytes, int n_ctas, int threads, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -244,6 +244,38 @@ inline int make_tmap_2d_bf16(CUtensorMap* m, const void* base, uint64_t inner, u
   return (int)r;
 }
 
+// MN-major operand [K rows][MN elements] viewed as {64 (mn), K, MN/64}: one box {64, box_k, nblk} lands in shared
+// memory as nblk consecutive [box_k x 128 B] swizzled blocks - the layout tcgen05 wants for an MN-major tile -
+// so a whole operand tile is ONE TMA instruction.  Needs MN % 64 == 0.
+inline int make_tmap_mn_blocked_bf16(CUtensorMap* m, const void* base, uint64_t mn, uint64_t k, uint64_t pitch_bytes,
+                                     uint32_t box_k, uint32_t nblk) {
+  PFN_encodeTiled enc = get_encode_fn();
+  if (enc == nullptr) return -1;
+  cuuint64_t dims[3] = {64, k, mn / 64};
+  cuuint64_t strides[2] = {pitch_bytes, 128};
+  cuuint32_t box[3] = {64, box_k, nblk};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (int)r;
+}
+
+// Same, without swizzle: for plain copies, where the inner box may be up to 256 elements wide.
+inline int make_tmap_2d_bf16_linear(CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint64_t pitch_bytes,
+                                    uint32_t box_inner, uint32_t box_outer) {
+  PFN_encodeTiled enc = get_encode_fn();
+  if (enc == nullptr) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (int)r;
+}
+
 // 3-D bf16 tensor {inner, mid, outer} with byte pitches for mid and outer.
 inline int make_tmap_3d_bf16(CUtensorMap* m, const void* base, uint64_t inner, uint64_t mid, uint64_t outer,
                              uint64_t pitch_mid_bytes, uint64_t pitch_outer_bytes, uint32_t box_inner,

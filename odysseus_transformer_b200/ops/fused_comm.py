@@ -1,14 +1,36 @@
 """Single-kernel compute+collective paths over NVLink peer memory (sm_100a only).
 
-``enabled(x, group)`` says whether the fused kernels serve this call: CUDA tensors, the ``fused``
-backend, a multi-rank group and a symmetric heap registered for that group.  Otherwise callers run
-the torch.distributed + GEMM composition in ``parallel.linear`` / ``parallel.attention``.
+``enabled(x, group)`` says whether the fused kernels serve this call: CUDA bf16 tensors, a backend other
+than ``library``, a multi-rank group and a symmetric heap registered for that group
+(``comm.symm.setup_fused_comm``).  Otherwise callers run the torch.distributed + GEMM composition in
+``parallel.linear``.  Each autograd function below replaces a collective + GEMM pair of the reference by
+ONE launch of ``csrc/gemm_comm.cu``:
+
+=====================  ===============================  =========================================
+op                     forward                          backward
+=====================  ===============================  =========================================
+``ag_linear``          all-gather(x) -> GEMM            dgrad GEMM -> reduce-scatter ;
+(column parallel)      (reference linear_tpsp.py:159-173)  all-gather(x) -> wgrad GEMM (:205-298)
+``linear_rs``          GEMM -> reduce-scatter           all-gather(dy) -> dgrad GEMM ; wgrad GEMM on
+(row parallel)         (reference linear_tpsp.py:588-591)  the gathered dy (:97, autograd of F.linear)
+``zero3_linear``       all-gather(W) -> GEMM            all-gather(W) -> dgrad GEMM ;
+                       (reference linear_zero3.py:35-44)   wgrad GEMM -> reduce-scatter (:62-84)
+=====================  ===============================  =========================================
+
+A shape the kernels do not take (shard rows not a multiple of 64, heap exhausted) falls back, op by op,
+to the unfused function.
 """
 from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch.autograd import Function
 
 from . import native
 
 _heaps = {}   # id(group) -> comm.symm.SymmetricHeap
+stats = {"gather": 0, "scatter": 0, "fallback": 0}   # fused launches / per-op fallbacks since import
 
 
 def register_heap(group, heap) -> None:
@@ -19,7 +41,239 @@ def heap_for(group):
     return _heaps.get(id(group))
 
 
+def clear_heaps() -> None:
+    _heaps.clear()
+
+
 def enabled(x, group) -> bool:
-    if group is None or not x.is_cuda or native.get_backend() == "library":
+    if group is None or not x.is_cuda or x.dtype != torch.bfloat16 or native.get_backend() == "library":
         return False
     return id(group) in _heaps and native.available()
+
+
+def ring_enabled(x, group) -> bool:
+    """Ring attention with in-kernel peer K/V pulls; not provided yet, the all-gather composition runs."""
+    return False
+
+
+def _lib():
+    return native.lib()
+
+
+def _n_cta(heap, M: int, N: int) -> int:
+    return min(((M + 127) // 128) * ((N + 255) // 256), heap.sm_count)
+
+
+def _push_only(heap, shard: torch.Tensor):
+    """Deliver ``shard`` into every rank's gathered buffer with a push-only launch; returns the slot."""
+    shard = shard if shard.stride(-1) == 1 else shard.contiguous()
+    slot = heap.gather_slot(shard.shape[0], shard.shape[1])
+    if slot is None:
+        return None
+    _lib().push_shard(slot.push_desc(shard, heap.sm_count))
+    stats["push_only"] = stats.get("push_only", 0) + 1
+    return slot
+
+
+def _gather_gemm(heap, shard: torch.Tensor, which: int, other: torch.Tensor, layout: int,
+                 out: Optional[torch.Tensor] = None, slot=None, prefetch: Optional[torch.Tensor] = None):
+    """GEMM whose operand ``which`` (1 = A, 2 = B) is the all-gather of ``shard``.
+
+    ``slot``: the gathered buffer when an earlier launch already delivered ``shard`` (prefetch), else the
+    comm warps of THIS launch deliver it.  ``prefetch``: another shard for this launch's comm warps to
+    deliver when they have nothing else to do (only possible when ``slot`` was given).
+    Returns (result, gathered view, slot holding the prefetched shard or None); result None = unsupported."""
+    shard = shard if shard.stride(-1) == 1 else shard.contiguous()
+    pushed = slot is not None
+    if slot is None:
+        slot = heap.gather_slot(shard.shape[0], shard.shape[1])
+        if slot is None:
+            stats["fallback"] += 1
+            return None, None, None
+    stats["gather"] += 1
+    g = slot.view()
+    a, b = (g, other) if which == 1 else (other, g)
+    M = a.shape[1] if layout == 2 else a.shape[0]
+    N = b.shape[0] if layout == 0 else b.shape[1]
+    n_cta = _n_cta(heap, M, N)
+    push, next_slot = None, None
+    if not pushed:
+        push = slot.push_desc(shard, n_cta)
+    elif prefetch is not None:
+        prefetch = prefetch if prefetch.stride(-1) == 1 else prefetch.contiguous()
+        next_slot = heap.gather_slot(prefetch.shape[0], prefetch.shape[1])
+        if next_slot is not None:
+            push = next_slot.push_desc(prefetch, n_cta)
+            stats["prefetch"] = stats.get("prefetch", 0) + 1
+    y = _lib().gemm_comm(a, b, out, layout, slot.consume_desc(which, n_cta), push, None)
+    return y, g, next_slot
+
+
+def _scatter_gemm(heap, a: torch.Tensor, b: torch.Tensor, layout: int, M: int, N: int,
+                  out: Optional[torch.Tensor] = None):
+    """GEMM whose [M, N] result is reduce-scattered on rows; returns this rank's [M/n, N] or None."""
+    if M % heap.n:
+        stats["fallback"] += 1
+        return None
+    chunk = M // heap.n
+    slot = heap.scatter_slot(chunk, N)
+    if slot is None:
+        stats["fallback"] += 1
+        return None
+    stats["scatter"] += 1
+    if out is None:
+        out = torch.empty(chunk, N, dtype=a.dtype, device=a.device)
+    _lib().gemm_comm(a, b, None, layout, None, None, slot.describe(out))
+    return out
+
+
+# ----------------------------------------------------------------------------- column parallel
+
+
+class _FusedAGLinear(Function):
+    @staticmethod
+    def forward(ctx, x, w, group):
+        from ..ops import functional as F
+        heap = heap_for(group)
+        ctx.group = group
+        ctx.save_for_backward(x, w)
+        y, _, _ = _gather_gemm(heap, x, 1, w, 0)
+        if y is None:
+            from ..comm import torch_backend as C
+            y = F.gemm_nt(C.all_gather_rows(x, group), w)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..comm import torch_backend as C
+        from ..ops import functional as F
+        x, w = ctx.saved_tensors
+        heap = heap_for(ctx.group)
+        dy = dy.contiguous()
+        # dX = reduce-scatter(dY @ W)
+        dx = _scatter_gemm(heap, dy, w, 1, dy.shape[0], w.shape[1])
+        if dx is None:
+            dx = C.reduce_scatter_rows(F.gemm_nn(dy, w), ctx.group)
+        # dW = dY^T @ all-gather(x): the gathered x streams in along K
+        mg = getattr(w, "main_grad", None)
+        fresh = mg is not None and not getattr(w, "_grad_written", False)
+        dw, _, _ = _gather_gemm(heap, x, 2, dy, 2, out=mg if fresh else None)
+        if dw is None:
+            return dx, F.store_weight_grad(w, dy, C.all_gather_rows(x, ctx.group)), None
+        if fresh:
+            w._grad_written = True
+            return dx, None, None
+        return dx, F.deliver_grad(w, dw), None
+
+
+def ag_linear(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
+    return _FusedAGLinear.apply(x, w, group)
+
+
+# ----------------------------------------------------------------------------- row parallel
+
+
+class _FusedLinearRS(Function):
+    @staticmethod
+    def forward(ctx, x, w, group):
+        from ..comm import torch_backend as C
+        from ..ops import functional as F
+        heap = heap_for(group)
+        ctx.group = group
+        ctx.save_for_backward(x, w)
+        x = x if x.stride(-1) == 1 else x.contiguous()
+        y = _scatter_gemm(heap, x, w, 0, x.shape[0], w.shape[0])
+        if y is None:
+            y = C.reduce_scatter_rows(F.gemm_nt(x, w), group)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..comm import torch_backend as C
+        from ..ops import functional as F
+        x, w = ctx.saved_tensors
+        heap = heap_for(ctx.group)
+        dy = dy.contiguous()
+        # dX = all-gather(dY) @ W ; the gathered dY stays in the slot for the wgrad GEMM that follows
+        dx, dy_full, _ = _gather_gemm(heap, dy, 1, w, 1)
+        if dx is None:
+            dy_full = C.all_gather_rows(dy, ctx.group)
+            dx = F.gemm_nn(dy_full, w)
+        dw = F.store_weight_grad(w, dy_full, x)
+        return dx, dw, None
+
+
+def linear_rs(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
+    return _FusedLinearRS.apply(x, w, group)
+
+
+# ----------------------------------------------------------------------------- ZeRO-3
+
+
+def _chain(sched, heap, idx: int, step: int, w: torch.Tensor):
+    """Prefetch bookkeeping of a ZeRO-3 linear: (slot already holding all-gather(w) or None, next weight to
+    prefetch or None, its index).  Weights register in forward order in ``sched``; forward walks +1, backward
+    -1.  The first linear of a pass has no earlier GEMM to ride on and starts the chain with a push-only launch."""
+    if sched is None or not getattr(sched, "enabled", True):
+        return None, None, None
+    pre = sched.__dict__.setdefault("_fused_prefetched", {})
+    slot = pre.pop(idx, None)
+    nxt = idx + step
+    nxt_w = None
+    if 0 <= nxt < len(sched.weights) and sched.groups[nxt] is sched.groups[idx] and nxt not in pre:
+        cand = sched.weights[nxt].detach()
+        if cand.is_cuda and cand.dtype == torch.bfloat16 and cand.shape[0] % 64 == 0 and cand.shape[1] % 64 == 0:
+            nxt_w = cand
+    if slot is None and nxt_w is not None:
+        slot = _push_only(heap, w)          # may be None (unsupported shape): then this op pushes in-kernel
+    return slot, nxt_w, nxt
+
+
+class _FusedZero3Linear(Function):
+    @staticmethod
+    def forward(ctx, x, w, group, sched, idx):
+        from ..comm import torch_backend as C
+        from ..ops import functional as F
+        heap = heap_for(group)
+        ctx.group, ctx.sched, ctx.idx = group, sched, idx
+        ctx.save_for_backward(x, w)
+        x = x if x.stride(-1) == 1 else x.contiguous()
+        slot, nxt_w, nxt = _chain(sched, heap, idx, +1, w.detach())
+        y, _, nslot = _gather_gemm(heap, w.detach(), 2, x, 0, slot=slot, prefetch=nxt_w)
+        if nslot is not None:
+            sched._fused_prefetched[nxt] = nslot
+        if y is None:
+            y = F.gemm_nt(x, C.all_gather_rows(w.detach(), group))
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..comm import torch_backend as C
+        from ..ops import functional as F
+        x, w = ctx.saved_tensors
+        group, sched, idx = ctx.group, ctx.sched, ctx.idx
+        heap = heap_for(group)
+        dy = dy.contiguous()
+        slot, nxt_w, nxt = _chain(sched, heap, idx, -1, w.detach())
+        dx = None
+        if ctx.needs_input_grad[0] or slot is not None:
+            dx, _, nslot = _gather_gemm(heap, w.detach(), 2, dy, 1, slot=slot, prefetch=nxt_w)   # W streams in along K
+            if nslot is not None:
+                sched._fused_prefetched[nxt] = nslot
+            if dx is None:
+                dx = F.gemm_nn(dy, C.all_gather_rows(w.detach(), group))
+        mg = getattr(w, "main_grad", None)
+        fresh = mg is not None and not getattr(w, "_grad_written", False)
+        n = heap.n
+        dw = _scatter_gemm(heap, dy, x, 2, n * w.shape[0], w.shape[1], out=mg if fresh else None)
+        if dw is None:
+            dw = C.reduce_scatter_rows(F.gemm_tn(dy, x), group)
+            return dx, F.deliver_grad(w, dw), None, None, None
+        if fresh:
+            w._grad_written = True
+            return dx, None, None, None, None
+        return dx, F.deliver_grad(w, dw), None, None, None
+
+
+def zero3_linear(x: torch.Tensor, w_shard: torch.Tensor, group, sched=None, idx: int = 0) -> torch.Tensor:
+    return _FusedZero3Linear.apply(x, w_shard, group, sched, idx)

@@ -215,7 +215,7 @@ class _PackedRopeAttention(Function):
         q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
         if C.group_size(ring_group) > 1:
             from ..ops import fused_comm
-            if fused_comm.enabled(qkv, ring_group):
+            if fused_comm.ring_enabled(qkv, ring_group):
                 o, lse = fused_comm.ring_attn_fwd(q, k, v, ring_group, scale)
             else:
                 o, lse = ring_attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), ring_group, scale)
@@ -235,7 +235,7 @@ class _PackedRopeAttention(Function):
         dqkv = torch.empty_like(qkv)
         if C.group_size(ring_group) > 1:
             from ..ops import fused_comm
-            if fused_comm.enabled(qkv, ring_group):
+            if fused_comm.ring_enabled(qkv, ring_group):
                 dq, dk, dv = fused_comm.ring_attn_bwd(do, q, k, v, o, lse, ring_group, scale)
             else:
                 dq, dk, dv = ring_attn_bwd(do, q.contiguous(), k.contiguous(), v.contiguous(), o, lse,

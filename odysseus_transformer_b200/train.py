@@ -63,6 +63,9 @@ class Trainer:
         self.cfg, self.mode, self.ctx, self.seq_length = cfg, mode, ctx, seq_length
         self.ulysses_degree, self.ring_degree = ulysses_degree, ring_degree
         set_global_memory_buffer(ctx.device)
+        if ctx.world_size > 1 and ctx.device.type == "cuda" and native.get_backend() != "library" and dtype == torch.bfloat16:
+            from .comm import symm
+            symm.setup_fused_comm(ctx, cfg, max(1, seq_length // ctx.world_size))
         self.model = build_model(cfg, mode, ctx, dtype=dtype, device=ctx.device, seed=seed, state_dict=state_dict)
         if grad_checkpoint:
             self.model.gradient_checkpointing_enable()

@@ -55,9 +55,14 @@ def main():
             rel = ((grads[k].float() - v.float()).norm() / (v.float().norm() + 1e-6)).item()
             if rel > worst:
                 worst, worst_k = rel, k
+        from odysseus_transformer_b200.ops import fused_comm
+        print(f"FUSED {fused_comm.stats}", flush=True)
         print(f"RESULT mode={mode} backend={backend} loss={total.item():.5f} ref={rl.item():.5f} dloss={dl:.2e} "
               f"worst_rel_grad={worst:.3e} ({worst_k})", flush=True)
         ok = dl < 3e-2 and worst < 0.1
+        if backend == "fused" and fused_comm.stats["gather"] + fused_comm.stats["scatter"] == 0:
+            print("fused backend requested but no fused collective kernel ran", flush=True)
+            ok = False
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.broadcast(flag, 0)
     dist.barrier()

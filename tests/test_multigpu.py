@@ -25,6 +25,7 @@ def _launch(n, *args, timeout=600):
     tail = (r.stdout + r.stderr)[-3000:]
     assert r.returncode == 0, tail
     assert "RESULT" in r.stdout, tail
+    print(r.stdout[-600:])
     return r.stdout
 
 
