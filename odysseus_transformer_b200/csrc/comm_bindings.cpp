@@ -140,6 +140,7 @@ void peer_copy(int64_t dst, int64_t src, int64_t bytes, int64_t n_ctas, int64_t 
 void ody_register_comm(pybind11::module& m) {
   m.def("peer_copy", &peer_copy);
   m.def("push_shard", &push_shard);
+  m.def("set_peer_wait_limit", [](int64_t cycles) { req(ody_set_peer_wait_limit(cycles) == 0, "set_peer_wait_limit failed"); });
   m.def("gemm_comm", &gemm_comm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("layout"), py::arg("gather"),
         py::arg("push"), py::arg("scatter"));
 }

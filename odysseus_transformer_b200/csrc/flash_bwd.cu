@@ -7,7 +7,8 @@
 //   prep   : delta[h,t] = sum_d dO*O, and LSE converted to the exp2 domain, both padded to 64 rows.
 //   dkdv   : one CTA per (128-row KV tile, kv head).  K and V stay in shared memory; 64-row blocks of Q
 //            and dO stream through a TMA ring.  S^T = K Q^T and dP^T = V dO^T land in TMEM (double
-//            buffered, kv rows on lanes), four warps turn them into P^T and dS^T (bf16, written back over
+//            buffered, kv rows on lanes), eight warps (two per lane quarter, 32 columns each) turn them into
+//            P^T and dS^T (bf16, written back over
 //            the same TMEM columns) and the tensor core accumulates dV += P^T dO, dK += dS^T Q in TMEM
 //            (2*64 + 2*64 + 128 + 128 = 512 columns).  Query heads sharing the kv head are looped inside.
 //   dq     : one CTA per (128-row query tile, head).  Q and dO stay in shared memory; 64-row blocks of K
@@ -31,7 +32,7 @@ constexpr int BLK_BYTES = BLK * HD * 2;          // 16 KB (two halves of [64 x 1
 constexpr int BLK_HALF = BLK_BYTES / 2;
 constexpr int STAGES = 3;
 constexpr int STAT_BYTES = 2 * BLK * 4;          // lse2 + delta of one 64-row block
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;             // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quarter)
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -119,7 +120,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   if (threadIdx.x == 0) {
     mbar_init(&bars->kv_full, 1);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->qd_full[s], 1); mbar_init(&bars->qd_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&bars->s_full[b], 1); mbar_init(&bars->p_full[b], 128); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&bars->s_full[b], 1); mbar_init(&bars->p_full[b], 256); }
     mbar_init(&bars->acc_done, 1);
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
@@ -161,23 +162,25 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       constexpr uint32_t IDESC_S = make_idesc_bf16(BIG, BLK, 0, 0);
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BIG, HD, 0, 1);
       bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
+      const uint64_t kdesc0 = make_smem_desc(smem_u32(sK), 16, 1024), vdesc0 = make_smem_desc(smem_u32(sV), 16, 1024);
+      const uint64_t stage_k0 = make_smem_desc(smem_u32(sStage), 16, 1024);            // K-major view of a streamed block
+      const uint64_t stage_mn0 = make_smem_desc(smem_u32(sStage), BLK_HALF, 1024);     // MN-major view (B of dV / dK)
       int stage = 0; uint32_t phase = 0;          // ring position of the next S/dP issue
       int stage2 = 0;                             // ring position of the next dV/dK issue
       auto issue_s = [&](int it) -> bool {
         if (!mbar_wait(&bars->qd_full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
         tc_fence_after();
         const int b = it & 1;
-        const uint32_t aQ = smem_u32(sStage + stage * 2 * BLK_BYTES), aD = aQ + BLK_BYTES;
+        const uint64_t q0d = desc_advance(stage_k0, stage * 2 * BLK_BYTES), d0d = desc_advance(q0d, BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
-          umma_ss(tmem + b * 64, make_smem_desc(aK + offA, 16, 1024), make_smem_desc(aQ + offB, 16, 1024), IDESC_S, kk > 0);
+          umma_ss(tmem + b * 64, desc_advance(kdesc0, offA), desc_advance(q0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
-          umma_ss(tmem + 128 + b * 64, make_smem_desc(aV + offA, 16, 1024), make_smem_desc(aD + offB, 16, 1024), IDESC_S, kk > 0);
+          umma_ss(tmem + 128 + b * 64, desc_advance(vdesc0, offA), desc_advance(d0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars->s_full[b]);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -189,15 +192,14 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         const int b = it & 1;
         if (!mbar_wait(&bars->p_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sStage + stage2 * 2 * BLK_BYTES), aD = aQ + BLK_BYTES;
+        const uint64_t qmn = desc_advance(stage_mn0, stage2 * 2 * BLK_BYTES), dmn = desc_advance(qmn, BLK_BYTES);
+        const uint32_t acc0 = it > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)   // dV += P^T dO
-          umma_ts(tmem + 256, tmem + b * 64 + kk * 8, make_smem_desc(aD + kk * 2048, BLK_HALF, 1024), IDESC_ACC,
-                  (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tmem + 256, tmem + b * 64 + kk * 8, desc_advance(dmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)   // dK += dS^T Q
-          umma_ts(tmem + 384, tmem + 128 + b * 64 + kk * 8, make_smem_desc(aQ + kk * 2048, BLK_HALF, 1024), IDESC_ACC,
-                  (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tmem + 384, tmem + 128 + b * 64 + kk * 8, desc_advance(qmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
         umma_commit(&bars->qd_empty[stage2]);
         if (++stage2 == STAGES) stage2 = 0;
       }
@@ -209,7 +211,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3;                               // TMEM lane quarter
+    const int hf = (warp - 2) >> 2;                       // which 32 of the block's 64 query columns this warp handles
     const int r = q * 32 + lane;                          // kv row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const float sl2 = scale * LOG2E;
@@ -217,22 +220,25 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     int stage = 0; uint32_t phase = 0;
     for (int it = 0; it < total; ++it) {
       const int b = it & 1;
-      const int qrow0 = (i0 + it % per_head) * BLK;
-      if (!mbar_wait(&bars->s_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+      const int qrow0 = (i0 + it % per_head) * BLK + hf * 32;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
       // s_full implies qd_full[stage] completed earlier (the MMAs consumed it); the stats are in smem
-      tc_fence_after();
-      const float* st = (const float*)(sStat + stage * STAT_BYTES);
-      uint32_t sv[64], dp[64];
-      tmem_ld_32x32(tmem + b * 64 + lane_off, sv);
-      tmem_ld_32x32(tmem + b * 64 + lane_off + 32, sv + 32);
-      tmem_ld_32x32(tmem + 128 + b * 64 + lane_off, dp);
-      tmem_ld_32x32(tmem + 128 + b * 64 + lane_off + 32, dp + 32);
-      tmem_ld_wait();
-      const bool diag = causal && (qrow0 < kv0 + BIG);     // some (q, kv) pairs of this block are masked
-      uint32_t pp[32], ds[32];
+      const float* st = (const float*)(sStat + stage * STAT_BYTES) + hf * 32;
+      uint32_t sv[32], dp[32];
+      if (ok) {
+        tc_fence_after();
+        tmem_ld_32x32(tmem + b * 64 + hf * 32 + lane_off, sv);
+        tmem_ld_32x32(tmem + 128 + b * 64 + hf * 32 + lane_off, dp);
+        tmem_ld_wait();
+      }
+      // P^T / dS^T are written over the first 32 columns of S^T / dP^T: the other warp of this lane quarter
+      // must have read its inputs before either of us stores; the two also agree here on leaving the loop
+      if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
+      const bool diag = causal && (qrow0 < kv0 + BIG);     // some (q, kv) pairs of this half block are masked
+      uint32_t pp[16], ds[16];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const float4 stl = *reinterpret_cast<const float4*>(st + (c >> 1) * 4);   // lse2 of columns 4*(c/2)..+3
+      for (int c = 0; c < 16; ++c) {
+        const float4 stl = *reinterpret_cast<const float4*>(st + (c >> 1) * 4);
         const float4 std_ = *reinterpret_cast<const float4*>(st + BLK + (c >> 1) * 4);
         const float l0 = (c & 1) ? stl.z : stl.x, l1 = (c & 1) ? stl.w : stl.y;
         const float d0 = (c & 1) ? std_.z : std_.x, d1 = (c & 1) ? std_.w : std_.y;
@@ -245,30 +251,28 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         pp[c] = pack_bf16(p0, p1);
         ds[c] = pack_bf16(p0 * (__uint_as_float(dp[2 * c]) - d0) * scale, p1 * (__uint_as_float(dp[2 * c + 1]) - d1) * scale);
       }
-      tmem_st_32x16(tmem + b * 64 + lane_off, pp);
-      tmem_st_32x16(tmem + b * 64 + lane_off + 16, pp + 16);
-      tmem_st_32x16(tmem + 128 + b * 64 + lane_off, ds);
-      tmem_st_32x16(tmem + 128 + b * 64 + lane_off + 16, ds + 16);
+      tmem_st_32x16(tmem + b * 64 + hf * 16 + lane_off, pp);
+      tmem_st_32x16(tmem + 128 + b * 64 + hf * 16 + lane_off, ds);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full[b]);
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
     (void)phase;
-    if (ok) ok = mbar_wait(&bars->acc_done, 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_done, 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
     if (ok) {
       tc_fence_after();
-      // dV -> sV region, dK -> sK region (both dead now), bf16, swizzled for the TMA store
+      // dV -> sV region, dK -> sK region (both dead now), bf16, swizzled for the TMA store; this warp converts
+      // output columns [hf * 64, hf * 64 + 64), which is exactly one 64-column half of the staging tile
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
-        uint8_t* dst = which == 0 ? sV : sK;
-        const uint32_t col = which == 0 ? 256 : 384;
+        uint8_t* dst = (which == 0 ? sV : sK) + hf * BIG_HALF;
+        const uint32_t col = (which == 0 ? 256 : 384) + hf * 64;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t o[16];
           tmem_ld_32x16(tmem + col + lane_off + c * 16, o);
           tmem_ld_wait();
-          const int half = c >> 2;
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             uint4 v4;
@@ -276,15 +280,15 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
             v4.y = pack_bf16(__uint_as_float(o[8 * t + 2]), __uint_as_float(o[8 * t + 3]));
             v4.z = pack_bf16(__uint_as_float(o[8 * t + 4]), __uint_as_float(o[8 * t + 5]));
             v4.w = pack_bf16(__uint_as_float(o[8 * t + 6]), __uint_as_float(o[8 * t + 7]));
-            const int chunk = (c & 3) * 2 + t;
-            *reinterpret_cast<uint4*>(dst + half * BIG_HALF + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
+            const int chunk = c * 2 + t;
+            *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
           }
         }
       }
       fence_proxy_async_smem();
     }
     tc_fence_before();
-    named_barrier(1, 128);
+    named_barrier(1, 256);
     if (ok && warp == 2 && lane == 0 && !*abort_flag) {
       tma_store_3d(&tmDV, sV, 0, kvh, kv0);
       tma_store_3d(&tmDV, sV + BIG_HALF, 64, kvh, kv0);
@@ -337,7 +341,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     mbar_init(&bars->qd_full, 1);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&bars->s_full[b], 1); mbar_init(&bars->p_full[b], 128); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&bars->s_full[b], 1); mbar_init(&bars->p_full[b], 256); }
     mbar_init(&bars->acc_done, 1);
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
@@ -374,23 +378,25 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       constexpr uint32_t IDESC_S = make_idesc_bf16(BIG, BLK, 0, 0);
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BIG, HD, 0, 1);
       bool ok = mbar_wait(&bars->qd_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
-      const uint32_t aQ = smem_u32(sQ), aD = smem_u32(sD);
+      const uint64_t qdesc0 = make_smem_desc(smem_u32(sQ), 16, 1024), ddesc0 = make_smem_desc(smem_u32(sD), 16, 1024);
+      const uint64_t stage_k0 = make_smem_desc(smem_u32(sStage), 16, 1024);
+      const uint64_t stage_mn0 = make_smem_desc(smem_u32(sStage), BLK_HALF, 1024);
       int stage = 0; uint32_t phase = 0;
       int stage2 = 0;
       auto issue_s = [&](int it) -> bool {
         if (!mbar_wait(&bars->kv_full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
         tc_fence_after();
         const int b = it & 1;
-        const uint32_t aK = smem_u32(sStage + stage * 2 * BLK_BYTES), aV = aK + BLK_BYTES;
+        const uint64_t k0d = desc_advance(stage_k0, stage * 2 * BLK_BYTES), v0d = desc_advance(k0d, BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
-          umma_ss(tmem + b * 64, make_smem_desc(aQ + offA, 16, 1024), make_smem_desc(aK + offB, 16, 1024), IDESC_S, kk > 0);
+          umma_ss(tmem + b * 64, desc_advance(qdesc0, offA), desc_advance(k0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
-          umma_ss(tmem + 128 + b * 64, make_smem_desc(aD + offA, 16, 1024), make_smem_desc(aV + offB, 16, 1024), IDESC_S, kk > 0);
+          umma_ss(tmem + 128 + b * 64, desc_advance(ddesc0, offA), desc_advance(v0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars->s_full[b]);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -402,11 +408,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int b = it & 1;
         if (!mbar_wait(&bars->p_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t aK = smem_u32(sStage + stage2 * 2 * BLK_BYTES);
+        const uint64_t kmn = desc_advance(stage_mn0, stage2 * 2 * BLK_BYTES);
+        const uint32_t acc0 = it > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)   // dQ += dS K
-          umma_ts(tmem + 256, tmem + b * 64 + kk * 8, make_smem_desc(aK + kk * 2048, BLK_HALF, 1024), IDESC_ACC,
-                  (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(tmem + 256, tmem + b * 64 + kk * 8, desc_advance(kmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
         umma_commit(&bars->kv_empty[stage2]);
         if (++stage2 == STAGES) stage2 = 0;
       }
@@ -419,29 +425,32 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else {
     const int q = warp & 3;
+    const int hf = (warp - 2) >> 2;                       // which 32 of the block's 64 key columns this warp handles
     const int r = q * 32 + lane;                          // query row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const float sl2 = scale * LOG2E;
-    const int64_t srow = (int64_t)head * Tq_pad + q0 + r;  // Tq_pad covers every row of the last tile? see launcher
-    const float my_lse2 = (q0 + r < Tq_pad) ? lse2_pad[srow] : 0.f;
-    const float my_delta = (q0 + r < Tq_pad) ? delta_pad[srow] : 0.f;
+    const int64_t srow = (int64_t)head * Tq_pad + q0 + r;  // Tq_pad is a multiple of 128: every tile row has an entry
+    const float my_lse2 = lse2_pad[srow];
+    const float my_delta = delta_pad[srow];
     bool ok = true;
     for (int it = 0; it < total; ++it) {
       const int b = it & 1;
-      const int kvb0 = it * BLK;
-      if (!mbar_wait(&bars->s_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t sv[64], dp[64];
-      tmem_ld_32x32(tmem + b * 64 + lane_off, sv);
-      tmem_ld_32x32(tmem + b * 64 + lane_off + 32, sv + 32);
-      tmem_ld_32x32(tmem + 128 + b * 64 + lane_off, dp);
-      tmem_ld_32x32(tmem + 128 + b * 64 + lane_off + 32, dp + 32);
-      tmem_ld_wait();
-      const bool diag = causal && (kvb0 + BLK - 1 > q0);
-      const bool tail = kvb0 + BLK > Tk;
-      uint32_t ds[32];
+      const int kvb0 = it * BLK + hf * 32;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      uint32_t sv[32], dp[32];
+      if (ok) {
+        tc_fence_after();
+        tmem_ld_32x32(tmem + b * 64 + hf * 32 + lane_off, sv);
+        tmem_ld_32x32(tmem + 128 + b * 64 + hf * 32 + lane_off, dp);
+        tmem_ld_wait();
+      }
+      // dS overwrites S's first 32 columns: both warps of the quarter have loaded; they also agree on leaving
+      if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
+      const bool diag = causal && (kvb0 + 31 > q0);
+      const bool tail = kvb0 + 32 > Tk;
+      uint32_t ds[16];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
+      for (int c = 0; c < 16; ++c) {
         float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - my_lse2);
         float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - my_lse2);
         if (diag) {
@@ -455,21 +464,19 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         ds[c] = pack_bf16(p0 * (__uint_as_float(dp[2 * c]) - my_delta) * scale,
                           p1 * (__uint_as_float(dp[2 * c + 1]) - my_delta) * scale);
       }
-      tmem_st_32x16(tmem + b * 64 + lane_off, ds);
-      tmem_st_32x16(tmem + b * 64 + lane_off + 16, ds + 16);
+      tmem_st_32x16(tmem + b * 64 + hf * 16 + lane_off, ds);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full[b]);
     }
-    if (ok) ok = mbar_wait(&bars->acc_done, 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_done, 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
     if (ok) {
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t o[16];
-        tmem_ld_32x16(tmem + 256 + lane_off + c * 16, o);
+        tmem_ld_32x16(tmem + 256 + hf * 64 + lane_off + c * 16, o);
         tmem_ld_wait();
-        const int half = c >> 2;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           uint4 v4;
@@ -477,14 +484,14 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           v4.y = pack_bf16(__uint_as_float(o[8 * t + 2]), __uint_as_float(o[8 * t + 3]));
           v4.z = pack_bf16(__uint_as_float(o[8 * t + 4]), __uint_as_float(o[8 * t + 5]));
           v4.w = pack_bf16(__uint_as_float(o[8 * t + 6]), __uint_as_float(o[8 * t + 7]));
-          const int chunk = (c & 3) * 2 + t;
-          *reinterpret_cast<uint4*>(sQ + half * BIG_HALF + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
+          const int chunk = c * 2 + t;
+          *reinterpret_cast<uint4*>(sQ + hf * BIG_HALF + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
         }
       }
       fence_proxy_async_smem();
     }
     tc_fence_before();
-    named_barrier(1, 128);
+    named_barrier(1, 256);
     if (ok && warp == 2 && lane == 0 && !*abort_flag) {
       tma_store_3d(&tmDQ, sQ, 0, head, q0);
       tma_store_3d(&tmDQ, sQ + BIG_HALF, 64, head, q0);

@@ -8,8 +8,9 @@
 //   * S = Q K^T and O += P V are tcgen05.mma instructions issued by one thread; S (double buffered), the
 //     bf16 probabilities P (double buffered, fed back as the TMEM A operand) and the fp32 O accumulator
 //     live in TMEM (2*128 + 2*64 + 128 = 512 columns);
-//   * four softmax warps, one thread per query row, read S straight from TMEM (no cross-thread
-//     reductions), work in the exp2 domain and rescale O lazily: the running maximum used for
+//   * eight softmax warps, two threads per query row (64 of the 128 key columns each, so every scheduler
+//     has two warps to interleave), read S straight from TMEM, exchange their partial row maxima through
+//     shared memory, work in the exp2 domain and rescale O lazily: the running maximum used for
 //     exponentiation only moves when it would grow by more than 2^8, so the O read-modify-write is rare;
 //   * QK^T of block j+1 is issued before P V of block j, so the tensor core works while the softmax
 //     warps are busy.
@@ -27,8 +28,8 @@ constexpr int TILE_BYTES = 128 * HD * 2;     // 32 KB: two 64-column halves of [
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
 constexpr int SMEM_TILES = TILE_BYTES * (1 + 2 * KV_STAGES);
-constexpr int SMEM_TOTAL = SMEM_TILES + 256 + 1024;
-constexpr int NUM_THREADS = 192;
+constexpr int SMEM_TOTAL = SMEM_TILES + 2560 + 1024;
+constexpr int NUM_THREADS = 320;     // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quarter)
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 
 struct Bars {
@@ -39,6 +40,7 @@ struct Bars {
   uint64_t drain;
   uint32_t tmem_base;
   int abort_flag;
+  float pmax[2][2][128];      // [parity][column half][row]: partial row maxima (and, at the end, row sums)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -83,7 +85,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->s_full[b], 1);
-      mbar_init(&bars->p_full[b], 128);
+      mbar_init(&bars->p_full[b], 256);
       mbar_init(&bars->pv_done[b], 1);
     }
     mbar_init(&bars->drain, 1);
@@ -128,19 +130,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t IDESC_QK = make_idesc_bf16(BM, BN, 0, 0);
       constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
-      const uint32_t aQ = smem_u32(sQ);
+      const uint64_t qdesc0 = make_smem_desc(smem_u32(sQ), 16, 1024);
+      const uint64_t kdesc0 = make_smem_desc(smem_u32(sK), 16, 1024);
+      const uint64_t vdesc0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
       auto issue_pv = [&](int j) -> bool {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&bars->p_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) return false;
         if (!mbar_wait(&bars->v_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint32_t aV = smem_u32(sV + b * TILE_BYTES);
+        const uint64_t v0 = desc_advance(vdesc0, b * TILE_BYTES);
+        const uint32_t pa = tmem + COL_P + b * 64;
+        umma_ts(tmem + COL_O, pa, v0, IDESC_PV, j > 0 ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const uint64_t bdesc = make_smem_desc(aV + kk * 2048, HALF_BYTES, 1024);
-          umma_ts(tmem + COL_O, tmem + COL_P + b * 64 + kk * 8, bdesc, IDESC_PV, (j > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 1; kk < BN / 16; ++kk) umma_ts(tmem + COL_O, pa + kk * 8, desc_advance(v0, kk * 2048), IDESC_PV, 1u);
         umma_commit(&bars->v_empty[b]);
         umma_commit(&bars->pv_done[b]);
         return true;
@@ -150,12 +153,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&bars->k_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t aK = smem_u32(sK + b * TILE_BYTES);
+        const uint64_t k0 = desc_advance(kdesc0, b * TILE_BYTES);
+        umma_ss(tmem + COL_S + b * BN, qdesc0, k0, IDESC_QK, 0u);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
+        for (int kk = 1; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          umma_ss(tmem + COL_S + b * BN, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024),
-                  IDESC_QK, kk > 0 ? 1u : 0u);
+          umma_ss(tmem + COL_S + b * BN, desc_advance(qdesc0, off), desc_advance(k0, off), IDESC_QK, 1u);
         }
         umma_commit(&bars->k_empty[b]);
         umma_commit(&bars->s_full[b]);
@@ -169,87 +172,103 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue (warps 2..5)
-    const int q = warp & 3;
+    // ------------------------------------------------------------------ softmax + epilogue (warps 2..9)
+    const int q = warp & 3;                            // TMEM lane quarter
+    const int hf = (warp - 2) >> 2;                    // key columns [hf * 64, hf * 64 + 64) of every block
     const int r = q * 32 + lane;                       // row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const float sl2 = scale * 1.4426950408889634f;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
+    // `ok` is kept warp-uniform; the two warps of a lane quarter agree on it at their exchange barrier, so
+    // they always leave the loop in the same iteration
     for (int j = 0; j < nblk; ++j) {
       const int b = j & 1;
-      if (!mbar_wait(&bars->s_full[b], (j >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t sv[128];
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (j >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      uint32_t sv[64];
+      float mx = -INFINITY;
+      if (ok) {
+        tc_fence_after();
+        tmem_ld_32x32(tmem + COL_S + b * BN + hf * 64 + lane_off, sv);
+        tmem_ld_32x32(tmem + COL_S + b * BN + hf * 64 + 32 + lane_off, sv + 32);
+        tmem_ld_wait();
+        const int kv0 = j * BN + hf * 64;
+        if (causal && j == qt) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem + COL_S + b * BN + lane_off + c * 32, sv + 32 * c);
-      tmem_ld_wait();
-      const int kv0 = j * BN;
-      if (causal && j == qt) {
+          for (int c = 0; c < 64; ++c)
+            if (hf * 64 + c > r) sv[c] = 0xff800000u;   // -inf
+        }
+        if (kv0 + 64 > Tk) {
 #pragma unroll
-        for (int c = 0; c < 128; ++c)
-          if (c > r) sv[c] = 0xff800000u;   // -inf
+          for (int c = 0; c < 64; ++c)
+            if (kv0 + c >= Tk) sv[c] = 0xff800000u;
+        }
+        mx = __uint_as_float(sv[0]);
+#pragma unroll
+        for (int c = 1; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+        // the two threads of a row swap partial maxima (double-buffered on the block parity)
+        bars->pmax[b][hf][r] = mx;
       }
-      if (kv0 + BN > Tk) {
-#pragma unroll
-        for (int c = 0; c < 128; ++c)
-          if (kv0 + c >= Tk) sv[c] = 0xff800000u;
-      }
-      float mx = __uint_as_float(sv[0]);
-#pragma unroll
-      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+      if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
+      mx = fmaxf(mx, bars->pmax[b][hf ^ 1][r]);
       const float m_new = fmaxf(m_used, mx * sl2);
       const bool need = (m_new - m_used) > 8.f;      // true on the first block (m_used = -inf)
       if (j == 0) {
         m_used = m_new;
       } else if (__any_sync(0xffffffffu, need)) {
-        // the running maximum moved by more than 2^8 for some row of this warp: rescale O and l
-        if (!mbar_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC)) { ok = false; break; }
-        tc_fence_after();
-        const float alpha = need ? fast_exp2(m_used - m_new) : 1.f;
-        if (need) m_used = m_new;
-        l *= alpha;
+        // the running maximum moved by more than 2^8 for some row of this warp: rescale O (our 64 columns) and l
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
+        if (ok) {
+          tc_fence_after();
+          const float alpha = need ? fast_exp2(m_used - m_new) : 1.f;
+          if (need) m_used = m_new;
+          l *= alpha;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t o[16];
-          tmem_ld_32x16(tmem + COL_O + lane_off + c * 16, o);
-          tmem_ld_wait();
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[16];
+            tmem_ld_32x16(tmem + COL_O + hf * 64 + lane_off + c * 16, o);
+            tmem_ld_wait();
 #pragma unroll
-          for (int t = 0; t < 16; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * alpha);
-          tmem_st_32x16(tmem + COL_O + lane_off + c * 16, o);
+            for (int t = 0; t < 16; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * alpha);
+            tmem_st_32x16(tmem + COL_O + hf * 64 + lane_off + c * 16, o);
+          }
+          tmem_st_wait();
         }
-        tmem_st_wait();
       }
       float rowsum = 0.f;
-      uint32_t pk[64];
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
+      for (int c = 0; c < 32; ++c) {
         const float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - m_used);
         const float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - m_used);
         rowsum += p0 + p1;
         pk[c] = pack_bf16(p0, p1);
       }
       l += rowsum;
-      if (j >= 2) {   // P buffer b was last read by P V of block j-2
-        if (!mbar_wait(&bars->pv_done[b], ((j - 2) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC)) { ok = false; break; }
+      if (ok && j >= 2)   // P buffer b was last read by P V of block j-2
+        ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[b], ((j - 2) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
+      if (ok) {
+        tmem_st_32x16(tmem + COL_P + b * 64 + hf * 32 + lane_off, pk);
+        tmem_st_32x16(tmem + COL_P + b * 64 + hf * 32 + 16 + lane_off, pk + 16);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[b]);
       }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_st_32x16(tmem + COL_P + b * 64 + lane_off + c * 16, pk + 16 * c);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&bars->p_full[b]);
     }
     // epilogue: O / l -> bf16 -> swizzled smem (the Q tile is dead by now) -> TMA store; lse
-    if (ok) ok = mbar_wait(&bars->pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
+    // the row sum is split over the two threads of a row
+    bars->pmax[0][hf][r] = l;
+    named_barrier(4 + q, 64);
+    l += bars->pmax[0][hf ^ 1][r];
     if (ok) {
       tc_fence_after();
       const float inv_l = 1.f / l;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {                   // our 64 output columns = staging half `hf`
         uint32_t o[16];
-        tmem_ld_32x16(tmem + COL_O + lane_off + c * 16, o);
+        tmem_ld_32x16(tmem + COL_O + hf * 64 + lane_off + c * 16, o);
         tmem_ld_wait();
-        const int half = c >> 2;                // 64 output columns per half
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           uint4 v4;
@@ -257,15 +276,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           v4.y = pack_bf16(__uint_as_float(o[8 * t + 2]) * inv_l, __uint_as_float(o[8 * t + 3]) * inv_l);
           v4.z = pack_bf16(__uint_as_float(o[8 * t + 4]) * inv_l, __uint_as_float(o[8 * t + 5]) * inv_l);
           v4.w = pack_bf16(__uint_as_float(o[8 * t + 6]) * inv_l, __uint_as_float(o[8 * t + 7]) * inv_l);
-          const int chunk = (c & 3) * 2 + t;    // 16-byte chunk inside the 128-byte row of this half
-          *reinterpret_cast<uint4*>(sQ + half * HALF_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
+          const int chunk = c * 2 + t;                // 16-byte chunk inside the 128-byte row of this half
+          *reinterpret_cast<uint4*>(sQ + hf * HALF_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
         }
       }
-      if (q0 + r < Tq) lse[(int64_t)head * Tq + q0 + r] = (m_used + log2f(l)) * 0.6931471805599453f;
+      if (hf == 0 && q0 + r < Tq) lse[(int64_t)head * Tq + q0 + r] = (m_used + log2f(l)) * 0.6931471805599453f;
       fence_proxy_async_smem();
     }
     tc_fence_before();
-    named_barrier(1, 128);
+    named_barrier(1, 256);
     if (ok && warp == 2 && lane == 0 && !*abort_flag) {
       tma_store_3d(&tmO, sQ, 0, head, q0);
       tma_store_3d(&tmO, sQ + HALF_BYTES, 64, head, q0);

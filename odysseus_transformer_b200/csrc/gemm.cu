@@ -156,6 +156,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int local_tile = 0;
       bool ok = true;
+      const uint32_t s0 = smem_u32(smem);
+      const uint64_t adesc0 = A_MN ? make_smem_desc(s0, 8192, 1024) : make_smem_desc(s0, 16, 1024);
+      const uint64_t bdesc0 = B_MN ? make_smem_desc(s0 + A_BYTES, 8192, 1024) : make_smem_desc(s0 + A_BYTES, 16, 1024);
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
         const int buf = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
@@ -165,14 +168,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&bars->full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sB = sA + A_BYTES;
+          const uint64_t a0 = desc_advance(adesc0, stage * STAGE_BYTES), b0 = desc_advance(bdesc0, stage * STAGE_BYTES);
+          umma_ss(d_tmem, a0, b0, IDESC, kb > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            const uint64_t adesc = A_MN ? make_smem_desc(sA + kk * 2048, 8192, 1024) : make_smem_desc(sA + kk * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc(sB + kk * 2048, 8192, 1024) : make_smem_desc(sB + kk * 32, 16, 1024);
-            umma_ss(d_tmem, adesc, bdesc, IDESC, (kb > 0 || kk > 0) ? 1u : 0u);
-          }
+          for (int kk = 1; kk < BK / UMMA_K; ++kk)
+            umma_ss(d_tmem, desc_advance(a0, kk * (A_MN ? 2048 : 32)), desc_advance(b0, kk * (B_MN ? 2048 : 32)), IDESC, 1u);
           umma_commit(&bars->empty[stage]);        // frees the smem stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }

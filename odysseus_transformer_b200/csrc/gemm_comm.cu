@@ -21,6 +21,12 @@
 // arrived / consumed), written with release.sys and polled with acquire.sys.  Every poll is bounded and
 // reports through the status word; nothing here can spin forever.
 #include "ody_kernels.h"
+
+// Waits in this file may legitimately last as long as another rank is behind (first-step set-up, host
+// jitter), so their bound is a run-time setting (default about 10 s of SM clocks) instead of the 1 s used
+// by the single-GPU kernels.  ody_set_peer_wait_limit changes it for the current device.
+namespace ody { namespace gc { __device__ long long g_spin_limit = 20000000000ll; } }
+#define ODY_SPIN_LIMIT_CYCLES (ody::gc::g_spin_limit)
 #include "sm100.cuh"
 
 namespace ody {
@@ -380,6 +386,9 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; int local_tile = 0; bool ok = true;
+      const uint32_t s0 = smem_u32(smem);
+      const uint64_t adesc0 = A_MN ? make_smem_desc(s0, 8192, 1024) : make_smem_desc(s0, 16, 1024);
+      const uint64_t bdesc0 = B_MN ? make_smem_desc(s0 + A_BYTES, 8192, 1024) : make_smem_desc(s0 + A_BYTES, 16, 1024);
       for (int tile = gemm_idx; tile < num_tiles && ok; tile += n_gemm, ++local_tile) {
         const int buf = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
@@ -389,13 +398,11 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&bars->full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES), sB = sA + A_BYTES;
+          const uint64_t a0 = desc_advance(adesc0, stage * STAGE_BYTES), b0 = desc_advance(bdesc0, stage * STAGE_BYTES);
+          umma_ss(d_tmem, a0, b0, IDESC, kb > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            const uint64_t adesc = A_MN ? make_smem_desc(sA + kk * 2048, 8192, 1024) : make_smem_desc(sA + kk * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc(sB + kk * 2048, 8192, 1024) : make_smem_desc(sB + kk * 32, 16, 1024);
-            umma_ss(d_tmem, adesc, bdesc, IDESC, (kb > 0 || kk > 0) ? 1u : 0u);
-          }
+          for (int kk = 1; kk < BK / UMMA_K; ++kk)
+            umma_ss(d_tmem, desc_advance(a0, kk * (A_MN ? 2048 : 32)), desc_advance(b0, kk * (B_MN ? 2048 : 32)), IDESC, 1u);
           umma_commit(&bars->empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -744,4 +751,9 @@ extern "C" int ody_push_shard(const OdyGatherDesc* pd, int* err, cudaStream_t st
   if (pd->shard == nullptr || (pd->shard_ld % 8) || ((uintptr_t)pd->shard & 15) || pd->n_cta <= 0) return (int)cudaErrorInvalidValue;
   push_shard_kernel<<<pd->n_cta, COMM_THREADS, 0, st>>>(pp, err);
   return (int)cudaGetLastError();
+}
+
+extern "C" int ody_set_peer_wait_limit(long long cycles) {
+  if (cycles <= 0) return (int)cudaErrorInvalidValue;
+  return (int)cudaMemcpyToSymbol(ody::gc::g_spin_limit, &cycles, sizeof(cycles));
 }

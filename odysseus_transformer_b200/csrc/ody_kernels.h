@@ -88,6 +88,8 @@ int ody_gemm_comm(const void* A, const void* B, void* C, int M, int N, int K, in
                   int layout, const OdyGatherDesc* gather, const OdyGatherDesc* push, const OdyScatterDesc* scatter, int* err,
                   cudaStream_t stream);
 int ody_push_shard(const OdyGatherDesc* push, int* err, cudaStream_t stream);
+// bound (SM clock cycles) of every wait inside the fused kernels on the current device; default ~10 s
+int ody_set_peer_wait_limit(long long cycles);
 
 // ---- copy between (peer-mapped) device buffers with plain 16-byte loads/stores on n_ctas x threads threads
 int ody_peer_copy(void* dst, const void* src, int64_t bytes, int n_ctas, int threads, cudaStream_t stream);

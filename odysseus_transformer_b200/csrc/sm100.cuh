@@ -120,6 +120,17 @@ __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* tmap) {
 __device__ __forceinline__ void named_barrier(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// Named barrier that also ANDs a predicate over its participants: used so that the warps sharing a barrier
+// leave a loop together when one of them saw a wait give up (a warp that left alone would strand the others).
+__device__ __forceinline__ bool named_barrier_and(int id, int nthreads, bool ok) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, %3, q;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(r)
+      : "r"((uint32_t)ok), "r"(id), "r"(nthreads)
+      : "memory");
+  return r != 0;
+}
 
 // ---- tcgen05 / TMEM (cta_group::1)
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {   // whole warp
@@ -202,6 +213,14 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   d |= (uint64_t)1 << 46;   // descriptor version for sm_100
   d |= (uint64_t)2 << 61;   // SWIZZLE_128B
   return d;
+}
+// Advance a descriptor's start address by `bytes` (a multiple of 16).  Only the low word changes - the issuing
+// thread spends one add per MMA instead of rebuilding the descriptor, and a single thread's instruction
+// stream is what bounds how fast small MMAs can be issued.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t bytes) {
+  uint2 v = *reinterpret_cast<uint2*>(&d);
+  v.x += bytes >> 4;
+  return *reinterpret_cast<uint64_t*>(&v);
 }
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_major, int b_mn_major) {

@@ -16,6 +16,7 @@ def test_unsatisfied_peer_wait_reports_status_and_returns():
     lib = native.lib()
     dev = torch.device("cuda", 0)
     lib.clear_status(0)
+    lib.set_peer_wait_limit(1_000_000_000)        # ~0.5 s instead of the 10 s default, to keep the test short
     n, chunk, cols, N = 2, 128, 256, 256
     gathered = torch.zeros(n * chunk, cols, device=dev, dtype=torch.bfloat16)
     w = torch.randn(N, cols, device=dev).to(torch.bfloat16)
@@ -35,6 +36,7 @@ def test_unsatisfied_peer_wait_reports_status_and_returns():
     torch.cuda.synchronize()
     assert e0.elapsed_time(e1) < 10_000, "the bounded wait did not end in time"
     assert lib.status(0) == 105
+    lib.set_peer_wait_limit(20_000_000_000)
     with pytest.raises(RuntimeError):
         native.check_status(0)
     assert lib.status(0) == 0
