@@ -98,7 +98,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                       const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
                       const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad, int Tq, int Tk, int Tq_pad,
-                      int H, int Hkv, int causal, float scale, int* __restrict__ err) {
+                      int H, int Hkv, int causal, float scale, int* __restrict__ err, long long* __restrict__ dbg) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -167,22 +167,23 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       const uint64_t stage_mn0 = make_smem_desc(smem_u32(sStage), BLK_HALF, 1024);     // MN-major view (B of dV / dK)
       int stage = 0; uint32_t phase = 0;          // ring position of the next S/dP issue
       int stage2 = 0;                             // ring position of the next dV/dK issue
+      const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
       auto issue_s = [&](int it) -> bool {
+        if (trace && it < 48) dbg[it * 8 + 0] = clock64();                 // MMA thread starts on S/dP(it)
         if (!mbar_wait(&bars->qd_full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
+        if (trace && it < 48) dbg[it * 8 + 1] = clock64();                 // Q/dO block landed
         tc_fence_after();
         const int b = it & 1;
         const uint64_t q0d = desc_advance(stage_k0, stage * 2 * BLK_BYTES), d0d = desc_advance(q0d, BLK_BYTES);
+        // S^T and dP^T alternate so consecutive instructions never accumulate into the same TMEM tile
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
           umma_ss(tmem + b * 64, desc_advance(kdesc0, offA), desc_advance(q0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
           umma_ss(tmem + 128 + b * 64, desc_advance(vdesc0, offA), desc_advance(d0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars->s_full[b]);
+        if (trace && it < 48) dbg[it * 8 + 2] = clock64();                 // S/dP(it) issued
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
         return true;
       };
@@ -191,16 +192,17 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         if (it + 1 < total && !issue_s(it + 1)) { ok = false; break; }
         const int b = it & 1;
         if (!mbar_wait(&bars->p_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        if (trace && it < 48) dbg[it * 8 + 3] = clock64();                 // MMA thread saw P(it)
         tc_fence_after();
         const uint64_t qmn = desc_advance(stage_mn0, stage2 * 2 * BLK_BYTES), dmn = desc_advance(qmn, BLK_BYTES);
         const uint32_t acc0 = it > 0 ? 1u : 0u;
 #pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk)   // dV += P^T dO
+        for (int kk = 0; kk < BLK / 16; ++kk) {   // dV += P^T dO and dK += dS^T Q, alternating
           umma_ts(tmem + 256, tmem + b * 64 + kk * 8, desc_advance(dmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
-#pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk)   // dK += dS^T Q
           umma_ts(tmem + 384, tmem + 128 + b * 64 + kk * 8, desc_advance(qmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        }
         umma_commit(&bars->qd_empty[stage2]);
+        if (trace && it < 48) dbg[it * 8 + 4] = clock64();                 // dV/dK(it) issued
         if (++stage2 == STAGES) stage2 = 0;
       }
       if (ok) umma_commit(&bars->acc_done);
@@ -221,7 +223,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     for (int it = 0; it < total; ++it) {
       const int b = it & 1;
       const int qrow0 = (i0 + it % per_head) * BLK + hf * 32;
+      const bool strace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64 && it < 48;
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      if (strace) dbg[it * 8 + 5] = clock64();                             // softmax saw S(it)
       // s_full implies qd_full[stage] completed earlier (the MMAs consumed it); the stats are in smem
       const float* st = (const float*)(sStat + stage * STAT_BYTES) + hf * 32;
       uint32_t sv[32], dp[32];
@@ -234,6 +238,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       // P^T / dS^T are written over the first 32 columns of S^T / dP^T: the other warp of this lane quarter
       // must have read its inputs before either of us stores; the two also agree here on leaving the loop
       if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
+      if (strace) dbg[it * 8 + 6] = clock64();                             // loaded + pair barrier
       const bool diag = causal && (qrow0 < kv0 + BIG);     // some (q, kv) pairs of this half block are masked
       uint32_t pp[16], ds[16];
 #pragma unroll
@@ -256,6 +261,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full[b]);
+      if (strace) dbg[it * 8 + 7] = clock64();                             // P(it) published
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
     (void)phase;
@@ -392,10 +398,6 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
           umma_ss(tmem + b * 64, desc_advance(qdesc0, offA), desc_advance(k0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
           umma_ss(tmem + 128 + b * 64, desc_advance(ddesc0, offA), desc_advance(v0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
         }
         umma_commit(&bars->s_full[b]);
@@ -507,6 +509,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }  // namespace bwd
 }  // namespace ody
 
+static long long* g_bwd_trace = nullptr;
+// Optional per-block timeline of CTA (0,0) of the dK/dV kernel: 48 x 8 SM-clock stamps (see the kernel).
+extern "C" void ody_flash_bwd_set_trace(long long* buf) { g_bwd_trace = buf; }
+
 extern "C" int64_t ody_flash_bwd_workspace_bytes(int Tq, int H) {
   const int64_t Tpad = ((int64_t)Tq + 127) / 128 * 128;
   return 2 * (int64_t)H * Tpad * 4;
@@ -558,7 +564,7 @@ extern "C" int ody_flash_bwd(const void* dO, const void* q, const void* k, const
   if ((r = make_tmap_3d_bf16(&tDV, dv, HD, Hkv, Tk, HD * 2, dv_row * 2, 64, 1, BIG))) return 790000 + r;
   dim3 gkv((Tk + BIG - 1) / BIG, Hkv);
   flash_bwd_dkdv_kernel<<<gkv, NUM_THREADS, KV_SMEM_TOTAL, st>>>(tQ64, tDO64, tK, tV, tDK, tDV, lse2_pad, delta_pad, Tq, Tk,
-                                                                 Tpad, H, Hkv, causal, scale, err);
+                                                                 Tpad, H, Hkv, causal, scale, err, g_bwd_trace);
   dim3 gq((Tq + BIG - 1) / BIG, H);
   flash_bwd_dq_kernel<<<gq, NUM_THREADS, Q_SMEM_TOTAL, st>>>(tQ, tDO, tK64, tV64, tDQ, lse2_pad, delta_pad, Tq, Tk, Tpad, H,
                                                              Hkv, causal, scale, err);

@@ -12,8 +12,10 @@
 //     has two warps to interleave), read S straight from TMEM, exchange their partial row maxima through
 //     shared memory, work in the exp2 domain and rescale O lazily: the running maximum used for
 //     exponentiation only moves when it would grow by more than 2^8, so the O read-modify-write is rare;
-//   * QK^T of block j+1 is issued before P V of block j, so the tensor core works while the softmax
-//     warps are busy.
+//   * S = Q K^T and O += P V are issued by two different warps: a single thread sustains only about one
+//     tcgen05.mma per ~85 cycles, and with 64-cycle instructions one issuer would leave the tensor core
+//     idle a third of the time.  Q K^T of block j+2 goes out as soon as the softmax warps have loaded
+//     S of block j into registers.
 //
 // q [Tq, H, 128], k/v [Tk, Hkv, 128] with arbitrary row pitch; out [Tq, H, 128] bf16; lse [H, Tq] fp32
 // (natural log).  causal requires Tq == Tk (row i sees keys 0..i).
@@ -29,14 +31,14 @@ constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
 constexpr int SMEM_TILES = TILE_BYTES * (1 + 2 * KV_STAGES);
 constexpr int SMEM_TOTAL = SMEM_TILES + 2560 + 1024;
-constexpr int NUM_THREADS = 320;     // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quarter)
+constexpr int NUM_THREADS = 352;     // TMA warp, QK^T issuer, 8 softmax warps (two per TMEM lane quarter), P V issuer
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 
 struct Bars {
   uint64_t q_full;
   uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
   uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-  uint64_t s_full[2], p_full[2], pv_done[2];
+  uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
   uint64_t drain;
   uint32_t tmem_base;
   int abort_flag;
@@ -85,6 +87,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->s_full[b], 1);
+      mbar_init(&bars->s_free[b], 256);
       mbar_init(&bars->p_full[b], 256);
       mbar_init(&bars->pv_done[b], 1);
     }
@@ -125,33 +128,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ Q K^T issuer
     if (lane == 0) {
       constexpr uint32_t IDESC_QK = make_idesc_bf16(BM, BN, 0, 0);
-      constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
       const uint64_t qdesc0 = make_smem_desc(smem_u32(sQ), 16, 1024);
       const uint64_t kdesc0 = make_smem_desc(smem_u32(sK), 16, 1024);
-      const uint64_t vdesc0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
-      auto issue_pv = [&](int j) -> bool {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&bars->p_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) return false;
-        if (!mbar_wait(&bars->v_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
-        tc_fence_after();
-        const uint64_t v0 = desc_advance(vdesc0, b * TILE_BYTES);
-        const uint32_t pa = tmem + COL_P + b * 64;
-        umma_ts(tmem + COL_O, pa, v0, IDESC_PV, j > 0 ? 1u : 0u);
-#pragma unroll
-        for (int kk = 1; kk < BN / 16; ++kk) umma_ts(tmem + COL_O, pa + kk * 8, desc_advance(v0, kk * 2048), IDESC_PV, 1u);
-        umma_commit(&bars->v_empty[b]);
-        umma_commit(&bars->pv_done[b]);
-        return true;
-      };
       for (int j = 0; j < nblk && ok; ++j) {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&bars->k_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
+        // S buffer b was last read by the softmax of block j-2
+        if (j >= 2 && !mbar_wait(&bars->s_free[b], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint64_t k0 = desc_advance(kdesc0, b * TILE_BYTES);
         umma_ss(tmem + COL_S + b * BN, qdesc0, k0, IDESC_QK, 0u);
@@ -162,13 +150,31 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         umma_commit(&bars->k_empty[b]);
         umma_commit(&bars->s_full[b]);
-        if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
       }
-      if (ok) ok = issue_pv(nblk - 1);
       if (!ok) {
         umma_commit(&bars->drain);
         const long long t0 = clock64();
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ P V issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
+      const uint64_t vdesc0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
+      for (int j = 0; j < nblk; ++j) {
+        const int b = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&bars->p_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) break;
+        if (!mbar_wait(&bars->v_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) break;
+        tc_fence_after();
+        const uint64_t v0 = desc_advance(vdesc0, b * TILE_BYTES);
+        const uint32_t pa = tmem + COL_P + b * 64;
+        umma_ts(tmem + COL_O, pa, v0, IDESC_PV, j > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 1; kk < BN / 16; ++kk) umma_ts(tmem + COL_O, pa + kk * 8, desc_advance(v0, kk * 2048), IDESC_PV, 1u);
+        umma_commit(&bars->v_empty[b]);
+        umma_commit(&bars->pv_done[b]);
       }
     }
   } else {
@@ -192,6 +198,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(tmem + COL_S + b * BN + hf * 64 + lane_off, sv);
         tmem_ld_32x32(tmem + COL_S + b * BN + hf * 64 + 32 + lane_off, sv + 32);
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->s_free[b]);                 // S(j) is in registers: Q K^T of block j+2 may overwrite it
         const int kv0 = j * BN + hf * 64;
         if (causal && j == qt) {
 #pragma unroll
@@ -203,11 +211,32 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int c = 0; c < 64; ++c)
             if (kv0 + c >= Tk) sv[c] = 0xff800000u;
         }
-        mx = __uint_as_float(sv[0]);
+        // partial row maximum over our 64 columns, four independent chains
+        float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]), m2 = __uint_as_float(sv[2]), m3 = __uint_as_float(sv[3]);
 #pragma unroll
-        for (int c = 1; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+        for (int c = 4; c < 64; c += 4) {
+          m0 = fmaxf(m0, __uint_as_float(sv[c]));
+          m1 = fmaxf(m1, __uint_as_float(sv[c + 1]));
+          m2 = fmaxf(m2, __uint_as_float(sv[c + 2]));
+          m3 = fmaxf(m3, __uint_as_float(sv[c + 3]));
+        }
+        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         // the two threads of a row swap partial maxima (double-buffered on the block parity)
         bars->pmax[b][hf][r] = mx;
+      }
+      // Speculation: the maximum used for exponentiation almost never moves after the first blocks (it only
+      // moves when it would grow by more than 2^8), so the first half of the exponentials is issued with the
+      // current one BEFORE the partner's partial maximum is known; they are redone in the rare case it moves.
+      float rowsum = 0.f;
+      uint32_t pk[32];
+      if (ok && j > 0) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - m_used);
+          const float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - m_used);
+          rowsum += p0 + p1;
+          pk[c] = pack_bf16(p0, p1);
+        }
       }
       if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
       mx = fmaxf(mx, bars->pmax[b][hf ^ 1][r]);
@@ -235,10 +264,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_wait();
         }
       }
-      float rowsum = 0.f;
-      uint32_t pk[32];
+      if (j == 0 || need) {                           // the speculative half used a stale maximum: redo it
+        rowsum = 0.f;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
+        for (int c = 0; c < 16; ++c) {
+          const float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - m_used);
+          const float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - m_used);
+          rowsum += p0 + p1;
+          pk[c] = pack_bf16(p0, p1);
+        }
+      }
+#pragma unroll
+      for (int c = 16; c < 32; ++c) {
         const float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - m_used);
         const float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - m_used);
         rowsum += p0 + p1;
