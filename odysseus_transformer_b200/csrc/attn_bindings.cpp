@@ -73,6 +73,10 @@ std::vector<at::Tensor> attn_bwd(const at::Tensor& dO, const at::Tensor& q, cons
 
 void ody_register_attention(pybind11::module& m) {
   m.def("attn_fwd", &attn_fwd);
+  m.def("attn_fwd_set_trace", [](const c10::optional<at::Tensor>& t) {
+    if (t.has_value()) { req(t.value().is_cuda() && t.value().scalar_type() == at::kLong && t.value().numel() >= 48 * 8, "trace: int64 [48*8]"); ody_flash_fwd_set_trace((long long*)t.value().data_ptr()); }
+    else ody_flash_fwd_set_trace(nullptr);
+  });
   m.def("attn_bwd_set_trace", [](const c10::optional<at::Tensor>& t) {
     if (t.has_value()) { req(t.value().is_cuda() && t.value().scalar_type() == at::kLong && t.value().numel() >= 48 * 8, "trace: int64 [48*8]"); ody_flash_bwd_set_trace((long long*)t.value().data_ptr()); }
     else ody_flash_bwd_set_trace(nullptr);

@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                  float* __restrict__ lse, int Tq, int Tk, int H, int Hkv, int causal, float scale,
-                 int* __restrict__ err) {
+                 int* __restrict__ err, long long* __restrict__ dbg) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -137,9 +137,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < nblk && ok; ++j) {
         const int b = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        const bool tr = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && j < 48;
+        if (tr) dbg[j * 8 + 0] = clock64();
         if (!mbar_wait(&bars->k_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
         // S buffer b was last read by the softmax of block j-2
         if (j >= 2 && !mbar_wait(&bars->s_free[b], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+        if (tr) dbg[j * 8 + 1] = clock64();
         tc_fence_after();
         const uint64_t k0 = desc_advance(kdesc0, b * TILE_BYTES);
         umma_ss(tmem + COL_S + b * BN, qdesc0, k0, IDESC_QK, 0u);
@@ -150,6 +153,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         umma_commit(&bars->k_empty[b]);
         umma_commit(&bars->s_full[b]);
+        if (tr) dbg[j * 8 + 2] = clock64();
       }
       if (!ok) {
         umma_commit(&bars->drain);
@@ -167,6 +171,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&bars->p_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) break;
         if (!mbar_wait(&bars->v_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) break;
+        const bool tr = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && j < 48;
+        if (tr) dbg[j * 8 + 3] = clock64();
         tc_fence_after();
         const uint64_t v0 = desc_advance(vdesc0, b * TILE_BYTES);
         const uint32_t pa = tmem + COL_P + b * 64;
@@ -175,6 +181,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int kk = 1; kk < BN / 16; ++kk) umma_ts(tmem + COL_O, pa + kk * 8, desc_advance(v0, kk * 2048), IDESC_PV, 1u);
         umma_commit(&bars->v_empty[b]);
         umma_commit(&bars->pv_done[b]);
+        if (tr) dbg[j * 8 + 4] = clock64();
       }
     }
   } else {
@@ -190,7 +197,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // they always leave the loop in the same iteration
     for (int j = 0; j < nblk; ++j) {
       const int b = j & 1;
+      const bool str_ = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64 && j < 48;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (j >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      if (str_) dbg[j * 8 + 5] = clock64();
       uint32_t sv[64];
       float mx = -INFINITY;
       if (ok) {
@@ -224,21 +233,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // the two threads of a row swap partial maxima (double-buffered on the block parity)
         bars->pmax[b][hf][r] = mx;
       }
-      // Speculation: the maximum used for exponentiation almost never moves after the first blocks (it only
-      // moves when it would grow by more than 2^8), so the first half of the exponentials is issued with the
-      // current one BEFORE the partner's partial maximum is known; they are redone in the rare case it moves.
-      float rowsum = 0.f;
-      uint32_t pk[32];
-      if (ok && j > 0) {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - m_used);
-          const float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - m_used);
-          rowsum += p0 + p1;
-          pk[c] = pack_bf16(p0, p1);
-        }
-      }
       if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
+      if (str_) dbg[j * 8 + 6] = clock64();
       mx = fmaxf(mx, bars->pmax[b][hf ^ 1][r]);
       const float m_new = fmaxf(m_used, mx * sl2);
       const bool need = (m_new - m_used) > 8.f;      // true on the first block (m_used = -inf)
@@ -264,18 +260,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_wait();
         }
       }
-      if (j == 0 || need) {                           // the speculative half used a stale maximum: redo it
-        rowsum = 0.f;
+      float rowsum = 0.f;
+      uint32_t pk[32];
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - m_used);
-          const float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - m_used);
-          rowsum += p0 + p1;
-          pk[c] = pack_bf16(p0, p1);
-        }
-      }
-#pragma unroll
-      for (int c = 16; c < 32; ++c) {
+      for (int c = 0; c < 32; ++c) {
         const float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - m_used);
         const float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - m_used);
         rowsum += p0 + p1;
@@ -290,6 +278,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&bars->p_full[b]);
+        if (str_) dbg[j * 8 + 7] = clock64();
       }
     }
     // epilogue: O / l -> bf16 -> swizzled smem (the Q tile is dead by now) -> TMA store; lse
@@ -341,6 +330,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }  // namespace fwd
 }  // namespace ody
 
+static long long* g_fwd_trace = nullptr;
+// Optional per-block timeline (48 x 8 SM-clock stamps) of the CTA with blockIdx (0, 0).
+extern "C" void ody_flash_fwd_set_trace(long long* buf) { g_fwd_trace = buf; }
+
 // q/k/v/o: bf16, head_dim 128, element strides: *_row (token pitch), heads packed (pitch 128).
 extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H,
                              int Hkv, int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal,
@@ -364,6 +357,6 @@ extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* 
   if ((r = make_tmap_3d_bf16(&tV, v, HD, Hkv, Tk, HD * 2, v_row * 2, 64, 1, BN))) return 750000 + r;
   if ((r = make_tmap_3d_bf16(&tO, o, HD, H, Tq, HD * 2, o_row * 2, 64, 1, BM))) return 760000 + r;
   dim3 grid((Tq + BM - 1) / BM, H);
-  flash_fwd_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err);
+  flash_fwd_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, g_fwd_trace);
   return (int)cudaGetLastError();
 }

@@ -69,6 +69,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef ODY_WAIT_SLEEP_NS
+    __nanosleep(ODY_WAIT_SLEEP_NS);     // a polling warp otherwise competes for issue slots with the working warps of its scheduler
+#endif
     if ((++spins & 0x3f) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > ODY_SPIN_LIMIT_CYCLES) {
