@@ -127,7 +127,8 @@ class SymmetricHeap:
         dist.barrier(group=group)
         self._data_top = 0
         self._flag_top = 0
-        self._gather: Dict[Tuple[int, int], List[GatherSlot]] = {}
+        self._side: Optional[torch.cuda.Stream] = None
+        self._gather: Dict[Tuple[int, int, str], List[GatherSlot]] = {}
         self._scatter: Dict[Tuple[int, int], List[ScatterSlot]] = {}
         self._toggle: Dict[Tuple[str, int, int], int] = {}
         # optional per-CTA timeline of the last gather launch (set by enable_stats)
@@ -169,8 +170,16 @@ class SymmetricHeap:
         return self._data_top + _round_up(nbytes, ALIGN) * 2 <= self.capacity
 
     # ---- slots
-    def gather_slot(self, chunk_rows: int, cols: int) -> Optional[GatherSlot]:
-        key = (chunk_rows, cols)
+    def side_stream(self) -> torch.cuda.Stream:
+        """A second stream of this device for push-only launches that overlap compute."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        return self._side
+
+    def gather_slot(self, chunk_rows: int, cols: int, tag: str = "") -> Optional[GatherSlot]:
+        """``tag`` separates call sites whose flag protocols differ (ring attention never raises the
+        row-block counters of a rank's own rows) from the GEMM gathers of the same shape."""
+        key = (chunk_rows, cols, tag)
         if key not in self._gather:
             if chunk_rows % 64 or cols % 64 or not self.can_hold(self.n * chunk_rows * cols * 2):
                 return None
@@ -195,7 +204,8 @@ def heap_bytes_estimate(cfg, tokens_per_rank: int, n: int) -> int:
     d, i = cfg.hidden_size, cfg.intermediate_size
     act = n * tokens_per_rank * d * 2
     weights = (2 * i * d + d * i + cfg.vocab_size * d) * 2
-    return 2 * (2 * act) + 2 * (2 * weights) + (64 << 20)
+    kv = n * tokens_per_rank * 2 * cfg.num_key_value_heads * cfg.head_dim * 2     # ring attention's gathered K|V
+    return 2 * (2 * act) + 2 * (2 * weights) + 2 * kv + (64 << 20)
 
 
 def setup_fused_comm(ctx, cfg=None, tokens_per_rank: int = 0, data_bytes: int = 0) -> bool:
@@ -206,7 +216,7 @@ def setup_fused_comm(ctx, cfg=None, tokens_per_rank: int = 0, data_bytes: int = 
     if ctx.world_size == 1 or ctx.device.type != "cuda" or not native.available():
         return False
     groups = []
-    for g in (ctx.inner_group, ctx.world_group):
+    for g in (ctx.inner_group, ctx.world_group, ctx.ring_group):
         if g is not None and dist.get_world_size(g) > 1 and all(g is not h for h in groups):
             groups.append(g)
     ok = False

@@ -63,6 +63,57 @@ void fill_gather_desc(const py::dict& d, OdyGatherDesc& gd, std::vector<at::Tens
   gd.prev_epoch = get<uint32_t>(d, "prev_epoch");
   gd.uses = get<uint32_t>(d, "uses");
   gd.which = d.contains("which") ? get<int>(d, "which") : 0;
+  gd.dest_first = d.contains("dest_first") ? get<int>(d, "dest_first") : 0;
+  gd.dest_count = d.contains("dest_count") ? get<int>(d, "dest_count") : 0;
+}
+
+void check_heads(const at::Tensor& t, const char* name) {
+  req(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 3 && t.size(2) == 128 && t.stride(2) == 1 &&
+          t.stride(1) == 128 && t.stride(0) % 8 == 0,
+      std::string(name) + " must be CUDA bf16 [T, heads, 128] with packed heads");
+}
+
+// Attention forward (as attn_fwd) whose comm warps deliver push["shard"] (the packed local K|V rows) to the ring
+// peers named by push["dest_first"/"dest_count"] while the tiles run.
+std::vector<at::Tensor> attn_fwd_push(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, bool causal, double scale,
+                                      const py::dict& push) {
+  check_heads(q, "q"); check_heads(k, "k"); check_heads(v, "v");
+  req(k.size(0) == v.size(0) && k.size(1) == v.size(1) && q.size(1) % k.size(1) == 0, "q/k/v shape mismatch");
+  req(!causal || q.size(0) == k.size(0), "causal attention needs Tq == Tk");
+  c10::cuda::CUDAGuard guard(q.device());
+  OdyGatherDesc pd;
+  std::vector<at::Tensor> keep;
+  fill_gather_desc(push, pd, keep, true);
+  req((pd.shard_ld % 8) == 0 && ((uintptr_t)pd.shard & 15) == 0, "push shard alignment");
+  const int64_t Tq = q.size(0), Tk = k.size(0), H = q.size(1), Hkv = k.size(1);
+  auto o = at::empty({Tq, H, 128}, q.options());
+  auto lse = at::empty({H, Tq}, q.options().dtype(at::kFloat));
+  int rc = ody_flash_fwd_push(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), (int)Tq, (int)Tk,
+                              (int)H, (int)Hkv, q.stride(0), k.stride(0), v.stride(0), o.stride(0), causal ? 1 : 0, (float)scale,
+                              &pd, ody_status_ptr(q), at::cuda::getCurrentCUDAStream().stream());
+  req(rc == 0, "flash_fwd_push failed with code " + std::to_string(rc));
+  ody_count_launches(1);
+  return {o, lse};
+}
+
+void wait_shard(const py::dict& slot, int64_t src) {
+  OdyGatherDesc d;
+  std::vector<at::Tensor> keep;
+  fill_gather_desc(slot, d, keep, false);
+  c10::cuda::CUDAGuard guard(keep[0].device());
+  int rc = ody_wait_shard(&d, (int)src, ody_status_ptr(keep[0]), at::cuda::getCurrentCUDAStream().stream());
+  req(rc == 0, "wait_shard failed with code " + std::to_string(rc));
+  ody_count_launches(1);
+}
+
+void signal_free(const py::dict& slot) {
+  OdyGatherDesc d;
+  std::vector<at::Tensor> keep;
+  fill_gather_desc(slot, d, keep, false);
+  c10::cuda::CUDAGuard guard(keep[0].device());
+  int rc = ody_signal_free(&d, at::cuda::getCurrentCUDAStream().stream());
+  req(rc == 0, "signal_free failed with code " + std::to_string(rc));
+  ody_count_launches(1);
 }
 
 at::Tensor gemm_comm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& out, int64_t layout,
@@ -140,6 +191,9 @@ void peer_copy(int64_t dst, int64_t src, int64_t bytes, int64_t n_ctas, int64_t 
 void ody_register_comm(pybind11::module& m) {
   m.def("peer_copy", &peer_copy);
   m.def("push_shard", &push_shard);
+  m.def("attn_fwd_push", &attn_fwd_push);
+  m.def("wait_shard", &wait_shard);
+  m.def("signal_free", &signal_free);
   m.def("set_peer_wait_limit", [](int64_t cycles) { req(ody_set_peer_wait_limit(cycles) == 0, "set_peer_wait_limit failed"); });
   m.def("gemm_comm", &gemm_comm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("layout"), py::arg("gather"),
         py::arg("push"), py::arg("scatter"));

@@ -21,6 +21,7 @@
 // (natural log).  causal requires Tq == Tk (row i sees keys 0..i).
 #include "ody_kernels.h"
 #include "sm100.cuh"
+#include "peer_comm.cuh"
 
 namespace ody {
 namespace fwd {
@@ -31,7 +32,10 @@ constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
 constexpr int SMEM_TILES = TILE_BYTES * (1 + 2 * KV_STAGES);
 constexpr int SMEM_TOTAL = SMEM_TILES + 2560 + 1024;
-constexpr int NUM_THREADS = 352;     // TMA warp, QK^T issuer, 8 softmax warps (two per TMEM lane quarter), P V issuer
+// Warp roles, grouped by warpgroup so that the PUSH variant can move registers between them:
+//   0 TMA producer, 1 Q K^T issuer, 2 P V issuer, 3 idle | 4..11 softmax (two per TMEM lane quarter) | 12..15 comm (PUSH only)
+constexpr int NUM_THREADS = 384;
+constexpr int NUM_THREADS_PUSH = NUM_THREADS + gc::COMM_THREADS;
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 
 struct Bars {
@@ -56,11 +60,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&t);
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// PUSH: four extra comm warps in CTAs 0..push_ctas-1 store this rank's K/V shard into the gathered
+// buffers of the ring peers named by `pp` while the attention tiles run (ring attention: the kernel of
+// ring step s delivers the shard that the peer s+1 places downstream needs for its step s+1).
+template <bool PUSH>
+__global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                  float* __restrict__ lse, int Tq, int Tk, int H, int Hkv, int causal, float scale,
-                 int* __restrict__ err, long long* __restrict__ dbg) {
+                 int* __restrict__ err, long long* __restrict__ dbg, const __grid_constant__ gc::GatherParams pp,
+                 int push_ctas) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -108,7 +122,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 0) {
+  // PUSH: 512 threads start with 128 registers each; the softmax warpgroups need more, everyone else far less
+  if (warp >= 12) {
+    // ------------------------------------------------------------------ comm warps (PUSH only)
+    if constexpr (PUSH) {
+      reg_dec<104>();
+      const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+      if (cta < push_ctas) gc::comm_warps_main(pp, cta, push_ctas, 12 * 32, abort_flag, err);
+    }
+  } else if (warp < 4) {
+   if constexpr (PUSH) reg_dec<56>();
+   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(&bars->q_full, TILE_BYTES);
@@ -161,7 +185,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
       }
     }
-  } else if (warp == 10) {
+  } else if (warp == 2) {
     // ------------------------------------------------------------------ P V issuer
     if (lane == 0) {
       constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
@@ -184,10 +208,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (tr) dbg[j * 8 + 4] = clock64();
       }
     }
+   }   // warp 3 idles: it only keeps the warpgroups aligned
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue (warps 2..9)
+    // ------------------------------------------------------------------ softmax + epilogue (warps 4..11)
+    if constexpr (PUSH) reg_inc<176>();
     const int q = warp & 3;                            // TMEM lane quarter
-    const int hf = (warp - 2) >> 2;                    // key columns [hf * 64, hf * 64 + 64) of every block
+    const int hf = (warp - 4) >> 2;                    // key columns [hf * 64, hf * 64 + 64) of every block
     const int r = q * 32 + lane;                       // row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const float sl2 = scale * 1.4426950408889634f;
@@ -197,7 +223,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // they always leave the loop in the same iteration
     for (int j = 0; j < nblk; ++j) {
       const int b = j & 1;
-      const bool str_ = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64 && j < 48;
+      const bool str_ = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 128 && j < 48;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (j >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
       if (str_) dbg[j * 8 + 5] = clock64();
       uint32_t sv[64];
@@ -311,7 +337,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     tc_fence_before();
     named_barrier(1, 256);
-    if (ok && warp == 2 && lane == 0 && !*abort_flag) {
+    if (ok && warp == 4 && lane == 0 && !*abort_flag) {
       tma_store_3d(&tmO, sQ, 0, head, q0);
       tma_store_3d(&tmO, sQ + HALF_BYTES, 64, head, q0);
       tma_store_commit();
@@ -338,6 +364,18 @@ extern "C" void ody_flash_fwd_set_trace(long long* buf) { g_fwd_trace = buf; }
 extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H,
                              int Hkv, int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal,
                              float scale, int* err, cudaStream_t st) {
+  return ody_flash_fwd_push(q, k, v, o, lse, Tq, Tk, H, Hkv, q_row, k_row, v_row, o_row, causal, scale, nullptr, err, st);
+}
+
+extern "C" int ody_flash_set_peer_wait_limit(long long cycles) {
+  if (cycles <= 0) return (int)cudaErrorInvalidValue;
+  return (int)cudaMemcpyToSymbol(ody::gc::g_peer_spin_limit, &cycles, sizeof(cycles));
+}
+
+// Same kernel; when `push` is given, CTAs 0..push->n_cta-1 also deliver push->shard to the destinations it names.
+extern "C" int ody_flash_fwd_push(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H,
+                                  int Hkv, int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal,
+                                  float scale, const OdyGatherDesc* push, int* err, cudaStream_t st) {
   using namespace ody;
   using namespace ody::fwd;
   if (Tq <= 0 || Tk <= 0 || H <= 0 || Hkv <= 0 || H % Hkv) return (int)cudaErrorInvalidValue;
@@ -346,7 +384,8 @@ extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* 
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -357,6 +396,19 @@ extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* 
   if ((r = make_tmap_3d_bf16(&tV, v, HD, Hkv, Tk, HD * 2, v_row * 2, 64, 1, BN))) return 750000 + r;
   if ((r = make_tmap_3d_bf16(&tO, o, HD, H, Tq, HD * 2, o_row * 2, 64, 1, BM))) return 760000 + r;
   dim3 grid((Tq + BM - 1) / BM, H);
-  flash_fwd_kernel<<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, g_fwd_trace);
+  if (push != nullptr) {
+    gc::GatherParams pp;
+    memset(&pp, 0, sizeof(pp));
+    if ((r = gc::fill_gather(pp, push))) return r;
+    const int ctas = (int)(grid.x * grid.y);
+    if (push->n_cta <= 0 || push->n_cta > ctas) return (int)cudaErrorInvalidValue;
+    flash_fwd_kernel<true><<<grid, NUM_THREADS_PUSH, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
+                                                                       g_fwd_trace, pp, push->n_cta);
+  } else {
+    gc::GatherParams pp;
+    memset(&pp, 0, sizeof(pp));
+    flash_fwd_kernel<false><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
+                                                                    g_fwd_trace, pp, 0);
+  }
   return (int)cudaGetLastError();
 }

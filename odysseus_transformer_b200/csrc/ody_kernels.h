@@ -79,6 +79,7 @@ typedef struct OdyGatherDesc {
   uint32_t consume_total;/* running total of CTAs that consumed this slot (all uses, the current one included) */
   uint32_t epoch, prev_epoch, uses;
   int which;
+  int dest_first, dest_count; /* push only: destinations rank + dest_first ... (mod n_ranks); dest_count 0 = every rank, own included */
 } OdyGatherDesc;
 typedef struct OdyScatterDesc {
   void* stage_peer[8]; uint32_t* arrived_peer[8]; uint32_t* consumed_peer[8];
@@ -90,6 +91,15 @@ int ody_gemm_comm(const void* A, const void* B, void* C, int M, int N, int K, in
                   int layout, const OdyGatherDesc* gather, const OdyGatherDesc* push, const OdyScatterDesc* scatter, int* err,
                   cudaStream_t stream);
 int ody_push_shard(const OdyGatherDesc* push, int* err, cudaStream_t stream);
+// one-thread kernel: bounded wait until source `src`'s whole shard of the slot's current epoch has arrived here
+int ody_wait_shard(const OdyGatherDesc* slot, int src, int* err, cudaStream_t stream);
+// tell every pusher that this rank has finished reading the slot's current epoch (stream-ordered after the readers)
+int ody_signal_free(const OdyGatherDesc* slot, cudaStream_t stream);
+// attention forward whose comm warps also push a K/V shard to ring peers (push == NULL: plain ody_flash_fwd)
+int ody_flash_fwd_push(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H, int Hkv,
+                       int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal, float scale,
+                       const OdyGatherDesc* push, int* err, cudaStream_t stream);
+int ody_flash_set_peer_wait_limit(long long cycles);
 // bound (SM clock cycles) of every wait inside the fused kernels on the current device; default ~10 s
 int ody_set_peer_wait_limit(long long cycles);
 

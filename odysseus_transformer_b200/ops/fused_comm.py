@@ -52,8 +52,10 @@ def enabled(x, group) -> bool:
 
 
 def ring_enabled(x, group) -> bool:
-    """Ring attention with in-kernel peer K/V pulls; not provided yet, the all-gather composition runs."""
-    return False
+    """Ring attention whose attention kernels carry the K/V exchange (``ring_attn_fwd`` below): packed
+    ``[Tb, heads, 128]`` input with Tb a multiple of 128 and a heap for the ring group."""
+    return (enabled(x, group) and x.dim() == 3 and x.shape[-1] == 128 and x.shape[0] % 128 == 0
+            and native.has_native_attention() and native.has_native_attention_bwd())
 
 
 def _lib():
@@ -277,3 +279,121 @@ class _FusedZero3Linear(Function):
 
 def zero3_linear(x: torch.Tensor, w_shard: torch.Tensor, group, sched=None, idx: int = 0) -> torch.Tensor:
     return _FusedZero3Linear.apply(x, w_shard, group, sched, idx)
+
+
+# ----------------------------------------------------------------------------- zigzag ring attention
+
+
+def _kv_shard(k: torch.Tensor, v: torch.Tensor) -> Optional[torch.Tensor]:
+    """The rows ``[k heads | v heads]`` of the packed qkv tensor as one strided [Tb, 2 * hkv * 128] view."""
+    Tb, hkv, hd = k.shape
+    adjacent = (v.data_ptr() == k.data_ptr() + hkv * hd * k.element_size() and k.stride() == v.stride()
+                and k.stride(1) == hd and k.stride(2) == 1 and k.stride(0) >= 2 * hkv * hd)
+    if not adjacent:
+        return None
+    return torch.as_strided(k, (Tb, 2 * hkv * hd), (k.stride(0), 1))
+
+
+def _ring_setup(q, k, v, group):
+    heap = _heaps[id(group)]
+    shard = _kv_shard(k, v)
+    slot = heap.gather_slot(k.shape[0], 2 * k.shape[1] * k.shape[2], tag="ring") if shard is not None else None
+    return heap, shard, slot
+
+
+def ring_attn_fwd(q, k, v, group, scale):
+    """Zigzag ring forward over peer memory -> (out [Tb, H, 128] bf16, lse [H, Tb] fp32).
+
+    The reference's dependency passes K/V blocks hop by hop with batched isend/irecv between attention
+    calls (``zigzag_ring_flash_attn_func``, called at reference ``decoder/ring.py:30-37``).  Here the
+    attention kernel of ring step ``s`` carries comm warps that store this rank's K/V rows straight into
+    the buffer of the rank ``s + 1`` places downstream - the rank whose step ``s + 1`` reads them - so
+    every transfer is hidden behind one step of tensor-core work and crosses NVSwitch exactly once.  A
+    one-thread kernel in front of step ``s`` waits (bounded) for that step's source to have arrived."""
+    from ..parallel import attention as PA
+    heap, shard, slot = _ring_setup(q, k, v, group)
+    if slot is None:
+        stats["fallback"] += 1
+        return PA.ring_attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), group, scale)
+    lib = _lib()
+    R, j = heap.n, heap.rank
+    Tb, hq = q.shape[0], q.shape[1]
+    half = Tb // 2
+    n_push = min(((half + 127) // 128) * hq, heap.sm_count)
+    base = slot.push_desc(shard, n_push)
+    gathered = slot.view().view(R, Tb, 2, k.shape[1], 128)
+
+    def push(step):
+        d = dict(base)
+        d["dest_first"], d["dest_count"] = step + 1, 1
+        return d
+
+    o, lse = lib.attn_fwd_push(q, k, v, True, scale, push(0))
+    out = o.float()
+    for s in range(1, R):
+        src = (j - s) % R
+        lib.wait_shard(base, src)
+        ks, vs = gathered[src, :, 0], gathered[src, :, 1]
+        # zigzag: an earlier source's first chunk precedes both of ours; a later source is seen, whole, by our late chunk only
+        args = (q, ks[:half], vs[:half]) if src < j else (q[half:], ks, vs)
+        if s < R - 1:
+            o, l = lib.attn_fwd_push(*args, False, scale, push(s))
+        else:
+            o, l = lib.attn_fwd(*args, False, scale)
+        lib.attn_merge_(out, lse, o, l, 0 if src < j else half)
+    lib.signal_free(base)
+    stats["ring"] = stats.get("ring", 0) + 1
+    return out.to(q.dtype), lse
+
+
+def ring_attn_bwd(do, q, k, v, o, lse, group, scale):
+    """Zigzag ring backward -> (dq, dk, dv) with dk/dv summed over the ring for this rank's block.
+
+    K/V are exchanged again (nothing gathered is kept between forward and backward): a push-only launch on
+    a side stream delivers this rank's rows to every peer while the local causal block runs, and each later
+    step waits for its source as in the forward.  dK/dV are accumulated in fp32 per source and
+    reduce-scattered once."""
+    from ..comm import torch_backend as C
+    from ..parallel import attention as PA
+    from . import functional as F
+    heap, shard, slot = _ring_setup(q, k, v, group)
+    if slot is None:
+        stats["fallback"] += 1
+        return PA.ring_attn_bwd(do, q.contiguous(), k.contiguous(), v.contiguous(), o, lse, group, scale)
+    lib = _lib()
+    R, j = heap.n, heap.rank
+    Tb, hkv = k.shape[0], k.shape[1]
+    half = Tb // 2
+    base = slot.push_desc(shard, heap.sm_count)
+    base["dest_first"], base["dest_count"] = 1, R - 1
+    main = torch.cuda.current_stream()
+    side = heap.side_stream()
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        lib.push_shard(base)
+    gathered = slot.view().view(R, Tb, 2, hkv, 128)
+    dkv = torch.zeros((R, 2, Tb, hkv, 128), dtype=torch.float32, device=q.device)
+    dq, dk0, dv0 = F.attn_block_bwd(do, q, k, v, o, lse, True, scale)
+    dq = dq.float()
+    dkv[j, 0] += dk0
+    dkv[j, 1] += dv0
+    do_hi, o_hi, lse_hi = do[half:], o[half:], lse[:, half:].contiguous()
+    for s in range(1, R):
+        src = (j - s) % R
+        lib.wait_shard(base, src)
+        ks, vs = gathered[src, :, 0], gathered[src, :, 1]
+        if src < j:
+            dqs, dks, dvs = F.attn_block_bwd(do, q, ks[:half], vs[:half], o, lse, False, scale)
+            dq += dqs
+            dkv[src, 0, :half] += dks
+            dkv[src, 1, :half] += dvs
+        else:
+            dqs, dks, dvs = F.attn_block_bwd(do_hi, q[half:], ks, vs, o_hi, lse_hi, False, scale)
+            dq[half:] += dqs
+            dkv[src, 0] += dks
+            dkv[src, 1] += dvs
+    lib.signal_free(base)
+    main.wait_stream(side)
+    mine = C.reduce_scatter_rows(dkv, group)[0]
+    stats["ring"] = stats.get("ring", 0) + 1
+    return dq, mine[0], mine[1]

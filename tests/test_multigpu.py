@@ -35,6 +35,12 @@ def test_modes_2gpu(mode, backend):
     _launch(2, mode, "small", 1024, 0, 1, backend)
 
 
+def test_ring_4gpu():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    _launch(4, "ring", "small-gqa", 2048, 0, 1, "fused")
+
+
 @pytest.mark.parametrize("mode", ["odysseus", "ulysses"])
 def test_hybrid_4gpu(mode):
     if torch.cuda.device_count() < 4:
