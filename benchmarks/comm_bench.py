@@ -10,6 +10,8 @@ Cases (Llama-2-7B shapes, bf16; ``tokens`` = global sequence length, sharded on 
   wag_gateup all-gather(W [2*11008/N,4096]) -> GEMM with x [L/N,4096]
   wag_dgrad  all-gather(W) along K -> dgrad GEMM
   wgrad_rs   wgrad GEMM dy^T x -> reduce-scatter of [2*11008, 4096]
+  ring_fwd   zigzag ring attention forward, 32 heads x 128, L/N tokens per rank (gemm_only = the same attention
+  ring_bwd   launches on already-gathered K/V, no exchange); backward includes the fp32 dK/dV reduce-scatter
 
 Each case is timed with CUDA events on the launching stream after warm-up, a 256 MB write between
 iterations, and reduced as the max over ranks.  The roofline is the slower of FLOPs / measured bf16 peak
@@ -141,6 +143,50 @@ def main():
         nccl = timeit(lambda: C.reduce_scatter_rows(F.gemm_tn(dy, x), g))
         gemm = timeit(lambda: F.gemm_tn(dy, x))
         report("wgrad_rs", fused, nccl, gemm, 2.0 * t * d * 2 * i, (n - 1) * (2 * i // n) * d * 2, [2 * i, d, t])
+    if "ring_fwd" in cases or "ring_bwd" in cases:
+        from odysseus_transformer_b200.parallel import attention as PA
+        H, hd = 32, 128
+        sc = hd ** -0.5
+        qkv = rnd(t, 3 * H, hd)
+        q, k, v = qkv[:, :H], qkv[:, H:2 * H], qkv[:, 2 * H:]
+        qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+        fake = rnd(n, 2, t, H, hd)
+        lib, half = native.lib(), t // 2
+        att_flops = 2.0 * L * L * hd * H / n             # causal: 4 L^2 hd H / 2, split over n ranks
+        kv_bytes = (n - 1) * t * 2 * H * hd * 2
+
+        def local_fwd():
+            lib.attn_fwd(qc, kc, vc, True, sc)
+            for s_ in range(1, n):
+                src = (rank - s_) % n
+                if src < rank:
+                    lib.attn_fwd(qc, fake[src, 0, :half], fake[src, 1, :half], False, sc)
+                else:
+                    lib.attn_fwd(qc[half:], fake[src, 0], fake[src, 1], False, sc)
+
+        if "ring_fwd" in cases:
+            fused = timeit(lambda: fused_comm.ring_attn_fwd(q, k, v, g, sc))
+            nccl = timeit(lambda: PA.ring_attn_fwd(qc, kc, vc, g, sc))
+            only = timeit(local_fwd)
+            report("ring_fwd", fused, nccl, only, att_flops, kv_bytes, [t, H, hd])
+        if "ring_bwd" in cases:
+            o, lse = fused_comm.ring_attn_fwd(q, k, v, g, sc)
+            do = rnd(t, H, hd)
+
+            def local_bwd():
+                lib.attn_bwd(do, qc, kc, vc, o, lse, True, sc, None, None, None)
+                lse_hi = lse[:, half:].contiguous()
+                for s_ in range(1, n):
+                    src = (rank - s_) % n
+                    if src < rank:
+                        lib.attn_bwd(do, qc, fake[src, 0, :half], fake[src, 1, :half], o, lse, False, sc, None, None, None)
+                    else:
+                        lib.attn_bwd(do[half:], qc[half:], fake[src, 0], fake[src, 1], o[half:], lse_hi, False, sc, None, None, None)
+
+            fused = timeit(lambda: fused_comm.ring_attn_bwd(do, q, k, v, o, lse, g, sc))
+            nccl = timeit(lambda: PA.ring_attn_bwd(do, qc, kc, vc, o, lse, g, sc))
+            only = timeit(local_bwd)
+            report("ring_bwd", fused, nccl, only, 2.5 * att_flops, 3 * kv_bytes, [t, H, hd])
     native.check_status(dev.index)
     dist.barrier()
     dist.destroy_process_group()

@@ -106,6 +106,43 @@ class ScatterSlot:
                 "reduce_counter": self.reduce_counter}
 
 
+class InboxSlot:
+    """Per-source inboxes ``[n (source), rows, cols]`` that peers fill with their own kernels' output stores
+    (ring attention backward: the dK/dV a rank computes for another rank's keys), with one ``arrived`` epoch
+    word per source and one ``consumed`` epoch word per owner."""
+
+    def __init__(self, heap: "SymmetricHeap", rows: int, cols: int):
+        n = heap.n
+        self.heap, self.rows, self.cols = heap, rows, cols
+        self.buf_off = heap.alloc(n * rows * cols * 2)
+        self.arrived_off = heap.alloc_flags(n)
+        self.consumed_off = heap.alloc_flags(n)
+        self.uses = 0
+
+    def begin(self) -> int:
+        self.uses += 1
+        return self.uses
+
+    def local(self) -> torch.Tensor:
+        return self.heap.view(self.buf_off, (self.heap.n, self.rows, self.cols), torch.bfloat16)
+
+    def on_peer(self, peer: int) -> torch.Tensor:
+        """Rank ``peer``'s inboxes as a tensor over its memory: only for this package's own kernels to store into."""
+        return self.heap.peer_view(peer, self.buf_off, (self.heap.n, self.rows, self.cols), torch.bfloat16)
+
+    def arrived_local(self) -> int:
+        return self.heap.ptr(self.heap.rank, self.arrived_off)
+
+    def consumed_local(self) -> int:
+        return self.heap.ptr(self.heap.rank, self.consumed_off)
+
+    def arrived_ptrs(self) -> List[int]:
+        return [self.heap.ptr(p, self.arrived_off) for p in range(self.heap.n)]
+
+    def consumed_ptrs(self) -> List[int]:
+        return [self.heap.ptr(p, self.consumed_off) for p in range(self.heap.n)]
+
+
 class SymmetricHeap:
     def __init__(self, group, device: torch.device, data_bytes: int):
         import torch.distributed._symmetric_memory as symm_mem
@@ -128,6 +165,8 @@ class SymmetricHeap:
         self._data_top = 0
         self._flag_top = 0
         self._side: Optional[torch.cuda.Stream] = None
+        self._peer_bufs: Dict[int, torch.Tensor] = {}
+        self._inbox: Dict[Tuple[int, int], List[InboxSlot]] = {}
         self._gather: Dict[Tuple[int, int, str], List[GatherSlot]] = {}
         self._scatter: Dict[Tuple[int, int], List[ScatterSlot]] = {}
         self._toggle: Dict[Tuple[str, int, int], int] = {}
@@ -165,6 +204,29 @@ class SymmetricHeap:
             n *= s
         nbytes = n * torch.empty((), dtype=dtype).element_size()
         return self.local[off:off + nbytes].view(dtype).view(*shape)
+
+    def peer_view(self, peer: int, off: int, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A tensor over rank ``peer``'s copy of the heap.  Hand it only to this package's own kernels
+        (plain or TMA stores / non-multicast loads); never to a library op."""
+        if peer == self.rank:
+            return self.view(off, shape, dtype)
+        if peer not in self._peer_bufs:
+            self._peer_bufs[peer] = self.handle.get_buffer(peer, (FLAG_BYTES + self.capacity,), torch.uint8, 0)
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self._peer_bufs[peer][off:off + nbytes].view(dtype).view(*shape)
+
+    def inbox_slot(self, rows: int, cols: int) -> Optional[InboxSlot]:
+        key = (rows, cols)
+        if key not in self._inbox:
+            if cols % 8 or not self.can_hold(self.n * rows * cols * 2):
+                return None
+            self._inbox[key] = [InboxSlot(self, rows, cols), InboxSlot(self, rows, cols)]
+        t = self._toggle.get(("i",) + key, 0)
+        self._toggle[("i",) + key] = t ^ 1
+        return self._inbox[key][t]
 
     def can_hold(self, nbytes: int) -> bool:
         return self._data_top + _round_up(nbytes, ALIGN) * 2 <= self.capacity
@@ -205,7 +267,7 @@ def heap_bytes_estimate(cfg, tokens_per_rank: int, n: int) -> int:
     act = n * tokens_per_rank * d * 2
     weights = (2 * i * d + d * i + cfg.vocab_size * d) * 2
     kv = n * tokens_per_rank * 2 * cfg.num_key_value_heads * cfg.head_dim * 2     # ring attention's gathered K|V
-    return 2 * (2 * act) + 2 * (2 * weights) + 2 * kv + (64 << 20)
+    return 2 * (2 * act) + 2 * (2 * weights) + 4 * kv + (64 << 20)     # kv: gathered K|V and dK|dV inboxes, two of each
 
 
 def setup_fused_comm(ctx, cfg=None, tokens_per_rank: int = 0, data_bytes: int = 0) -> bool:

@@ -238,6 +238,46 @@ void attn_merge_(at::Tensor out, at::Tensor lse, const at::Tensor& o, const at::
   ++g_launches;
 }
 
+// dst [T, C] (row pitch free) += sum of srcs; srcs[i] [rows_i, C] lands on rows begins[i] ..., summed in fp32
+void sum_rows_(at::Tensor dst, const std::vector<at::Tensor>& srcs, const std::vector<int64_t>& begins) {
+  ody_req(dst.is_cuda() && dst.scalar_type() == at::kBFloat16 && dst.dim() == 2 && dst.stride(1) == 1);
+  ody_req(srcs.size() == begins.size() && srcs.size() <= 8);
+  c10::cuda::CUDAGuard guard(dst.device());
+  const void* ptr[8];
+  int64_t ld[8], rows[8];
+  for (size_t i = 0; i < srcs.size(); ++i) {
+    const at::Tensor& t = srcs[i];
+    ody_req(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1 && t.size(1) == dst.size(1));
+    ptr[i] = t.data_ptr(); ld[i] = t.stride(0); rows[i] = t.size(0);
+  }
+  ODY_CHECK(ody_sum_rows(dst.data_ptr(), dst.stride(0), dst.size(0), dst.size(1), ptr, ld, begins.data(), rows, (int)srcs.size(),
+                         cur_stream()), "sum_rows");
+  ++g_launches;
+}
+
+// merge attention partials over disjoint key sets in one pass -> (out [T, H, hd] bf16, lse [H, T] fp32)
+std::vector<at::Tensor> attn_merge_parts(const std::vector<at::Tensor>& os, const std::vector<at::Tensor>& ls,
+                                         const std::vector<int64_t>& begins, int64_t T) {
+  ody_req(!os.empty() && os.size() <= 8 && os.size() == ls.size() && os.size() == begins.size());
+  const int64_t H = os[0].size(1), hd = os[0].size(2);
+  c10::cuda::CUDAGuard guard(os[0].device());
+  const void* op[8];
+  const float* lp[8];
+  int64_t rows[8];
+  for (size_t i = 0; i < os.size(); ++i) {
+    check_bf16(os[i], "o");
+    ody_req(os[i].is_contiguous() && os[i].dim() == 3 && os[i].size(1) == H && os[i].size(2) == hd);
+    ody_req(ls[i].scalar_type() == at::kFloat && ls[i].is_contiguous() && ls[i].size(0) == H && ls[i].size(1) == os[i].size(0));
+    op[i] = os[i].data_ptr(); lp[i] = ls[i].data_ptr<float>(); rows[i] = os[i].size(0);
+  }
+  auto out = at::empty({T, H, hd}, os[0].options());
+  auto lse = at::empty({H, T}, ls[0].options());
+  ODY_CHECK(ody_attn_merge_parts(out.data_ptr(), lse.data_ptr<float>(), T, (int)H, (int)hd, op, lp, begins.data(), rows,
+                                 (int)os.size(), cur_stream()), "attn_merge_parts");
+  ++g_launches;
+  return {out, lse};
+}
+
 // ------------------------------------------------------------------------------------------- status
 int64_t status(int64_t device) {
   at::Tensor t;
@@ -284,6 +324,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_bwd_", &ce_bwd_);
   m.def("adamw_step", &adamw_step);
   m.def("attn_merge_", &attn_merge_);
+  m.def("sum_rows_", &sum_rows_);
+  m.def("attn_merge_parts", &attn_merge_parts);
   m.def("status", &status);
   m.def("clear_status", &clear_status);
   m.def("launch_count", &launch_count);

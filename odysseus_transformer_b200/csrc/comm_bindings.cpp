@@ -116,6 +116,25 @@ void signal_free(const py::dict& slot) {
   ody_count_launches(1);
 }
 
+// epoch words in symmetric memory: base / ptrs are raw device addresses; `like` names the device
+void wait_flags(const at::Tensor& like, int64_t base, int64_t mask, int64_t target) {
+  c10::cuda::CUDAGuard guard(like.device());
+  int rc = ody_wait_flags(reinterpret_cast<const uint32_t*>(base), (uint32_t)mask, (uint32_t)target, ody_status_ptr(like),
+                          at::cuda::getCurrentCUDAStream().stream());
+  req(rc == 0, "wait_flags failed with code " + std::to_string(rc));
+  ody_count_launches(1);
+}
+
+void signal_flags(const at::Tensor& like, const std::vector<int64_t>& ptrs, int64_t mask, int64_t index, int64_t value) {
+  c10::cuda::CUDAGuard guard(like.device());
+  req(ptrs.size() >= 1 && ptrs.size() <= 8, "signal_flags: 1..8 ranks");
+  uint32_t* p[8];
+  for (size_t i = 0; i < ptrs.size(); ++i) p[i] = reinterpret_cast<uint32_t*>(ptrs[i]);
+  int rc = ody_signal_flags(p, (int)ptrs.size(), (uint32_t)mask, (int)index, (uint32_t)value, at::cuda::getCurrentCUDAStream().stream());
+  req(rc == 0, "signal_flags failed with code " + std::to_string(rc));
+  ody_count_launches(1);
+}
+
 at::Tensor gemm_comm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& out, int64_t layout,
                      const py::object& gather, const py::object& push, const py::object& scatter) {
   req(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "bf16 CUDA operands");
@@ -193,6 +212,8 @@ void ody_register_comm(pybind11::module& m) {
   m.def("push_shard", &push_shard);
   m.def("attn_fwd_push", &attn_fwd_push);
   m.def("wait_shard", &wait_shard);
+  m.def("wait_flags", &wait_flags);
+  m.def("signal_flags", &signal_flags);
   m.def("signal_free", &signal_free);
   m.def("set_peer_wait_limit", [](int64_t cycles) { req(ody_set_peer_wait_limit(cycles) == 0, "set_peer_wait_limit failed"); });
   m.def("gemm_comm", &gemm_comm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("layout"), py::arg("gather"),

@@ -4,6 +4,8 @@
 // The reference gets these from unfused ATen elementwise kernels inside HF Llama, a Triton loss from
 // flash-attn and torch.optim.AdamW (reference train.py:167,173; decoder/odysseus.py:210-213,293-295).
 // Every kernel here moves 16 bytes per thread per access and touches each operand once.
+#include <string.h>
+
 #include "common.cuh"
 #include "ody_kernels.h"
 
@@ -329,6 +331,86 @@ __global__ void attn_merge_k(float* __restrict__ out, float* __restrict__ lse, c
   if (kv == 0) lse[(int64_t)h * T_total + row0 + t] = ln;
 }
 
+// dst rows [begin_i, begin_i + rows_i) += src_i, summed in fp32 over all sources; dst [T, C] with row pitch dst_ld.
+struct SumRowsArgs {
+  const bf16* src[8];
+  int64_t src_ld[8], begin[8], rows[8];
+  int n;
+};
+__global__ void sum_rows_k(bf16* __restrict__ dst, int64_t dst_ld, int64_t T, int64_t C, const __grid_constant__ SumRowsArgs a) {
+  const int64_t vpr = C >> 3;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * vpr) return;
+  const int64_t t = i / vpr, c = (i % vpr) * 8;
+  bf16x8 part[8];
+  bool on[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    on[k] = k < a.n && t >= a.begin[k] && t < a.begin[k] + a.rows[k];
+    if (on[k]) part[k] = ld8(a.src[k] + (t - a.begin[k]) * a.src_ld[k] + c);
+  }
+  float acc[8];
+  unpack8(ld8(dst + t * dst_ld + c), acc);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (on[k]) {
+      float b[8];
+      unpack8(part[k], b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += b[e];
+    }
+  }
+  st8(dst + t * dst_ld + c, pack8(acc));
+}
+
+// One-pass merge of up to 8 attention partials over disjoint key sets: partial i covers rows
+// [begin_i, begin_i + rows_i) with o_i [rows_i, H, hd] bf16 and lse_i [H, rows_i].  out [T, H, hd] bf16, lse [H, T].
+struct MergeArgs {
+  const bf16* o[8];
+  const float* lse[8];
+  int64_t begin[8], rows[8];
+  int n;
+};
+__global__ void attn_merge_parts_k(bf16* __restrict__ out, float* __restrict__ lse, int64_t T, int H, int hd,
+                                   const __grid_constant__ MergeArgs a) {
+  const int vph = hd >> 3;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * H * vph) return;
+  const int kv = (int)(i % vph);
+  const int h = (int)((i / vph) % H);
+  const int64_t t = i / ((int64_t)vph * H);
+  float l[8], mx = -INFINITY;
+  bf16x8 part[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const bool on = k < a.n && t >= a.begin[k] && t < a.begin[k] + a.rows[k];
+    l[k] = -INFINITY;
+    if (on) {
+      const int64_t tt = t - a.begin[k];
+      l[k] = a.lse[k][(int64_t)h * a.rows[k] + tt];
+      part[k] = ld8(a.o[k] + (tt * H + h) * hd + kv * 8);
+      mx = fmaxf(mx, l[k]);
+    }
+  }
+  float den = 0.f, acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    if (l[k] != -INFINITY) {
+      const float w = __expf(l[k] - mx);
+      den += w;
+      float b[8];
+      unpack8(part[k], b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += w * b[e];
+    }
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] *= inv;
+  st8(out + (t * H + h) * hd + kv * 8, pack8(acc));
+  if (kv == 0) lse[(int64_t)h * T + t] = den > 0.f ? mx + logf(den) : -INFINITY;
+}
+
 }  // namespace ody
 
 // =========================================================================================== launchers
@@ -439,5 +521,35 @@ extern "C" int ody_attn_merge(float* out, float* lse, const void* o, const float
   const int64_t total = T * H * (hd / 8);
   if (total == 0) return 0;
   attn_merge_k<<<blocks_for(total, 256), 256, 0, st>>>(out, lse, (const bf16*)o, l, T, H, hd, row0, T_total);
+  return last_err();
+}
+
+extern "C" int ody_sum_rows(void* dst, int64_t dst_ld, int64_t T, int64_t C, const void* const* src, const int64_t* src_ld,
+                            const int64_t* begin, const int64_t* rows, int n, cudaStream_t st) {
+  if (n < 0 || n > 8 || (C % 8) || (dst_ld % 8) || ((uintptr_t)dst & 15)) return (int)cudaErrorInvalidValue;
+  if (n == 0 || T * C == 0) return 0;
+  SumRowsArgs a;
+  memset(&a, 0, sizeof(a));
+  a.n = n;
+  for (int k = 0; k < n; ++k) {
+    if ((src_ld[k] % 8) || ((uintptr_t)src[k] & 15) || begin[k] < 0 || begin[k] + rows[k] > T) return (int)cudaErrorInvalidValue;
+    a.src[k] = (const bf16*)src[k]; a.src_ld[k] = src_ld[k]; a.begin[k] = begin[k]; a.rows[k] = rows[k];
+  }
+  sum_rows_k<<<blocks_for(T * (C / 8), 256), 256, 0, st>>>((bf16*)dst, dst_ld, T, C, a);
+  return last_err();
+}
+
+extern "C" int ody_attn_merge_parts(void* out, float* lse, int64_t T, int H, int hd, const void* const* o,
+                                    const float* const* l, const int64_t* begin, const int64_t* rows, int n, cudaStream_t st) {
+  if (n < 1 || n > 8 || hd % 8 != 0) return (int)cudaErrorInvalidValue;
+  if (T * H == 0) return 0;
+  MergeArgs a;
+  memset(&a, 0, sizeof(a));
+  a.n = n;
+  for (int k = 0; k < n; ++k) {
+    if (begin[k] < 0 || begin[k] + rows[k] > T || ((uintptr_t)o[k] & 15)) return (int)cudaErrorInvalidValue;
+    a.o[k] = (const bf16*)o[k]; a.lse[k] = l[k]; a.begin[k] = begin[k]; a.rows[k] = rows[k];
+  }
+  attn_merge_parts_k<<<blocks_for(T * H * (hd / 8), 256), 256, 0, st>>>((bf16*)out, lse, T, H, hd, a);
   return last_err();
 }

@@ -599,6 +599,17 @@ __global__ void wait_shard_kernel(const uint32_t* counter, uint32_t target, int*
   abort_flag = 0;
   wait_word<true>(counter, target, &abort_flag, err, ODY_ERR_TIMEOUT_PEER);
 }
+struct PtrList { uint32_t* p[MAX_RANKS]; };
+__global__ void wait_flags_kernel(const uint32_t* base, uint32_t mask, uint32_t target, int* err) {
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) abort_flag = 0;
+  __syncthreads();
+  if ((mask >> threadIdx.x) & 1u) wait_word<true>(base + threadIdx.x, target, &abort_flag, err, ODY_ERR_TIMEOUT_PEER);
+}
+__global__ void signal_flags_kernel(const __grid_constant__ PtrList l, uint32_t mask, int index, uint32_t value) {
+  __threadfence_system();
+  if ((mask >> threadIdx.x) & 1u) st_release_sys(l.p[threadIdx.x] + index, value);
+}
 __global__ void signal_free_kernel(const __grid_constant__ GatherParams g) {
   __threadfence_system();
   if ((int)threadIdx.x < g.n_ranks) st_release_sys(g.free_peer[threadIdx.x] + g.rank, g.epoch);
@@ -610,6 +621,23 @@ extern "C" int ody_wait_shard(const OdyGatherDesc* d, int src, int* err, cudaStr
   using namespace ody::gc;
   if (d == nullptr || src < 0 || src >= d->n_ranks) return (int)cudaErrorInvalidValue;
   wait_shard_kernel<<<1, 1, 0, st>>>(d->counters_peer[d->rank] + src, d->push_total, err);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ody_wait_flags(const uint32_t* base, uint32_t mask, uint32_t target, int* err, cudaStream_t st) {
+  if (base == nullptr) return (int)cudaErrorInvalidValue;
+  if (mask == 0) return 0;
+  ody::gc::wait_flags_kernel<<<1, 32, 0, st>>>(base, mask, target, err);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int ody_signal_flags(uint32_t* const* ptrs, int n, uint32_t mask, int index, uint32_t value, cudaStream_t st) {
+  using namespace ody::gc;
+  if (n < 1 || n > MAX_RANKS || (mask >> n) != 0 || index < 0) return (int)cudaErrorInvalidValue;
+  if (mask == 0) return 0;
+  PtrList l;
+  for (int p = 0; p < MAX_RANKS; ++p) l.p[p] = p < n ? ptrs[p] : nullptr;
+  signal_flags_kernel<<<1, 32, 0, st>>>(l, mask, index, value);
   return (int)cudaGetLastError();
 }
 

@@ -43,6 +43,13 @@ int ody_adamw(float* master, float* m, float* v, const void* grad, void* param, 
 // ---- merge of two partial attention results (ring attention): out/lse fp32 running, o bf16 / l fp32 partial
 int ody_attn_merge(float* out, float* lse, const void* o, const float* l, int64_t T, int H, int hd, int64_t row0,
                    int64_t T_total, cudaStream_t stream);
+// dst [T, C] bf16 (row pitch dst_ld): rows [begin_i, begin_i + rows_i) += src_i (row pitch src_ld_i), fp32 sum over n <= 8 sources
+int ody_sum_rows(void* dst, int64_t dst_ld, int64_t T, int64_t C, const void* const* src, const int64_t* src_ld,
+                 const int64_t* begin, const int64_t* rows, int n, cudaStream_t stream);
+// one-pass merge of n <= 8 attention partials (o_i [rows_i, H, hd] bf16, lse_i [H, rows_i]) covering rows
+// [begin_i, begin_i + rows_i) of out [T, H, hd] bf16 / lse [H, T]; every row must be covered by at least one partial
+int ody_attn_merge_parts(void* out, float* lse, int64_t T, int H, int hd, const void* const* o, const float* const* l,
+                         const int64_t* begin, const int64_t* rows, int n, cudaStream_t stream);
 
 // ---- bf16 GEMM on tcgen05 (fp32 accumulate in TMEM).  layout 0: C = A[M,K] B[N,K]^T ; 1: C = A[M,K] B[K,N] ;
 // 2: C = A[K,M]^T B[K,N].  ld* are row pitches in elements (multiples of 8).  accumulate: C += result.
@@ -95,6 +102,10 @@ int ody_push_shard(const OdyGatherDesc* push, int* err, cudaStream_t stream);
 int ody_wait_shard(const OdyGatherDesc* slot, int src, int* err, cudaStream_t stream);
 // tell every pusher that this rank has finished reading the slot's current epoch (stream-ordered after the readers)
 int ody_signal_free(const OdyGatherDesc* slot, cudaStream_t stream);
+// n <= 32 threads: thread i with bit i of mask set waits (bounded) until base[i] >= target
+int ody_wait_flags(const uint32_t* base, uint32_t mask, uint32_t target, int* err, cudaStream_t stream);
+// for every p with bit p of mask set: ptrs[p][index] <- value with release at system scope, after a system fence
+int ody_signal_flags(uint32_t* const* ptrs, int n, uint32_t mask, int index, uint32_t value, cudaStream_t stream);
 // attention forward whose comm warps also push a K/V shard to ring peers (push == NULL: plain ody_flash_fwd)
 int ody_flash_fwd_push(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H, int Hkv,
                        int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal, float scale,

@@ -309,7 +309,8 @@ def ring_attn_fwd(q, k, v, group, scale):
     attention kernel of ring step ``s`` carries comm warps that store this rank's K/V rows straight into
     the buffer of the rank ``s + 1`` places downstream - the rank whose step ``s + 1`` reads them - so
     every transfer is hidden behind one step of tensor-core work and crosses NVSwitch exactly once.  A
-    one-thread kernel in front of step ``s`` waits (bounded) for that step's source to have arrived."""
+    one-thread kernel in front of step ``s`` waits (bounded) for that step's source to have arrived.  The
+    R partial results are merged in one pass at the end."""
     from ..parallel import attention as PA
     heap, shard, slot = _ring_setup(q, k, v, group)
     if slot is None:
@@ -319,7 +320,8 @@ def ring_attn_fwd(q, k, v, group, scale):
     R, j = heap.n, heap.rank
     Tb, hq = q.shape[0], q.shape[1]
     half = Tb // 2
-    n_push = min(((half + 127) // 128) * hq, heap.sm_count)
+    # the push is spread over every CTA of the smaller step grid: a CTA's comm warps then finish with its tiles
+    n_push = min(((half + 127) // 128) * hq, 4096)
     base = slot.push_desc(shard, n_push)
     gathered = slot.view().view(R, Tb, 2, k.shape[1], 128)
 
@@ -328,8 +330,8 @@ def ring_attn_fwd(q, k, v, group, scale):
         d["dest_first"], d["dest_count"] = step + 1, 1
         return d
 
-    o, lse = lib.attn_fwd_push(q, k, v, True, scale, push(0))
-    out = o.float()
+    o, l = lib.attn_fwd_push(q, k, v, True, scale, push(0))
+    os_, ls_, begins = [o], [l], [0]
     for s in range(1, R):
         src = (j - s) % R
         lib.wait_shard(base, src)
@@ -340,60 +342,84 @@ def ring_attn_fwd(q, k, v, group, scale):
             o, l = lib.attn_fwd_push(*args, False, scale, push(s))
         else:
             o, l = lib.attn_fwd(*args, False, scale)
-        lib.attn_merge_(out, lse, o, l, 0 if src < j else half)
+        os_.append(o)
+        ls_.append(l)
+        begins.append(0 if src < j else half)
     lib.signal_free(base)
     stats["ring"] = stats.get("ring", 0) + 1
-    return out.to(q.dtype), lse
+    out, lse = lib.attn_merge_parts(os_, ls_, begins, Tb)
+    return out, lse
 
 
-def ring_attn_bwd(do, q, k, v, o, lse, group, scale):
-    """Zigzag ring backward -> (dq, dk, dv) with dk/dv summed over the ring for this rank's block.
+def ring_attn_bwd(do, q, k, v, o, lse, group, scale, dqkv=None):
+    """Zigzag ring backward.  Returns (dq, dk, dv), or fills the packed gradient ``dqkv [Tb, hq + 2 hkv, 128]``
+    when it is given, with dk/dv summed over the ring for this rank's block.
 
     K/V are exchanged again (nothing gathered is kept between forward and backward): a push-only launch on
     a side stream delivers this rank's rows to every peer while the local causal block runs, and each later
-    step waits for its source as in the forward.  dK/dV are accumulated in fp32 per source and
-    reduce-scattered once."""
-    from ..comm import torch_backend as C
+    step waits for its source as in the forward.  The dK/dV that step ``s`` computes belong to the source
+    rank: the backward kernel stores them straight into that rank's inbox over NVLink (its output tensors
+    live in the peer's symmetric memory), an epoch word announces them, and every rank finally adds its R-1
+    inboxes to its own dK/dV in one fp32 pass.  There is no reduce-scatter and no fp32 staging: the
+    reference's dependency sends fp32 dK/dV around the ring R times."""
     from ..parallel import attention as PA
-    from . import functional as F
     heap, shard, slot = _ring_setup(q, k, v, group)
-    if slot is None:
+    Tb, hq, hkv = q.shape[0], q.shape[1], k.shape[1]
+    inbox = heap.inbox_slot(Tb, 2 * hkv * 128) if slot is not None else None
+    if inbox is None:
         stats["fallback"] += 1
-        return PA.ring_attn_bwd(do, q.contiguous(), k.contiguous(), v.contiguous(), o, lse, group, scale)
+        dq, dk, dv = PA.ring_attn_bwd(do, q.contiguous(), k.contiguous(), v.contiguous(), o, lse, group, scale)
+        if dqkv is None:
+            return dq, dk, dv
+        dqkv[:, :hq], dqkv[:, hq:hq + hkv], dqkv[:, hq + hkv:] = dq, dk, dv
+        return None
     lib = _lib()
     R, j = heap.n, heap.rank
-    Tb, hkv = k.shape[0], k.shape[1]
     half = Tb // 2
+    ret = dqkv is None
+    if ret:
+        dqkv = torch.empty((Tb, hq + 2 * hkv, 128), dtype=q.dtype, device=q.device)
     base = slot.push_desc(shard, heap.sm_count)
     base["dest_first"], base["dest_count"] = 1, R - 1
+    epoch = inbox.begin()
     main = torch.cuda.current_stream()
     side = heap.side_stream()
     side.wait_stream(main)
     with torch.cuda.stream(side):
         lib.push_shard(base)
     gathered = slot.view().view(R, Tb, 2, hkv, 128)
-    dkv = torch.zeros((R, 2, Tb, hkv, 128), dtype=torch.float32, device=q.device)
-    dq, dk0, dv0 = F.attn_block_bwd(do, q, k, v, o, lse, True, scale)
-    dq = dq.float()
-    dkv[j, 0] += dk0
-    dkv[j, 1] += dv0
+    lib.attn_bwd(do, q, k, v, o, lse, True, scale, dqkv[:, :hq], dqkv[:, hq:hq + hkv], dqkv[:, hq + hkv:])
     do_hi, o_hi, lse_hi = do[half:], o[half:], lse[:, half:].contiguous()
+    dq_parts, dq_begins = [], []
     for s in range(1, R):
         src = (j - s) % R
         lib.wait_shard(base, src)
+        # the owner must have folded the previous contents of our inbox there into its gradient
+        lib.wait_flags(heap.local, inbox.consumed_local(), 1 << src, epoch - 1)
         ks, vs = gathered[src, :, 0], gathered[src, :, 1]
+        mine_there = inbox.on_peer(src)[j].view(Tb, 2, hkv, 128)
         if src < j:
-            dqs, dks, dvs = F.attn_block_bwd(do, q, ks[:half], vs[:half], o, lse, False, scale)
-            dq += dqs
-            dkv[src, 0, :half] += dks
-            dkv[src, 1, :half] += dvs
+            dqs = torch.empty((Tb, hq, 128), dtype=q.dtype, device=q.device)
+            lib.attn_bwd(do, q, ks[:half], vs[:half], o, lse, False, scale, dqs, mine_there[:half, 0], mine_there[:half, 1])
+            dq_begins.append(0)
         else:
-            dqs, dks, dvs = F.attn_block_bwd(do_hi, q[half:], ks, vs, o_hi, lse_hi, False, scale)
-            dq[half:] += dqs
-            dkv[src, 0] += dks
-            dkv[src, 1] += dvs
+            dqs = torch.empty((Tb - half, hq, 128), dtype=q.dtype, device=q.device)
+            lib.attn_bwd(do_hi, q[half:], ks, vs, o_hi, lse_hi, False, scale, dqs, mine_there[:, 0], mine_there[:, 1])
+            dq_begins.append(half)
+        lib.signal_flags(heap.local, inbox.arrived_ptrs(), 1 << src, j, epoch)
+        dq_parts.append(dqs.view(dqs.shape[0], hq * 128))
     lib.signal_free(base)
     main.wait_stream(side)
-    mine = C.reduce_scatter_rows(dkv, group)[0]
+    others = ((1 << R) - 1) & ~(1 << j)
+    lib.wait_flags(heap.local, inbox.arrived_local(), others, epoch)
+    flat = dqkv.view(Tb, (hq + 2 * hkv) * 128)
+    lib.sum_rows_(flat[:, :hq * 128], dq_parts, dq_begins)
+    box = inbox.local()
+    # a later ring rank sees only the first chunk of our keys; an earlier one sees all of them
+    parts = [box[i, :half] if i > j else box[i] for i in range(R) if i != j]
+    lib.sum_rows_(flat[:, hq * 128:], parts, [0] * len(parts))
+    lib.signal_flags(heap.local, inbox.consumed_ptrs(), others, j, epoch)
     stats["ring"] = stats.get("ring", 0) + 1
-    return dq, mine[0], mine[1]
+    if ret:
+        return dqkv[:, :hq], dqkv[:, hq:hq + hkv], dqkv[:, hq + hkv:]
+    return None

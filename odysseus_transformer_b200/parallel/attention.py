@@ -236,13 +236,13 @@ class _PackedRopeAttention(Function):
         if C.group_size(ring_group) > 1:
             from ..ops import fused_comm
             if fused_comm.ring_enabled(qkv, ring_group):
-                dq, dk, dv = fused_comm.ring_attn_bwd(do, q, k, v, o, lse, ring_group, scale)
+                fused_comm.ring_attn_bwd(do, q, k, v, o, lse, ring_group, scale, dqkv=dqkv)
             else:
                 dq, dk, dv = ring_attn_bwd(do, q.contiguous(), k.contiguous(), v.contiguous(), o, lse,
                                            ring_group, scale)
-            dqkv[:, :hq] = dq
-            dqkv[:, hq:hq + hkv] = dk
-            dqkv[:, hq + hkv:] = dv
+                dqkv[:, :hq] = dq
+                dqkv[:, hq:hq + hkv] = dk
+                dqkv[:, hq + hkv:] = dv
         elif native.use_native(qkv) and native.has_native_attention_bwd() and hd == 128:
             # the kernel writes dq/dk/dv straight into the packed gradient
             native.lib().attn_bwd(do, q, k, v, o, lse, True, scale,

@@ -173,6 +173,40 @@ def test_attn_merge(lib):
     torch.testing.assert_close(got_o[:row0], out[:row0])
 
 
+def test_attn_merge_parts(lib):
+    """One-pass merge of three partials, two of which cover only part of the rows."""
+    T, H, hd = 96, 3, 128
+    spans = [(0, 96), (0, 48), (48, 48)]
+    os_ = [_rand(n, H, hd) for _, n in spans]
+    ls_ = [torch.randn(H, n, device="cuda") for _, n in spans]
+    got_o, got_l = lib.attn_merge_parts(os_, ls_, [b for b, _ in spans], T)
+    lse = torch.full((H, T), float("-inf"), device="cuda")
+    for (b, n), l in zip(spans, ls_):
+        lse[:, b:b + n] = torch.logaddexp(lse[:, b:b + n], l)
+    want = torch.zeros(T, H, hd, device="cuda")
+    for (b, n), o, l in zip(spans, os_, ls_):
+        want[b:b + n] += o.float() * torch.exp(l - lse[:, b:b + n]).t().unsqueeze(-1)
+    torch.testing.assert_close(got_l, lse, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(got_o.float(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_sum_rows(lib):
+    """Strided destination, sources landing on row sub-ranges, fp32 accumulation."""
+    T, C = 80, 256
+    big = _rand(T, C + 64)
+    dst = big[:, 32:32 + C]
+    srcs = [_rand(T, C), _rand(40, C), _rand(24, C + 8)[:, :C]]
+    begins = [0, 0, 56]
+    want = dst.float().clone()
+    for sct, b in zip(srcs, begins):
+        want[b:b + sct.shape[0]] += sct.float()
+    keep = big.clone()
+    lib.sum_rows_(dst, srcs, begins)
+    torch.testing.assert_close(dst.float(), want, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(big[:, :32], keep[:, :32])
+    torch.testing.assert_close(big[:, 32 + C:], keep[:, 32 + C:])
+
+
 def test_model_step_fused_vs_library():
     """One fwd+bwd of the small model: own kernels vs the torch/cuBLAS/flash path, same weights."""
     from odysseus_transformer_b200.config import get_model_config
