@@ -143,6 +143,59 @@ class InboxSlot:
         return [self.heap.ptr(p, self.consumed_off) for p in range(self.heap.n)]
 
 
+class A2ASlot:
+    """Receive buffer ``[rows, cols]`` of an all-to-all whose senders are kernels (a GEMM epilogue or an
+    attention epilogue storing straight into the destination), with one ``arrived`` word per source and
+    one ``consumed`` epoch word per destination.  GEMM senders count CTAs into ``arrived`` (cumulative
+    target); stream-ordered senders set it to the epoch."""
+
+    def __init__(self, heap: "SymmetricHeap", rows: int, cols: int):
+        n = heap.n
+        self.heap, self.rows, self.cols = heap, rows, cols
+        self.buf_off = heap.alloc(rows * cols * 2)
+        self.arrived_off = heap.alloc_flags(n)
+        self.consumed_off = heap.alloc_flags(n)
+        self.uses = 0
+        self.arrived_total = 0
+        self._dummy = torch.zeros(1, dtype=torch.int32, device=heap.device)
+
+    def local(self) -> torch.Tensor:
+        return self.heap.view(self.buf_off, (self.rows, self.cols), torch.bfloat16)
+
+    def on_peer(self, peer: int) -> torch.Tensor:
+        """Rank ``peer``'s receive buffer: only for this package's own kernels to store into."""
+        return self.heap.peer_view(peer, self.buf_off, (self.rows, self.cols), torch.bfloat16)
+
+    def begin_epoch(self) -> int:
+        self.uses += 1
+        self.arrived_total = self.uses
+        return self.uses
+
+    def gemm_desc(self, a2a_cols: int, row0: int, col0: int, n_cta: int) -> Dict:
+        """Scatter description (mode 2) for ``gemm_comm``: column group ``o`` of the product goes to rank ``o``'s
+        buffer at rows ``row0 + r`` and columns ``col0 + c``; every one of the ``n_cta`` CTAs reports once."""
+        h = self.heap
+        self.uses += 1
+        self.arrived_total += n_cta
+        return {"mode": 2, "n_ranks": h.n, "rank": h.rank, "chunk_rows": 0, "epoch": self.uses, "prev_epoch": self.uses - 1,
+                "uses": self.uses, "arrived_target": self.arrived_total, "out": self.local(),
+                "stage_ptrs": [h.ptr(p, self.buf_off) for p in range(h.n)],
+                "arrived_ptrs": self.arrived_ptrs(), "consumed_ptrs": self.consumed_ptrs(),
+                "reduce_counter": self._dummy, "a2a_cols": a2a_cols, "a2a_ld": self.cols, "a2a_row0": row0, "a2a_col0": col0}
+
+    def arrived_local(self) -> int:
+        return self.heap.ptr(self.heap.rank, self.arrived_off)
+
+    def consumed_local(self) -> int:
+        return self.heap.ptr(self.heap.rank, self.consumed_off)
+
+    def arrived_ptrs(self) -> List[int]:
+        return [self.heap.ptr(p, self.arrived_off) for p in range(self.heap.n)]
+
+    def consumed_ptrs(self) -> List[int]:
+        return [self.heap.ptr(p, self.consumed_off) for p in range(self.heap.n)]
+
+
 class SymmetricHeap:
     def __init__(self, group, device: torch.device, data_bytes: int):
         import torch.distributed._symmetric_memory as symm_mem
@@ -167,6 +220,7 @@ class SymmetricHeap:
         self._side: Optional[torch.cuda.Stream] = None
         self._peer_bufs: Dict[int, torch.Tensor] = {}
         self._inbox: Dict[Tuple[int, int], List[InboxSlot]] = {}
+        self._a2a: Dict[Tuple[int, int, str], List[A2ASlot]] = {}
         self._gather: Dict[Tuple[int, int, str], List[GatherSlot]] = {}
         self._scatter: Dict[Tuple[int, int], List[ScatterSlot]] = {}
         self._toggle: Dict[Tuple[str, int, int], int] = {}
@@ -228,6 +282,16 @@ class SymmetricHeap:
         self._toggle[("i",) + key] = t ^ 1
         return self._inbox[key][t]
 
+    def a2a_slot(self, rows: int, cols: int, tag: str = "") -> Optional[A2ASlot]:
+        key = (rows, cols, tag)
+        if key not in self._a2a:
+            if cols % 64 or not self.can_hold(rows * cols * 2):
+                return None
+            self._a2a[key] = [A2ASlot(self, rows, cols), A2ASlot(self, rows, cols)]
+        t = self._toggle.get(("a",) + key, 0)
+        self._toggle[("a",) + key] = t ^ 1
+        return self._a2a[key][t]
+
     def can_hold(self, nbytes: int) -> bool:
         return self._data_top + _round_up(nbytes, ALIGN) * 2 <= self.capacity
 
@@ -267,7 +331,8 @@ def heap_bytes_estimate(cfg, tokens_per_rank: int, n: int) -> int:
     act = n * tokens_per_rank * d * 2
     weights = (2 * i * d + d * i + cfg.vocab_size * d) * 2
     kv = n * tokens_per_rank * 2 * cfg.num_key_value_heads * cfg.head_dim * 2     # ring attention's gathered K|V
-    return 2 * (2 * act) + 2 * (2 * weights) + 4 * kv + (64 << 20)     # kv: gathered K|V and dK|dV inboxes, two of each
+    a2a = 2 * (2 * (cfg.q_size + 2 * cfg.kv_size) + 2 * cfg.q_size) * tokens_per_rank * 2   # Ulysses receive buffers, two of each
+    return 2 * (2 * act) + 2 * (2 * weights) + 4 * kv + a2a + (64 << 20)     # kv: gathered K|V and dK|dV inboxes, two of each
 
 
 def setup_fused_comm(ctx, cfg=None, tokens_per_rank: int = 0, data_bytes: int = 0) -> bool:

@@ -173,7 +173,15 @@ at::Tensor gemm_comm(const at::Tensor& a, const at::Tensor& b, const c10::option
     sd.prev_epoch = get<uint32_t>(d, "prev_epoch");
     sd.arrived_target = get<uint32_t>(d, "arrived_target");
     sd.uses = get<uint32_t>(d, "uses");
-    req(c.size(0) == sd.chunk_rows && c.size(1) == N && (int64_t)sd.chunk_rows * sd.n_ranks == M, "scatter shapes");
+    sd.mode = d.contains("mode") ? get<int>(d, "mode") : 1;
+    if (sd.mode == 2) {
+      sd.a2a_cols = get<int>(d, "a2a_cols");
+      sd.a2a_ld = get<int64_t>(d, "a2a_ld");
+      sd.a2a_row0 = get<int64_t>(d, "a2a_row0");
+      sd.a2a_col0 = get<int64_t>(d, "a2a_col0");
+    } else {
+      req(c.size(0) == sd.chunk_rows && c.size(1) == N && (int64_t)sd.chunk_rows * sd.n_ranks == M, "scatter shapes");
+    }
     sdp = &sd;
   } else {
     c = out.has_value() ? out.value() : at::empty({M, N}, a.options());

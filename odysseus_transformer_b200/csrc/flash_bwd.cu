@@ -93,12 +93,20 @@ constexpr int KV_SMEM_TILES = 2 * BIG_BYTES + STAGES * (2 * BLK_BYTES + STAT_BYT
 constexpr int KV_SMEM_TOTAL = KV_SMEM_TILES + 256 + 1024;
 // TMEM columns: S^T(b) at b*64, dP^T(b) at 128 + b*64 (P^T / dS^T overwrite their first 32 columns), dV 256, dK 384
 
+// Optional redirection of an output: rows [d * rows, (d + 1) * rows) go to tensor map m[d] instead of the
+// kernel's own output map (another rank's buffer: the Ulysses head->sequence exchange of the gradient).
+struct SplitMaps {
+  CUtensorMap m[8];
+  int rows;     // 0 = unused
+};
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmDO64,
                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                       const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
                       const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad, int Tq, int Tk, int Tq_pad,
-                      int H, int Hkv, int causal, float scale, int* __restrict__ err, long long* __restrict__ dbg) {
+                      int H, int Hkv, int causal, float scale, int* __restrict__ err, long long* __restrict__ dbg,
+                      const __grid_constant__ SplitMaps dk_split, const __grid_constant__ SplitMaps dv_split) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -296,10 +304,14 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     tc_fence_before();
     named_barrier(1, 256);
     if (ok && warp == 2 && lane == 0 && !*abort_flag) {
-      tma_store_3d(&tmDV, sV, 0, kvh, kv0);
-      tma_store_3d(&tmDV, sV + BIG_HALF, 64, kvh, kv0);
-      tma_store_3d(&tmDK, sK, 0, kvh, kv0);
-      tma_store_3d(&tmDK, sK + BIG_HALF, 64, kvh, kv0);
+      const int d = dk_split.rows > 0 ? kv0 / dk_split.rows : 0;
+      const int row = dk_split.rows > 0 ? kv0 - d * dk_split.rows : kv0;
+      const CUtensorMap* mV = dk_split.rows > 0 ? &dv_split.m[d] : &tmDV;
+      const CUtensorMap* mK = dk_split.rows > 0 ? &dk_split.m[d] : &tmDK;
+      tma_store_3d(mV, sV, 0, kvh, row);
+      tma_store_3d(mV, sV + BIG_HALF, 64, kvh, row);
+      tma_store_3d(mK, sK, 0, kvh, row);
+      tma_store_3d(mK, sK + BIG_HALF, 64, kvh, row);
       tma_store_commit();
       tma_store_wait<0>();
     }
@@ -327,7 +339,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
                     const __grid_constant__ CUtensorMap tmDQ, const float* __restrict__ lse2_pad,
                     const float* __restrict__ delta_pad, int Tq, int Tk, int Tq_pad, int H, int Hkv, int causal,
-                    float scale, int* __restrict__ err) {
+                    float scale, int* __restrict__ err, const __grid_constant__ SplitMaps dq_split) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -495,8 +507,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tc_fence_before();
     named_barrier(1, 256);
     if (ok && warp == 2 && lane == 0 && !*abort_flag) {
-      tma_store_3d(&tmDQ, sQ, 0, head, q0);
-      tma_store_3d(&tmDQ, sQ + BIG_HALF, 64, head, q0);
+      const int d = dq_split.rows > 0 ? q0 / dq_split.rows : 0;
+      const int row = dq_split.rows > 0 ? q0 - d * dq_split.rows : q0;
+      const CUtensorMap* mQ = dq_split.rows > 0 ? &dq_split.m[d] : &tmDQ;
+      tma_store_3d(mQ, sQ, 0, head, row);
+      tma_store_3d(mQ, sQ + BIG_HALF, 64, head, row);
       tma_store_commit();
       tma_store_wait<0>();
     }
@@ -523,8 +538,39 @@ extern "C" int ody_flash_bwd(const void* dO, const void* q, const void* k, const
                              void* dq, void* dk, void* dv, void* workspace, int Tq, int Tk, int H, int Hkv, int64_t do_row,
                              int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int64_t dq_row, int64_t dk_row,
                              int64_t dv_row, int causal, float scale, int* err, cudaStream_t st) {
+  return ody_flash_bwd_ex(dO, q, k, v, o, lse, dq, dk, dv, workspace, Tq, Tk, H, Hkv, do_row, q_row, k_row, v_row, o_row, dq_row,
+                          dk_row, dv_row, causal, scale, nullptr, nullptr, nullptr, 0, 0, err, st);
+}
+
+// Full form.  With n_split > 0 the gradients are not written to dq/dk/dv (which may then be null) but split by
+// rows: rows [d * split_rows, (d + 1) * split_rows) of dq go to dq_split[d] ([split_rows, H, 128]), of dk / dv to
+// dk_split[d] / dv_split[d] ([split_rows, Hkv, 128]); all with row pitches dq_row / dk_row / dv_row and possibly in
+// peer memory.  split_rows % 128 == 0 and Tq == Tk.
+extern "C" int ody_flash_bwd_ex(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                                void* dq, void* dk, void* dv, void* workspace, int Tq, int Tk, int H, int Hkv, int64_t do_row,
+                                int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int64_t dq_row, int64_t dk_row,
+                                int64_t dv_row, int causal, float scale, void* const* dq_split, void* const* dk_split,
+                                void* const* dv_split, int n_split, int split_rows, int* err, cudaStream_t st) {
   using namespace ody;
   using namespace ody::bwd;
+  SplitMaps sq, sk, sv;
+  memset(&sq, 0, sizeof(sq));
+  memset(&sk, 0, sizeof(sk));
+  memset(&sv, 0, sizeof(sv));
+  if (n_split > 0) {
+    if (n_split > 8 || split_rows <= 0 || (split_rows % BIG) || Tq != Tk || (int64_t)split_rows * n_split < Tq) return (int)cudaErrorInvalidValue;
+    if ((dq_row | dk_row | dv_row) % 8) return (int)cudaErrorInvalidValue;
+    for (int d = 0; d < n_split; ++d) {
+      if (((uintptr_t)dq_split[d] | (uintptr_t)dk_split[d] | (uintptr_t)dv_split[d]) & 15) return (int)cudaErrorInvalidValue;
+      int e;
+      if ((e = make_tmap_3d_bf16(&sq.m[d], dq_split[d], HD, H, split_rows, HD * 2, dq_row * 2, 64, 1, BIG))) return 795000 + e;
+      if ((e = make_tmap_3d_bf16(&sk.m[d], dk_split[d], HD, Hkv, split_rows, HD * 2, dk_row * 2, 64, 1, BIG))) return 795000 + e;
+      if ((e = make_tmap_3d_bf16(&sv.m[d], dv_split[d], HD, Hkv, split_rows, HD * 2, dv_row * 2, 64, 1, BIG))) return 795000 + e;
+    }
+    sq.rows = sk.rows = sv.rows = split_rows;
+    // the unsplit maps below still need a valid address
+    dq = dq_split[0]; dk = dk_split[0]; dv = dv_split[0];
+  }
   if (Tq <= 0 || Tk <= 0 || H <= 0 || Hkv <= 0 || H % Hkv) return (int)cudaErrorInvalidValue;
   if (causal && Tq != Tk) return (int)cudaErrorInvalidValue;
   if ((do_row | q_row | k_row | v_row | o_row | dq_row | dk_row | dv_row) % 8) return (int)cudaErrorInvalidValue;
@@ -564,9 +610,9 @@ extern "C" int ody_flash_bwd(const void* dO, const void* q, const void* k, const
   if ((r = make_tmap_3d_bf16(&tDV, dv, HD, Hkv, Tk, HD * 2, dv_row * 2, 64, 1, BIG))) return 790000 + r;
   dim3 gkv((Tk + BIG - 1) / BIG, Hkv);
   flash_bwd_dkdv_kernel<<<gkv, NUM_THREADS, KV_SMEM_TOTAL, st>>>(tQ64, tDO64, tK, tV, tDK, tDV, lse2_pad, delta_pad, Tq, Tk,
-                                                                 Tpad, H, Hkv, causal, scale, err, g_bwd_trace);
+                                                                 Tpad, H, Hkv, causal, scale, err, g_bwd_trace, sk, sv);
   dim3 gq((Tq + BIG - 1) / BIG, H);
   flash_bwd_dq_kernel<<<gq, NUM_THREADS, Q_SMEM_TOTAL, st>>>(tQ, tDO, tK64, tV64, tDQ, lse2_pad, delta_pad, Tq, Tk, Tpad, H,
-                                                             Hkv, causal, scale, err);
+                                                             Hkv, causal, scale, err, sq);
   return (int)cudaGetLastError();
 }

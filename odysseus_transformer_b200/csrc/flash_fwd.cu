@@ -38,6 +38,13 @@ constexpr int NUM_THREADS = 384;
 constexpr int NUM_THREADS_PUSH = NUM_THREADS + gc::COMM_THREADS;
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 
+// Optional second destination of the output: rows [d * rows, (d + 1) * rows) also go to tensor map m[d]
+// (another rank's buffer: the Ulysses head->sequence exchange happens in this epilogue).
+struct SplitMaps {
+  CUtensorMap m[8];
+  int rows;     // 0 = unused
+};
+
 struct Bars {
   uint64_t q_full;
   uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
@@ -74,7 +81,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                  float* __restrict__ lse, int Tq, int Tk, int H, int Hkv, int causal, float scale,
                  int* __restrict__ err, long long* __restrict__ dbg, const __grid_constant__ gc::GatherParams pp,
-                 int push_ctas) {
+                 int push_ctas, const __grid_constant__ SplitMaps osplit) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -340,6 +347,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (ok && warp == 4 && lane == 0 && !*abort_flag) {
       tma_store_3d(&tmO, sQ, 0, head, q0);
       tma_store_3d(&tmO, sQ + HALF_BYTES, 64, head, q0);
+      if (osplit.rows > 0) {
+        const int d = q0 / osplit.rows;
+        tma_store_3d(&osplit.m[d], sQ, 0, head, q0 - d * osplit.rows);
+        tma_store_3d(&osplit.m[d], sQ + HALF_BYTES, 64, head, q0 - d * osplit.rows);
+      }
       tma_store_commit();
       tma_store_wait<0>();
     }
@@ -364,7 +376,8 @@ extern "C" void ody_flash_fwd_set_trace(long long* buf) { g_fwd_trace = buf; }
 extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H,
                              int Hkv, int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal,
                              float scale, int* err, cudaStream_t st) {
-  return ody_flash_fwd_push(q, k, v, o, lse, Tq, Tk, H, Hkv, q_row, k_row, v_row, o_row, causal, scale, nullptr, err, st);
+  return ody_flash_fwd_ex(q, k, v, o, lse, Tq, Tk, H, Hkv, q_row, k_row, v_row, o_row, causal, scale, nullptr, nullptr, 0, 0, 0,
+                          err, st);
 }
 
 extern "C" int ody_flash_set_peer_wait_limit(long long cycles) {
@@ -376,6 +389,15 @@ extern "C" int ody_flash_set_peer_wait_limit(long long cycles) {
 extern "C" int ody_flash_fwd_push(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H,
                                   int Hkv, int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal,
                                   float scale, const OdyGatherDesc* push, int* err, cudaStream_t st) {
+  return ody_flash_fwd_ex(q, k, v, o, lse, Tq, Tk, H, Hkv, q_row, k_row, v_row, o_row, causal, scale, push, nullptr, 0, 0, 0, err, st);
+}
+
+// Full form: optional push (ring) and optional split of the output rows over n_split extra destinations
+// o_split[d] ([split_rows, H, 128], row pitch split_row elements; may be peer memory), split_rows % 128 == 0.
+extern "C" int ody_flash_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H,
+                                int Hkv, int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal, float scale,
+                                const OdyGatherDesc* push, void* const* o_split, int n_split, int split_rows,
+                                int64_t split_row, int* err, cudaStream_t st) {
   using namespace ody;
   using namespace ody::fwd;
   if (Tq <= 0 || Tk <= 0 || H <= 0 || Hkv <= 0 || H % Hkv) return (int)cudaErrorInvalidValue;
@@ -395,6 +417,16 @@ extern "C" int ody_flash_fwd_push(const void* q, const void* k, const void* v, v
   if ((r = make_tmap_3d_bf16(&tK, k, HD, Hkv, Tk, HD * 2, k_row * 2, 64, 1, BN))) return 740000 + r;
   if ((r = make_tmap_3d_bf16(&tV, v, HD, Hkv, Tk, HD * 2, v_row * 2, 64, 1, BN))) return 750000 + r;
   if ((r = make_tmap_3d_bf16(&tO, o, HD, H, Tq, HD * 2, o_row * 2, 64, 1, BM))) return 760000 + r;
+  SplitMaps sm;
+  memset(&sm, 0, sizeof(sm));
+  if (n_split > 0) {
+    if (n_split > 8 || split_rows <= 0 || (split_rows % BM) || (int64_t)split_rows * n_split < Tq || (split_row % 8)) return (int)cudaErrorInvalidValue;
+    for (int d = 0; d < n_split; ++d) {
+      if ((uintptr_t)o_split[d] & 15) return (int)cudaErrorInvalidValue;
+      if ((r = make_tmap_3d_bf16(&sm.m[d], o_split[d], HD, H, split_rows, HD * 2, split_row * 2, 64, 1, BM))) return 770000 + r;
+    }
+    sm.rows = split_rows;
+  }
   dim3 grid((Tq + BM - 1) / BM, H);
   if (push != nullptr) {
     gc::GatherParams pp;
@@ -403,12 +435,12 @@ extern "C" int ody_flash_fwd_push(const void* q, const void* k, const void* v, v
     const int ctas = (int)(grid.x * grid.y);
     if (push->n_cta <= 0 || push->n_cta > ctas) return (int)cudaErrorInvalidValue;
     flash_fwd_kernel<true><<<grid, NUM_THREADS_PUSH, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
-                                                                       g_fwd_trace, pp, push->n_cta);
+                                                                       g_fwd_trace, pp, push->n_cta, sm);
   } else {
     gc::GatherParams pp;
     memset(&pp, 0, sizeof(pp));
     flash_fwd_kernel<false><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
-                                                                    g_fwd_trace, pp, 0);
+                                                                    g_fwd_trace, pp, 0, sm);
   }
   return (int)cudaGetLastError();
 }

@@ -52,6 +52,10 @@ struct ScatterParams {
   uint32_t epoch, prev_epoch;
   uint32_t arrived_target;                // cumulative: GEMM CTAs of each source * uses
   uint32_t reduce_target;                 // cumulative: n_gemm CTAs * uses
+  // SCATTER == 2 (all-to-all on columns): columns [o * a2a_cols, (o + 1) * a2a_cols) of row r go to rank o's buffer
+  // stage_peer[o] at row a2a_row0 + r, column a2a_col0 + (c - o * a2a_cols), row pitch a2a_ld
+  int a2a_cols;
+  int64_t a2a_ld, a2a_row0, a2a_col0;
 };
 
 struct Bars {
@@ -137,7 +141,9 @@ __global__ void __launch_bounds__(COMM_THREADS) push_shard_kernel(const __grid_c
 
 // ------------------------------------------------------------------------------------------- kernel
 // GATHER: 0 none, 1 operand A is gathered, 2 operand B is gathered.  SCATTER: 0 plain TMA-store epilogue,
-// 1 push rows to their owner and reduce own rows.
+// 1 push rows to their owner and reduce own rows, 2 all-to-all: push column groups to their owner (the
+// Ulysses sequence<->head exchange, yunchang SeqAllToAll4D called at reference decoder/ulysses.py:40-47;
+// the receivers wait on the per-source counters with ody_wait_flags).
 template <int LAYOUT, int GATHER, int SCATTER>
 __global__ void __launch_bounds__(NUM_THREADS + COMM_THREADS, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -174,7 +180,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (G_ROWS_M) shift_m = (int)(((int64_t)gp.rank * gp.chunk_rows) / BM) % tiles_m;
   if (G_ROWS_N) shift_n = (int)(((int64_t)gp.rank * gp.chunk_rows) / BN) % tiles_n;
   if (G_ROWS_K) shift_k = (int)(((int64_t)gp.rank * gp.chunk_rows) / BK) % kblocks;
-  if (SCATTER) shift_m = (int)((((int64_t)(sp.rank + 1) * sp.chunk_rows + BM - 1) / BM) % tiles_m);   // others' rows first
+  if (SCATTER == 1) shift_m = (int)((((int64_t)(sp.rank + 1) * sp.chunk_rows + BM - 1) / BM) % tiles_m);   // others' rows first
 
   if (warp == 1) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
   tc_fence_before();
@@ -287,7 +293,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t verified = 0;                            // owners whose staging slot is known to be free
     bool alive = true;
     int remaining[MAX_RANKS];                         // tiles this CTA still has to push to each owner (store_thread only)
-    if (SCATTER && store_thread) {
+    if (SCATTER == 1 && store_thread) {
 #pragma unroll
       for (int o = 0; o < MAX_RANKS; ++o) remaining[o] = 0;
       for (int tile = gemm_idx; tile < num_tiles; tile += n_gemm) {
@@ -312,7 +318,13 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = mbar_wait(&bars->tmem_full[buf], acc_phase, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL);
       // rows this thread pushes in the coalesced copy phase: (et / 8) + 16 * i, 16-byte chunk et % 8
       __nv_bfloat16* push_rows[8];
-      if (SCATTER) {
+      if (SCATTER == 2) {
+        // every destination must have consumed what its buffer held before (checked once per CTA)
+        if (verified == 0 && et < sp.n_ranks && et != sp.rank)
+          ok = wait_word<true>(sp.consumed_local + et, sp.prev_epoch, abort_flag, err, ODY_ERR_TIMEOUT_PEER) && ok;
+        verified = 1;
+      }
+      if (SCATTER == 1) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int row = m0 + (et >> 3) + 16 * i;
@@ -357,7 +369,19 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           named_barrier(1, 128);
           // 8 consecutive threads write one 128-byte row segment: full lines on the wire
           const int j = et & 7;
-          if (col0 + j * 8 < N) {
+          if (SCATTER == 2) {
+            if (col0 < N) {
+              const int owner = col0 / sp.a2a_cols;
+              __nv_bfloat16* base = sp.stage_peer[owner] + sp.a2a_col0 + (col0 - owner * sp.a2a_cols) + j * 8;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int rr = (et >> 3) + 16 * i;
+                if (m0 + rr < M)
+                  *reinterpret_cast<uint4*>(base + (sp.a2a_row0 + m0 + rr) * sp.a2a_ld) =
+                      *reinterpret_cast<const uint4*>(sbuf + rr * 128 + ((j ^ (rr & 7)) << 4));
+              }
+            }
+          } else if (col0 + j * 8 < N) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const int rr = (et >> 3) + 16 * i;
@@ -381,7 +405,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (store_thread && col0 < N) { tma_store_2d(&tmC, sbuf, col0, m0); tma_store_commit(); }
         }
       }
-      if (SCATTER) {
+      if (SCATTER == 1) {
         // Every row of this tile is on its way.  When it was this CTA's last tile for an owner, one thread
         // fences at system scope (the barrier makes the other threads' stores part of what it releases) and
         // tells that owner that this CTA is done with it.
@@ -402,6 +426,13 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     if (!SCATTER) {
       if (store_thread) tma_store_wait<0>();
+    } else if (SCATTER == 2) {
+      // all of this CTA's column groups are on their way: one fence, then tell every destination
+      named_barrier(1, 128);
+      if (store_thread && alive) {
+        __threadfence_system();
+        for (int o = 0; o < sp.n_ranks; ++o) red_release_sys_add(sp.arrived_peer[o] + sp.rank, 1);
+      }
     } else if (alive) {
       // reduce this rank's rows over the N source slots once every source has delivered all its tiles
       bool ok = true;
@@ -532,7 +563,12 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
     }
   }
   if (SCATTER) {
-    if (sd == nullptr || sd->n_ranks < 2 || sd->n_ranks > MAX_RANKS || sd->chunk_rows * sd->n_ranks != M) return (int)cudaErrorInvalidValue;
+    if (sd == nullptr || sd->n_ranks < 2 || sd->n_ranks > MAX_RANKS) return (int)cudaErrorInvalidValue;
+    if (SCATTER == 1 && sd->chunk_rows * sd->n_ranks != M) return (int)cudaErrorInvalidValue;
+    if (SCATTER == 2 && (sd->a2a_cols <= 0 || (sd->a2a_cols % 64) || (int64_t)sd->a2a_cols * sd->n_ranks != N || (sd->a2a_ld % 8) ||
+                         (sd->a2a_col0 % 8) || sd->a2a_row0 < 0))
+      return (int)cudaErrorInvalidValue;
+    sp.a2a_cols = sd->a2a_cols; sp.a2a_ld = sd->a2a_ld; sp.a2a_row0 = sd->a2a_row0; sp.a2a_col0 = sd->a2a_col0;
     for (int p = 0; p < sd->n_ranks; ++p) {
       sp.stage_peer[p] = (__nv_bfloat16*)sd->stage_peer[p];
       sp.arrived_peer[p] = sd->arrived_peer[p];
@@ -549,7 +585,7 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
     ldc = N;
     C = sd->stage_peer[sd->rank];
   }
-  if ((r = make_tmap_2d_bf16(&tC, C, (uint64_t)N, (uint64_t)(SCATTER ? sd->chunk_rows : M), (uint64_t)ldc * 2, EPI_COLS, BM))) return 720000 + r;
+  if ((r = make_tmap_2d_bf16(&tC, C, (uint64_t)N, (uint64_t)(SCATTER == 1 ? sd->chunk_rows : M), (uint64_t)ldc * 2, EPI_COLS, BM))) return 720000 + r;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int n_gemm = g_sms;
   if (tiles < n_gemm) n_gemm = tiles;
@@ -571,11 +607,12 @@ extern "C" int ody_gemm_comm(const void* A, const void* B, void* C, int M, int N
   using namespace ody::gc;
   if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (N % 8)) return (int)cudaErrorInvalidValue;
   const int g = gd ? gd->which : 0;
-  const int s = sd ? 1 : 0;
+  const int s = sd ? (sd->mode == 2 ? 2 : 1) : 0;
 #define ODY_CASE(L, G, S) \
   if (layout == L && g == G && s == S) return launch<L, G, S>(A, B, C, M, N, K, lda, ldb, ldc, gd, pd, sd, err, st);
   ODY_CASE(0, 1, 0) ODY_CASE(0, 2, 0) ODY_CASE(1, 1, 0) ODY_CASE(1, 2, 0) ODY_CASE(2, 2, 0) ODY_CASE(2, 1, 0)
   ODY_CASE(0, 0, 1) ODY_CASE(1, 0, 1) ODY_CASE(2, 0, 1)
+  ODY_CASE(0, 2, 2) ODY_CASE(1, 2, 2)
 #undef ODY_CASE
   return (int)cudaErrorInvalidValue;
 }

@@ -72,6 +72,13 @@ int ody_flash_bwd(const void* dO, const void* q, const void* k, const void* v, c
                   void* dk, void* dv, void* workspace, int Tq, int Tk, int H, int Hkv, int64_t do_row, int64_t q_row,
                   int64_t k_row, int64_t v_row, int64_t o_row, int64_t dq_row, int64_t dk_row, int64_t dv_row, int causal,
                   float scale, int* err, cudaStream_t stream);
+// full form: with n_split > 0 the gradients go, split by rows of split_rows (a multiple of 128), to dq_split[d] /
+// dk_split[d] / dv_split[d] (possibly peer memory; row pitches dq_row / dk_row / dv_row) instead of dq / dk / dv
+int ody_flash_bwd_ex(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,
+                     void* dk, void* dv, void* workspace, int Tq, int Tk, int H, int Hkv, int64_t do_row, int64_t q_row,
+                     int64_t k_row, int64_t v_row, int64_t o_row, int64_t dq_row, int64_t dk_row, int64_t dv_row, int causal,
+                     float scale, void* const* dq_split, void* const* dk_split, void* const* dv_split, int n_split,
+                     int split_rows, int* err, cudaStream_t stream);
 
 // ---- GEMM fused with an all-gather of one operand and/or a reduce-scatter of the result over peer memory
 // (gemm_comm.cu).  Descriptions are plain data; pointers in *_peer[p] address rank p's symmetric memory.
@@ -93,6 +100,9 @@ typedef struct OdyScatterDesc {
   uint32_t* reduce_counter; void* out; int64_t out_ld;
   int n_ranks, rank, chunk_rows;
   uint32_t epoch, prev_epoch, arrived_target, uses;
+  /* mode 2 = all-to-all on columns (no reduction): column group o of row r -> stage_peer[o][(a2a_row0 + r) * a2a_ld + a2a_col0 + c'] */
+  int mode, a2a_cols;
+  int64_t a2a_ld, a2a_row0, a2a_col0;
 } OdyScatterDesc;
 int ody_gemm_comm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                   int layout, const OdyGatherDesc* gather, const OdyGatherDesc* push, const OdyScatterDesc* scatter, int* err,
@@ -110,6 +120,12 @@ int ody_signal_flags(uint32_t* const* ptrs, int n, uint32_t mask, int index, uin
 int ody_flash_fwd_push(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H, int Hkv,
                        int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal, float scale,
                        const OdyGatherDesc* push, int* err, cudaStream_t stream);
+// full form: optional push, and optional extra destinations for the output rows (Ulysses head->sequence exchange):
+// rows [d * split_rows, (d + 1) * split_rows) are also stored to o_split[d] ([split_rows, H, 128], row pitch split_row)
+int ody_flash_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H, int Hkv,
+                     int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal, float scale,
+                     const OdyGatherDesc* push, void* const* o_split, int n_split, int split_rows, int64_t split_row, int* err,
+                     cudaStream_t stream);
 int ody_flash_set_peer_wait_limit(long long cycles);
 // bound (SM clock cycles) of every wait inside the fused kernels on the current device; default ~10 s
 int ody_set_peer_wait_limit(long long cycles);

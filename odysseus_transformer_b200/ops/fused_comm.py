@@ -78,12 +78,14 @@ def _push_only(heap, shard: torch.Tensor):
 
 
 def _gather_gemm(heap, shard: torch.Tensor, which: int, other: torch.Tensor, layout: int,
-                 out: Optional[torch.Tensor] = None, slot=None, prefetch: Optional[torch.Tensor] = None):
+                 out: Optional[torch.Tensor] = None, slot=None, prefetch: Optional[torch.Tensor] = None, scatter=None):
     """GEMM whose operand ``which`` (1 = A, 2 = B) is the all-gather of ``shard``.
 
     ``slot``: the gathered buffer when an earlier launch already delivered ``shard`` (prefetch), else the
     comm warps of THIS launch deliver it.  ``prefetch``: another shard for this launch's comm warps to
     deliver when they have nothing else to do (only possible when ``slot`` was given).
+    ``scatter``: an all-to-all description (``comm.symm.A2ASlot.gemm_desc``) for the epilogue; the result
+    is then the local receive buffer, complete only after a wait on the slot's arrival words.
     Returns (result, gathered view, slot holding the prefetched shard or None); result None = unsupported."""
     shard = shard if shard.stride(-1) == 1 else shard.contiguous()
     pushed = slot is not None
@@ -107,7 +109,7 @@ def _gather_gemm(heap, shard: torch.Tensor, which: int, other: torch.Tensor, lay
         if next_slot is not None:
             push = next_slot.push_desc(prefetch, n_cta)
             stats["prefetch"] = stats.get("prefetch", 0) + 1
-    y = _lib().gemm_comm(a, b, out, layout, slot.consume_desc(which, n_cta), push, None)
+    y = _lib().gemm_comm(a, b, out, layout, slot.consume_desc(which, n_cta), push, scatter)
     return y, g, next_slot
 
 
@@ -264,17 +266,24 @@ class _FusedZero3Linear(Function):
                 sched._fused_prefetched[nxt] = nslot
             if dx is None:
                 dx = F.gemm_nn(dy, C.all_gather_rows(w.detach(), group))
-        mg = getattr(w, "main_grad", None)
-        fresh = mg is not None and not getattr(w, "_grad_written", False)
-        n = heap.n
-        dw = _scatter_gemm(heap, dy, x, 2, n * w.shape[0], w.shape[1], out=mg if fresh else None)
-        if dw is None:
-            dw = C.reduce_scatter_rows(F.gemm_tn(dy, x), group)
-            return dx, F.deliver_grad(w, dw), None, None, None
-        if fresh:
-            w._grad_written = True
-            return dx, None, None, None, None
-        return dx, F.deliver_grad(w, dw), None, None, None
+        return dx, zero3_wgrad(heap, group, w, dy, x), None, None, None
+
+
+def zero3_wgrad(heap, group, w, dy, x):
+    """Weight gradient of a ZeRO-3 linear: wgrad GEMM -> reduce-scatter in one kernel, written straight into
+    ``w.main_grad`` when that is fresh.  Returns what autograd should receive for ``w``."""
+    from ..comm import torch_backend as C
+    from ..ops import functional as F
+    mg = getattr(w, "main_grad", None)
+    fresh = mg is not None and not getattr(w, "_grad_written", False)
+    dw = _scatter_gemm(heap, dy, x, 2, heap.n * w.shape[0], w.shape[1], out=mg if fresh else None)
+    if dw is None:
+        dw = C.reduce_scatter_rows(F.gemm_tn(dy, x), group)
+        return F.deliver_grad(w, dw)
+    if fresh:
+        w._grad_written = True
+        return None
+    return F.deliver_grad(w, dw)
 
 
 def zero3_linear(x: torch.Tensor, w_shard: torch.Tensor, group, sched=None, idx: int = 0) -> torch.Tensor:

@@ -1,0 +1,158 @@
+"""DeepSpeed-Ulysses attention block whose four all-to-alls live inside the producing kernels (sm_100a).
+
+The reference runs the sequence<->head exchange as separate ``all_to_all_single`` calls with
+transposes and ``contiguous()`` copies around them (``yunchang`` ``SeqAllToAll4D``, called at reference
+``decoder/ulysses.py:40-47``; four exchanges forward, four backward).  Here every exchange is the
+epilogue of the kernel that produces the data, storing straight into the destination rank's receive
+buffer over NVLink:
+
+=========================  ==========================================================================
+exchange                   producer kernel
+=========================  ==========================================================================
+forward  q,k,v seq->head   QKV projection GEMM (ZeRO-3 weight gather fused as well): ``gemm_comm``
+                           with the all-to-all epilogue - column group ``u`` of a tile goes to rank ``u``
+forward  o head->seq       attention forward: each CTA's output tile is stored to the rank owning those rows
+backward do seq->head      output-projection dgrad GEMM with the all-to-all epilogue
+backward dq,dk,dv          attention backward kernels store each gradient tile to the rank owning the rows
+=========================  ==========================================================================
+
+Receivers wait (bounded, one small kernel) on per-source arrival words before the consumer kernel
+is launched, and tell the senders through ``consumed`` epoch words when a buffer may be overwritten.
+One autograd function covers the whole block, so no gradient ever exists in a layout autograd would
+have to understand.  Requirements: bf16, head_dim 128, local tokens a multiple of 128, ring degree 1,
+symmetric heaps for the weight group and the exchange group; otherwise ``available`` is False and the
+module runs the torch.distributed composition.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from . import fused_comm as FC
+from . import native
+
+
+def available(mod, x: torch.Tensor) -> bool:
+    pc = mod.pctx
+    if pc.inner_size < 2 or pc.ring_size > 1 or mod.head_dim != 128 or x.shape[0] % 128:
+        return False
+    if not (FC.enabled(x, pc.inner_group) and FC.enabled(x, pc.world_group)):
+        return False
+    return native.has_native_attention() and native.has_native_attention_bwd()
+
+
+def _need(v, what: str):
+    if v is None:
+        raise RuntimeError(f"fused Ulysses block: symmetric heap exhausted while allocating {what}; "
+                           "give comm.symm.setup_fused_comm a larger data_bytes")
+    return v
+
+
+def _gather_w(heap, sched, idx, step, w, other, layout, scatter=None):
+    """ZeRO-3 weight gather fused with its GEMM (operand B), riding the prefetch chain of ``sched``."""
+    slot, nxt_w, nxt = FC._chain(sched, heap, idx, step, w)
+    y, _, nslot = FC._gather_gemm(heap, w, 2, other, layout, slot=slot, prefetch=nxt_w, scatter=scatter)
+    if nslot is not None:
+        sched._fused_prefetched[nxt] = nslot
+    return _need(y, "a weight gather buffer")
+
+
+class _FusedUlyssesAttention(Function):
+    @staticmethod
+    def forward(ctx, x, wqkv, wo, cos, sin, mod):
+        from ..parallel.attention import _rope_inplace_
+        lib = native.lib()
+        pc = mod.pctx
+        heap_w, heap_a = FC.heap_for(pc.world_group), FC.heap_for(pc.inner_group)
+        U, r = heap_a.n, heap_a.rank
+        t, hq, hkv = x.shape[0], mod.hq, mod.hkv
+        nh = hq + 2 * hkv
+        G, Tb = nh * 128, U * t
+        everyone = (1 << U) - 1
+        sched, iq, io = mod.qkv_proj.sched, mod.qkv_proj.idx, mod.o_proj.idx
+        x = x.contiguous()
+        flag_dev = heap_a.local
+
+        # 1. QKV projection; the epilogue scatters head group u to rank u (rows r*t.. of its [Tb, G] buffer)
+        s_qkv = _need(heap_a.a2a_slot(Tb, G, "qkv"), "the q/k/v receive buffer")
+        desc = s_qkv.gemm_desc(G, r * t, 0, FC._n_cta(heap_w, t, U * G))
+        _gather_w(heap_w, sched, iq, +1, wqkv.detach(), x, 0, scatter=desc)
+        lib.wait_flags(flag_dev, s_qkv.arrived_local(), everyone, s_qkv.arrived_total)
+        qkv = s_qkv.local().clone()                     # kept for backward; the buffer is free again at once
+        lib.signal_flags(flag_dev, s_qkv.consumed_ptrs(), everyone, r, s_qkv.uses)
+        qkv3 = qkv.view(Tb, nh, 128)
+        _rope_inplace_(qkv3, hq + hkv, cos, sin, False)
+        q, k, v = qkv3[:, :hq], qkv3[:, hq:hq + hkv], qkv3[:, hq + hkv:]
+
+        # 2. attention; each output tile also goes to the rank that owns its rows (columns of head group r there)
+        s_o = _need(heap_a.a2a_slot(t, U * hq * 128, "o"), "the attention-output receive buffer")
+        e_o = s_o.begin_epoch()
+        lib.wait_flags(flag_dev, s_o.consumed_local(), everyone, e_o - 1)
+        dests = [s_o.on_peer(p).view(t, U, hq, 128)[:, r] for p in range(U)]
+        o, lse = lib.attn_fwd_split(q, k, v, True, mod.head_dim ** -0.5, dests)
+        lib.signal_flags(flag_dev, s_o.arrived_ptrs(), everyone, r, e_o)
+        lib.wait_flags(flag_dev, s_o.arrived_local(), everyone, e_o)
+        o_seq = s_o.local().clone()                     # [t, H * 128], kept for the o_proj wgrad
+        lib.signal_flags(flag_dev, s_o.consumed_ptrs(), everyone, r, e_o)
+
+        # 3. output projection (ZeRO-3 weight gather fused)
+        y = _gather_w(heap_w, sched, io, +1, wo.detach(), o_seq, 0)
+        ctx.save_for_backward(x, wqkv, wo, cos, sin, qkv, o, lse, o_seq)
+        ctx.mod = mod
+        FC.stats["ulysses"] = FC.stats.get("ulysses", 0) + 1
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..parallel.attention import _rope_inplace_
+        x, wqkv, wo, cos, sin, qkv, o, lse, o_seq = ctx.saved_tensors
+        mod = ctx.mod
+        lib = native.lib()
+        pc = mod.pctx
+        heap_w, heap_a = FC.heap_for(pc.world_group), FC.heap_for(pc.inner_group)
+        U, r = heap_a.n, heap_a.rank
+        t, hq, hkv = x.shape[0], mod.hq, mod.hkv
+        nh = hq + 2 * hkv
+        G, Tb = nh * 128, U * t
+        everyone = (1 << U) - 1
+        sched, iq, io = mod.qkv_proj.sched, mod.qkv_proj.idx, mod.o_proj.idx
+        flag_dev = heap_a.local
+        dy = dy.contiguous()
+
+        # 1. o_proj dgrad; the epilogue scatters the columns of head group u to rank u: dO arrives as [Tb, hq * 128]
+        s_do = _need(heap_a.a2a_slot(Tb, hq * 128, "do"), "the dO receive buffer")
+        desc = s_do.gemm_desc(hq * 128, r * t, 0, FC._n_cta(heap_w, t, U * hq * 128))
+        _gather_w(heap_w, sched, io, -1, wo.detach(), dy, 1, scatter=desc)
+        g_wo = FC.zero3_wgrad(heap_w, pc.world_group, wo, dy, o_seq)
+        lib.wait_flags(flag_dev, s_do.arrived_local(), everyone, s_do.arrived_total)
+        do = s_do.local().view(Tb, hq, 128)
+
+        # 2. attention backward; gradient tiles go to the rank owning the rows, landing packed as [t, U * G]
+        s_dqkv = _need(heap_a.a2a_slot(t, U * G, "dqkv"), "the dq/dk/dv receive buffer")
+        e = s_dqkv.begin_epoch()
+        lib.wait_flags(flag_dev, s_dqkv.consumed_local(), everyone, e - 1)
+        qkv3 = qkv.view(Tb, nh, 128)
+        q, k, v = qkv3[:, :hq], qkv3[:, hq:hq + hkv], qkv3[:, hq + hkv:]
+        there = [s_dqkv.on_peer(p).view(t, U, nh, 128)[:, r] for p in range(U)]
+        lib.attn_bwd_split(do, q, k, v, o, lse, True, mod.head_dim ** -0.5, [d[:, :hq] for d in there],
+                           [d[:, hq:hq + hkv] for d in there], [d[:, hq + hkv:] for d in there])
+        lib.signal_flags(flag_dev, s_do.consumed_ptrs(), everyone, r, s_do.uses)
+        lib.signal_flags(flag_dev, s_dqkv.arrived_ptrs(), everyone, r, e)
+        lib.wait_flags(flag_dev, s_dqkv.arrived_local(), everyone, e)
+        dqkv = s_dqkv.local()
+        # inverse rotation of the dq / dk heads of every head group, at this rank's own token positions
+        cos_l, sin_l = cos[r * t:(r + 1) * t], sin[r * t:(r + 1) * t]
+        by_group = dqkv.view(t, U, nh, 128)
+        for u in range(U):
+            _rope_inplace_(by_group[:, u], hq + hkv, cos_l, sin_l, True)
+
+        # 3. QKV projection backward, reading the receive buffer in place
+        dx = _gather_w(heap_w, sched, iq, -1, wqkv.detach(), dqkv, 1)
+        g_wqkv = FC.zero3_wgrad(heap_w, pc.world_group, wqkv, dqkv, x)
+        lib.signal_flags(flag_dev, s_dqkv.consumed_ptrs(), everyone, r, e)
+        return dx, g_wqkv, g_wo, None, None, None
+
+
+def attention_block(mod, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """``SequenceParallelAttention.forward`` on the fused path: x [t, d] local tokens -> [t, d]."""
+    return _FusedUlyssesAttention.apply(x, mod.qkv_proj.weight, mod.o_proj.weight, cos, sin, mod)

@@ -35,6 +35,11 @@ class SequenceParallelAttention(nn.Module):
         """x [t, d] local tokens; cos/sin for the positions of this rank's ring block [U*t, hd/2]."""
         U, hd = self.pctx.inner_size, self.head_dim
         t = x.shape[0]
+        if U > 1 and x.is_cuda:
+            from ..ops import fused_ulysses
+            if fused_ulysses.available(self, x):
+                # all four sequence<->head exchanges happen inside the GEMM / attention kernels
+                return fused_ulysses.attention_block(self, x, cos, sin)
         qkv = self.qkv_proj(x)                                                   # [t, U*(hq+2hkv)*hd]
         qkv = seq_to_head(qkv.view(t, U * (self.hq + 2 * self.hkv), hd), self.pctx.inner_group)
         o = packed_rope_attention(qkv.reshape(U * t, -1), cos, sin, self.hq, self.hkv, self.pctx.ring_group)

@@ -63,6 +63,10 @@ def main():
         if backend == "fused" and fused_comm.stats["gather"] + fused_comm.stats["scatter"] == 0:
             print("fused backend requested but no fused collective kernel ran", flush=True)
             ok = False
+        if backend == "fused" and mode == "ulysses" and ctx.ring_size == 1 and cfg.head_dim == 128 and L // world % 128 == 0 \
+                and fused_comm.stats.get("ulysses", 0) == 0:
+            print("fused backend requested but the Ulysses exchanges ran as separate all-to-alls", flush=True)
+            ok = False
         if backend == "fused" and ctx.ring_size > 1 and cfg.head_dim == 128 and fused_comm.stats.get("ring", 0) == 0:
             print("fused backend requested but ring attention ran the all-gather composition", flush=True)
             ok = False
