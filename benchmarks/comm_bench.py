@@ -10,6 +10,8 @@ Cases (Llama-2-7B shapes, bf16; ``tokens`` = global sequence length, sharded on 
   wag_gateup all-gather(W [2*11008/N,4096]) -> GEMM with x [L/N,4096]
   wag_dgrad  all-gather(W) along K -> dgrad GEMM
   wgrad_rs   wgrad GEMM dy^T x -> reduce-scatter of [2*11008, 4096]
+  ulysses_block  one Ulysses attention block (QKV projection, exchanges, attention, output projection; ZeRO-3
+             weights) forward + backward: exchanges inside the kernels vs separate NCCL all-to-alls
   ring_fwd   zigzag ring attention forward, 32 heads x 128, L/N tokens per rank (gemm_only = the same attention
   ring_bwd   launches on already-gathered K/V, no exchange); backward includes the fp32 dK/dV reduce-scatter
 
@@ -143,6 +145,36 @@ def main():
         nccl = timeit(lambda: C.reduce_scatter_rows(F.gemm_tn(dy, x), g))
         gemm = timeit(lambda: F.gemm_tn(dy, x))
         report("wgrad_rs", fused, nccl, gemm, 2.0 * t * d * 2 * i, (n - 1) * (2 * i // n) * d * 2, [2 * i, d, t])
+    if "ulysses_block" in cases:
+        from odysseus_transformer_b200.ops import fused_ulysses
+        from odysseus_transformer_b200.parallel.linear import Zero3Schedule
+        from odysseus_transformer_b200.parallel.ulysses import SequenceParallelAttention
+        sched = Zero3Schedule()
+        blk = SequenceParallelAttention(cfg, ctx, sched, 0, dtype=torch.bfloat16, device=dev)
+        for p_ in blk.parameters():
+            torch.nn.init.normal_(p_, std=0.02)
+        xb = rnd(t, d).requires_grad_(True)
+        cos = torch.randn(L, 64, device=dev)
+        sin = torch.randn(L, 64, device=dev)
+        dyb = rnd(t, d)
+
+        def step():
+            for p_ in blk.parameters():
+                p_.grad = None
+            xb.grad = None
+            blk(xb, cos, sin).backward(dyb)
+
+        assert fused_ulysses.available(blk, xb), "fused Ulysses block unavailable for this shape"
+        fused = timeit(step)
+        keep = fused_ulysses.available
+        fused_ulysses.available = lambda *_: False
+        nccl = timeit(step)
+        fused_ulysses.available = keep
+        # projections 4 * 2 t d^2 (fwd) * 3 (fwd + dgrad + wgrad), attention causal 3.5 * 4 L^2 hd H / 2 / n
+        fl = 3 * 8.0 * t * d * d + 3.5 * 2.0 * L * L * 128 * 32 / n
+        a2a_bytes = (n - 1) / n * t * (3 * d + d) * 2 * 2
+        w_bytes = (n - 1) / n * 4 * d * d * 2 * 3
+        report("ulysses_block", fused, nccl, 0.0, fl, a2a_bytes + w_bytes, [t, d, n])
     if "ring_fwd" in cases or "ring_bwd" in cases:
         from odysseus_transformer_b200.parallel import attention as PA
         H, hd = 32, 128

@@ -4,15 +4,19 @@
 // decoder/odysseus.py:256-263; its ring dependency calls the same kernel per block).  Here it is three
 // kernels built on tcgen05 / TMEM / TMA:
 //
-//   prep   : delta[h,t] = sum_d dO*O, and LSE converted to the exp2 domain, both padded to 64 rows.
-//   dkdv   : one CTA per (128-row KV tile, kv head).  K and V stay in shared memory; 64-row blocks of Q
-//            and dO stream through a TMA ring.  S^T = K Q^T and dP^T = V dO^T land in TMEM (double
-//            buffered, kv rows on lanes), eight warps (two per lane quarter, 32 columns each) turn them into
-//            P^T and dS^T (bf16, written back over
-//            the same TMEM columns) and the tensor core accumulates dV += P^T dO, dK += dS^T Q in TMEM
-//            (2*64 + 2*64 + 128 + 128 = 512 columns).  Query heads sharing the kv head are looped inside.
-//   dq     : one CTA per (128-row query tile, head).  Q and dO stay in shared memory; 64-row blocks of K
-//            and V stream.  S = Q K^T, dP = dO V^T, dS (bf16 in TMEM) and dQ += dS K.
+//   prep   : -delta[h,t] = -sum_d dO*O, and -LSE in the exp2 domain (negated so the kernels can fuse them into packed
+//            fma / add instructions), both padded to 128 rows.
+//   dkdv   : one CTA per (128-row KV tile, kv head).  K and V stay in shared memory; 128-row blocks of Q
+//            and dO stream through two TMA rings.  S^T = K Q^T and dP^T = V dO^T land in TMEM (kv rows on
+//            lanes), eight warps (two per lane quarter, 64 columns each) turn them into P^T and dS^T (bf16,
+//            written back over the same TMEM columns) and the tensor core accumulates dV += P^T dO,
+//            dK += dS^T Q in TMEM (128 + 128 + 128 + 128 = 512 columns).  Every tcgen05.mma is 128x128x16:
+//            a single thread issues one instruction per ~80 cycles whatever its shape, so 64-wide blocks
+//            would leave the tensor core half idle.  S^T / dP^T are single buffered; the issue order
+//            dV(i), S^T(i+1), dK(i), dP^T(i+1) keeps the in-order tensor pipe busy while the softmax warps
+//            work on the other matrix.  Query heads sharing the kv head are looped inside.
+//   dq     : one CTA per (128-row query tile, head).  Q and dO stay in shared memory; 128-row blocks of K
+//            and V stream.  S = Q K^T, dP = dO V^T (double buffered), dS (bf16 in TMEM) and dQ += dS K.
 //
 // Splitting dQ from dK/dV recomputes S and dP once more but needs no atomics and is deterministic.
 // Gradients are written with TMA stores through row-pitched tensor maps, so dq/dk/dv may be slices
@@ -20,26 +24,35 @@
 #include "ody_kernels.h"
 #include "sm100.cuh"
 
+// Of every ODY_BWD_POLY_DEN column pairs, the first ODY_BWD_POLY_NUM take their exponentials on the FMA pipe
+// (exp2_poly2) instead of the special-function unit.  Measured on B200: any mix is a few percent slower than
+// all-MUFU - the softmax warps are bound by the latency of their dependent chains, not by either pipe - so it is off.
+#ifndef ODY_BWD_POLY_NUM
+#define ODY_BWD_POLY_NUM 0
+#define ODY_BWD_POLY_DEN 2
+#endif
+
 namespace ody {
 namespace bwd {
 
 constexpr int HD = 128;
 constexpr int BIG = 128;                         // resident tile rows
-constexpr int BLK = 64;                          // streamed block rows
+constexpr int BLK = 128;                         // streamed block rows
 constexpr int BIG_BYTES = BIG * HD * 2;          // 32 KB (two halves of [128 x 128 B])
 constexpr int BIG_HALF = BIG_BYTES / 2;
-constexpr int BLK_BYTES = BLK * HD * 2;          // 16 KB (two halves of [64 x 128 B])
+constexpr int BLK_BYTES = BLK * HD * 2;          // 32 KB (two halves of [128 x 128 B])
 constexpr int BLK_HALF = BLK_BYTES / 2;
-constexpr int STAGES = 3;
-constexpr int STAT_BYTES = 2 * BLK * 4;          // lse2 + delta of one 64-row block
-constexpr int NUM_THREADS = 320;             // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quarter)
+constexpr int STAGES = 2;
+constexpr int STAT_BYTES = 2 * BLK * 4;          // lse2 + delta of one streamed block
+// warps 0..3: TMA producer, MMA issuer, two idle (they complete the warpgroup whose registers are given away);
+// warps 4..11: softmax / epilogue, two per TMEM lane quarter
+constexpr int NUM_THREADS = 384;
+// Register split by setmaxnreg.  A CTA of 384 threads is launched with 168 registers per thread (65536 / 384,
+// rounded down to a multiple of 8); the split must fit inside THAT allocation or the increase never returns.
+constexpr int REGS_LAUNCH = 168, REGS_ISSUE = 72, REGS_MATH = 216;
+static_assert(128 * REGS_ISSUE + 256 * REGS_MATH <= NUM_THREADS * REGS_LAUNCH, "setmaxnreg split exceeds the CTA's registers");
 constexpr float LOG2E = 1.4426950408889634f;
 
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
@@ -51,7 +64,7 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
 }
 
 // ------------------------------------------------------------------------------------------- prep
-// delta_pad / lse2_pad: [H, Tpad] fp32, Tpad multiple of 64; rows >= T are zero.
+// delta_pad / lse2_pad: [H, Tpad] fp32 holding -delta and -lse * log2(e); Tpad multiple of 128; rows >= T are zero.
 __global__ void prep_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
                             const float* __restrict__ lse, float* __restrict__ delta_pad, float* __restrict__ lse2_pad,
                             int T, int Tpad, int H, int64_t do_row, int64_t o_row) {
@@ -75,23 +88,25 @@ __global__ void prep_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfl
     l2 = lse[(int64_t)h * T + t] * LOG2E;
   }
   if (lane == 0) {
-    delta_pad[(int64_t)h * Tpad + t] = s;
-    lse2_pad[(int64_t)h * Tpad + t] = l2;
+    delta_pad[(int64_t)h * Tpad + t] = -s;
+    lse2_pad[(int64_t)h * Tpad + t] = -l2;
   }
 }
 
 // ------------------------------------------------------------------------------------------- dK / dV
 struct BarsKV {
   uint64_t kv_full;
-  uint64_t qd_full[STAGES], qd_empty[STAGES];
-  uint64_t s_full[2], p_full[2];
+  uint64_t q_full[STAGES], q_empty[STAGES];      // Q block + its lse2 / delta rows
+  uint64_t d_full[STAGES], d_empty[STAGES];      // dO block
+  uint64_t s_full, dp_full, p_full, ds_full;     // one completion per block each: parity = block & 1
   uint64_t acc_done, drain;
   uint32_t tmem_base;
   int abort_flag;
 };
 constexpr int KV_SMEM_TILES = 2 * BIG_BYTES + STAGES * (2 * BLK_BYTES + STAT_BYTES);
 constexpr int KV_SMEM_TOTAL = KV_SMEM_TILES + 256 + 1024;
-// TMEM columns: S^T(b) at b*64, dP^T(b) at 128 + b*64 (P^T / dS^T overwrite their first 32 columns), dV 256, dK 384
+// TMEM columns: S^T 0..127 (P^T, bf16, overwrites 0..63), dP^T 128..255 (dS^T overwrites 128..191), dV 256, dK 384
+constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 384;
 
 // Optional redirection of an output: rows [d * rows, (d + 1) * rows) go to tensor map m[d] instead of the
 // kernel's own output map (another rank's buffer: the Ulysses head->sequence exchange of the gradient).
@@ -101,7 +116,7 @@ struct SplitMaps {
 };
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmDO64,
+flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                       const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
                       const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad, int Tq, int Tk, int Tq_pad,
@@ -111,8 +126,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
   uint8_t* sV = smem + BIG_BYTES;
-  uint8_t* sStage = smem + 2 * BIG_BYTES;                 // per stage: Q block | dO block
-  uint8_t* sStat = sStage + STAGES * 2 * BLK_BYTES;       // per stage: lse2[64] | delta[64]
+  uint8_t* sQs = smem + 2 * BIG_BYTES;                    // STAGES Q blocks
+  uint8_t* sDs = sQs + STAGES * BLK_BYTES;                // STAGES dO blocks
+  uint8_t* sStat = sDs + STAGES * BLK_BYTES;              // per stage: lse2[128] | delta[128]
   BarsKV* bars = (BarsKV*)(smem + KV_SMEM_TILES);
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -127,8 +143,14 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->kv_full, 1);
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->qd_full[s], 1); mbar_init(&bars->qd_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&bars->s_full[b], 1); mbar_init(&bars->p_full[b], 256); }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->q_full[s], 1); mbar_init(&bars->q_empty[s], 1);
+      mbar_init(&bars->d_full[s], 1); mbar_init(&bars->d_empty[s], 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->p_full, 256);
+    mbar_init(&bars->ds_full, 256);
     mbar_init(&bars->acc_done, 1);
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
@@ -140,29 +162,34 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 0) {
+  if (warp < 4) {
+   reg_dec<REGS_ISSUE>();
+   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(&bars->kv_full, 2 * BIG_BYTES);
       tma_load_3d(sK, &tmK, 0, kvh, kv0, &bars->kv_full);
       tma_load_3d(sK + BIG_HALF, &tmK, 64, kvh, kv0, &bars->kv_full);
       tma_load_3d(sV, &tmV, 0, kvh, kv0, &bars->kv_full);
       tma_load_3d(sV + BIG_HALF, &tmV, 64, kvh, kv0, &bars->kv_full);
-      int stage = 0; uint32_t phase = 0;
       for (int it = 0; it < total; ++it) {
+        const int stage = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
         const int head = kvh * G + it / per_head;
         const int qrow = (i0 + it % per_head) * BLK;
-        if (!mbar_wait(&bars->qd_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
-        uint8_t* sQ = sStage + stage * 2 * BLK_BYTES;
-        uint8_t* sD = sQ + BLK_BYTES;
+        // the Q ring is released by dK, the dO ring (earlier) by dV
+        if (!mbar_wait(&bars->q_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        uint8_t* sQ = sQs + stage * BLK_BYTES;
         float* st = (float*)(sStat + stage * STAT_BYTES);
-        mbar_expect_tx(&bars->qd_full[stage], 2 * BLK_BYTES + STAT_BYTES);
-        tma_load_3d(sQ, &tmQ64, 0, head, qrow, &bars->qd_full[stage]);
-        tma_load_3d(sQ + BLK_HALF, &tmQ64, 64, head, qrow, &bars->qd_full[stage]);
-        tma_load_3d(sD, &tmDO64, 0, head, qrow, &bars->qd_full[stage]);
-        tma_load_3d(sD + BLK_HALF, &tmDO64, 64, head, qrow, &bars->qd_full[stage]);
-        bulk_load_1d(st, lse2_pad + (int64_t)head * Tq_pad + qrow, BLK * 4, &bars->qd_full[stage]);
-        bulk_load_1d(st + BLK, delta_pad + (int64_t)head * Tq_pad + qrow, BLK * 4, &bars->qd_full[stage]);
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        mbar_expect_tx(&bars->q_full[stage], BLK_BYTES + STAT_BYTES);
+        tma_load_3d(sQ, &tmQ, 0, head, qrow, &bars->q_full[stage]);
+        tma_load_3d(sQ + BLK_HALF, &tmQ, 64, head, qrow, &bars->q_full[stage]);
+        bulk_load_1d(st, lse2_pad + (int64_t)head * Tq_pad + qrow, BLK * 4, &bars->q_full[stage]);
+        bulk_load_1d(st + BLK, delta_pad + (int64_t)head * Tq_pad + qrow, BLK * 4, &bars->q_full[stage]);
+        if (!mbar_wait(&bars->d_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        uint8_t* sD = sDs + stage * BLK_BYTES;
+        mbar_expect_tx(&bars->d_full[stage], BLK_BYTES);
+        tma_load_3d(sD, &tmDO, 0, head, qrow, &bars->d_full[stage]);
+        tma_load_3d(sD + BLK_HALF, &tmDO, 64, head, qrow, &bars->d_full[stage]);
       }
     }
   } else if (warp == 1) {
@@ -171,47 +198,64 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BIG, HD, 0, 1);
       bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
       const uint64_t kdesc0 = make_smem_desc(smem_u32(sK), 16, 1024), vdesc0 = make_smem_desc(smem_u32(sV), 16, 1024);
-      const uint64_t stage_k0 = make_smem_desc(smem_u32(sStage), 16, 1024);            // K-major view of a streamed block
-      const uint64_t stage_mn0 = make_smem_desc(smem_u32(sStage), BLK_HALF, 1024);     // MN-major view (B of dV / dK)
-      int stage = 0; uint32_t phase = 0;          // ring position of the next S/dP issue
-      int stage2 = 0;                             // ring position of the next dV/dK issue
+      const uint64_t q_k0 = make_smem_desc(smem_u32(sQs), 16, 1024), d_k0 = make_smem_desc(smem_u32(sDs), 16, 1024);
+      const uint64_t q_mn0 = make_smem_desc(smem_u32(sQs), BLK_HALF, 1024), d_mn0 = make_smem_desc(smem_u32(sDs), BLK_HALF, 1024);
       const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+      // S^T(it) = K Q^T: waits for the Q block
       auto issue_s = [&](int it) -> bool {
-        if (trace && it < 48) dbg[it * 8 + 0] = clock64();                 // MMA thread starts on S/dP(it)
-        if (!mbar_wait(&bars->qd_full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
-        if (trace && it < 48) dbg[it * 8 + 1] = clock64();                 // Q/dO block landed
+        const int stage = it % STAGES;
+        if (!mbar_wait(&bars->q_full[stage], (it / STAGES) & 1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const int b = it & 1;
-        const uint64_t q0d = desc_advance(stage_k0, stage * 2 * BLK_BYTES), d0d = desc_advance(q0d, BLK_BYTES);
-        // S^T and dP^T alternate so consecutive instructions never accumulate into the same TMEM tile
+        const uint64_t qd = desc_advance(q_k0, stage * BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
-          umma_ss(tmem + b * 64, desc_advance(kdesc0, offA), desc_advance(q0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
-          umma_ss(tmem + 128 + b * 64, desc_advance(vdesc0, offA), desc_advance(d0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
+          const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+          umma_ss(tmem + COL_ST, desc_advance(kdesc0, off), desc_advance(qd, off), IDESC_S, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bars->s_full[b]);
-        if (trace && it < 48) dbg[it * 8 + 2] = clock64();                 // S/dP(it) issued
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        umma_commit(&bars->s_full);
         return true;
       };
-      if (ok && total > 0) ok = issue_s(0);
-      for (int it = 0; it < total && ok; ++it) {
-        if (it + 1 < total && !issue_s(it + 1)) { ok = false; break; }
-        const int b = it & 1;
-        if (!mbar_wait(&bars->p_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-        if (trace && it < 48) dbg[it * 8 + 3] = clock64();                 // MMA thread saw P(it)
+      // dP^T(it) = V dO^T: waits for the dO block
+      auto issue_dp = [&](int it) -> bool {
+        const int stage = it % STAGES;
+        if (!mbar_wait(&bars->d_full[stage], (it / STAGES) & 1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint64_t qmn = desc_advance(stage_mn0, stage2 * 2 * BLK_BYTES), dmn = desc_advance(qmn, BLK_BYTES);
-        const uint32_t acc0 = it > 0 ? 1u : 0u;
+        const uint64_t dd = desc_advance(d_k0, stage * BLK_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk) {   // dV += P^T dO and dK += dS^T Q, alternating
-          umma_ts(tmem + 256, tmem + b * 64 + kk * 8, desc_advance(dmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
-          umma_ts(tmem + 384, tmem + 128 + b * 64 + kk * 8, desc_advance(qmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+          umma_ss(tmem + COL_DPT, desc_advance(vdesc0, off), desc_advance(dd, off), IDESC_S, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bars->qd_empty[stage2]);
-        if (trace && it < 48) dbg[it * 8 + 4] = clock64();                 // dV/dK(it) issued
-        if (++stage2 == STAGES) stage2 = 0;
+        umma_commit(&bars->dp_full);
+        return true;
+      };
+      if (ok && total > 0) ok = issue_s(0) && issue_dp(0);
+      // The tensor pipe executes in issue order, so S^T(it+1) may overwrite P^T(it) once dV(it) has been issued,
+      // and dP^T(it+1) may overwrite dS^T(it) once dK(it) has.  While the softmax warps turn dP^T(it) into
+      // dS^T(it) the pipe runs dV(it) and S^T(it+1); while they turn S^T(it+1) into P^T(it+1) it runs dK(it)
+      // and dP^T(it+1).
+      for (int it = 0; it < total && ok; ++it) {
+        const int stage = it % STAGES;
+        const uint32_t par = it & 1;
+        const uint32_t acc0 = it > 0 ? 1u : 0u;
+        if (trace && it < 48) dbg[it * 8 + 0] = clock64();
+        if (!mbar_wait(&bars->p_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        if (trace && it < 48) dbg[it * 8 + 1] = clock64();                 // P^T(it) seen
+        tc_fence_after();
+        const uint64_t dmn = desc_advance(d_mn0, stage * BLK_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk)      // dV += P^T dO
+          umma_ts(tmem + COL_DV, tmem + COL_ST + kk * 8, desc_advance(dmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        umma_commit(&bars->d_empty[stage]);
+        if (it + 1 < total && !issue_s(it + 1)) { ok = false; break; }
+        if (!mbar_wait(&bars->ds_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t qmn = desc_advance(q_mn0, stage * BLK_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk)      // dK += dS^T Q
+          umma_ts(tmem + COL_DK, tmem + COL_DPT + kk * 8, desc_advance(qmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        umma_commit(&bars->q_empty[stage]);
+        if (it + 1 < total && !issue_dp(it + 1)) { ok = false; break; }
       }
       if (ok) umma_commit(&bars->acc_done);
       else {
@@ -220,59 +264,101 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
       }
     }
+   }
   } else {
+    reg_inc<REGS_MATH>();
     const int q = warp & 3;                               // TMEM lane quarter
-    const int hf = (warp - 2) >> 2;                       // which 32 of the block's 64 query columns this warp handles
+    const int hf = (warp - 4) >> 2;                       // which 64 of the block's 128 query columns this warp handles
     const int r = q * 32 + lane;                          // kv row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const float sl2 = scale * LOG2E;
+    const uint64_t sl2_2 = pk2(sl2, sl2);
     bool ok = true;
-    int stage = 0; uint32_t phase = 0;
     for (int it = 0; it < total; ++it) {
-      const int b = it & 1;
-      const int qrow0 = (i0 + it % per_head) * BLK + hf * 32;
-      const bool strace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64 && it < 48;
-      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
-      if (strace) dbg[it * 8 + 5] = clock64();                             // softmax saw S(it)
-      // s_full implies qd_full[stage] completed earlier (the MMAs consumed it); the stats are in smem
-      const float* st = (const float*)(sStat + stage * STAT_BYTES) + hf * 32;
-      uint32_t sv[32], dp[32];
+      const int stage = it % STAGES;
+      const uint32_t par = it & 1;
+      const int qrow0 = (i0 + it % per_head) * BLK + hf * 64;
+      const bool strace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 128 && it < 48;
+      // ---- part 1: S^T -> P^T
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      // s_full implies q_full[stage] completed earlier (the MMAs consumed the block); its stats are in smem
+      const float* st = (const float*)(sStat + stage * STAT_BYTES) + hf * 64;
+      if (strace) dbg[it * 8 + 2] = clock64();                             // S^T(it) complete
+      uint32_t sv[64];
       if (ok) {
         tc_fence_after();
-        tmem_ld_32x32(tmem + b * 64 + hf * 32 + lane_off, sv);
-        tmem_ld_32x32(tmem + 128 + b * 64 + hf * 32 + lane_off, dp);
+        tmem_ld_32x32(tmem + COL_ST + hf * 64 + lane_off, sv);
+        tmem_ld_32x32(tmem + COL_ST + hf * 64 + 32 + lane_off, sv + 32);
         tmem_ld_wait();
       }
-      // P^T / dS^T are written over the first 32 columns of S^T / dP^T: the other warp of this lane quarter
-      // must have read its inputs before either of us stores; the two also agree here on leaving the loop
+      // P^T is written over the first 64 columns of S^T: the other warp of this lane quarter must have read
+      // its inputs before either of us stores; the two also agree here on leaving the loop
       if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
-      if (strace) dbg[it * 8 + 6] = clock64();                             // loaded + pair barrier
+      if (strace) dbg[it * 8 + 3] = clock64();                             // S^T in registers, pair agreed
       const bool diag = causal && (qrow0 < kv0 + BIG);     // some (q, kv) pairs of this half block are masked
-      uint32_t pp[16], ds[16];
+      {
+        uint32_t pp[32];
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const float4 stl = *reinterpret_cast<const float4*>(st + (c >> 1) * 4);
-        const float4 std_ = *reinterpret_cast<const float4*>(st + BLK + (c >> 1) * 4);
-        const float l0 = (c & 1) ? stl.z : stl.x, l1 = (c & 1) ? stl.w : stl.y;
-        const float d0 = (c & 1) ? std_.z : std_.x, d1 = (c & 1) ? std_.w : std_.y;
-        float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - l0);
-        float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - l1);
-        if (diag) {
-          if (qrow0 + 2 * c < kv0 + r) p0 = 0.f;
-          if (qrow0 + 2 * c + 1 < kv0 + r) p1 = 0.f;
+        for (int c = 0; c < 32; ++c) {
+          // x = s * scale * log2(e) - lse2 for two query columns at once (the stats are stored negated)
+          const uint64_t x2 = fma2(pk2u(sv[2 * c], sv[2 * c + 1]), sl2_2, *reinterpret_cast<const uint64_t*>(st + 2 * c));
+          float p0, p1;
+          if ((c % ODY_BWD_POLY_DEN) < ODY_BWD_POLY_NUM) {
+            exp2_poly2(x2, p0, p1);
+          } else {
+            upk2(x2, p0, p1);
+            p0 = exp2_mufu(p0);
+            p1 = exp2_mufu(p1);
+          }
+          if (diag) {
+            if (qrow0 + 2 * c < kv0 + r) p0 = 0.f;
+            if (qrow0 + 2 * c + 1 < kv0 + r) p1 = 0.f;
+          }
+          sv[2 * c] = __float_as_uint(p0);
+          sv[2 * c + 1] = __float_as_uint(p1);
+          pp[c] = pack_bf16(p0, p1);
         }
-        pp[c] = pack_bf16(p0, p1);
-        ds[c] = pack_bf16(p0 * (__uint_as_float(dp[2 * c]) - d0) * scale, p1 * (__uint_as_float(dp[2 * c + 1]) - d1) * scale);
+        if (dbg != nullptr) {   // tracing only: pin every packed value before the stamp
+          asm volatile("" ::"r"(pp[0]), "r"(pp[1]), "r"(pp[2]), "r"(pp[3]), "r"(pp[4]), "r"(pp[5]), "r"(pp[6]), "r"(pp[7]), "r"(pp[8]), "r"(pp[9]), "r"(pp[10]), "r"(pp[11]), "r"(pp[12]), "r"(pp[13]), "r"(pp[14]), "r"(pp[15]));
+          asm volatile("" ::"r"(pp[16]), "r"(pp[17]), "r"(pp[18]), "r"(pp[19]), "r"(pp[20]), "r"(pp[21]), "r"(pp[22]), "r"(pp[23]), "r"(pp[24]), "r"(pp[25]), "r"(pp[26]), "r"(pp[27]), "r"(pp[28]), "r"(pp[29]), "r"(pp[30]), "r"(pp[31]));
+        }
+        if (strace) dbg[it * 8 + 4] = clock64();                           // P^T computed
+        tmem_st_32x16(tmem + COL_ST + hf * 32 + lane_off, pp);
+        tmem_st_32x16(tmem + COL_ST + hf * 32 + 16 + lane_off, pp + 16);
+        tmem_st_wait();
+        if (strace) dbg[it * 8 + 5] = clock64();                           // P^T stored
+        tc_fence_before();
+        mbar_arrive(&bars->p_full);
       }
-      tmem_st_32x16(tmem + b * 64 + hf * 16 + lane_off, pp);
-      tmem_st_32x16(tmem + 128 + b * 64 + hf * 16 + lane_off, ds);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&bars->p_full[b]);
-      if (strace) dbg[it * 8 + 7] = clock64();                             // P(it) published
-      if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      // ---- part 2: dP^T -> dS^T = P^T * (dP^T - delta) * scale
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->dp_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      uint32_t dp[64];
+      if (ok) {
+        tc_fence_after();
+        tmem_ld_32x32(tmem + COL_DPT + hf * 64 + lane_off, dp);
+        tmem_ld_32x32(tmem + COL_DPT + hf * 64 + 32 + lane_off, dp + 32);
+        tmem_ld_wait();
+      }
+      if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
+      if (strace) dbg[it * 8 + 6] = clock64();                             // dP^T in registers, pair agreed
+      {
+        uint32_t ds[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          // dS = P * (dP - delta); the softmax scale is applied once, to dK, in the epilogue
+          const uint64_t t2 = add2(pk2u(dp[2 * c], dp[2 * c + 1]), *reinterpret_cast<const uint64_t*>(st + BLK + 2 * c));
+          float d0, d1;
+          upk2(mul2(pk2u(sv[2 * c], sv[2 * c + 1]), t2), d0, d1);
+          ds[c] = pack_bf16(d0, d1);
+        }
+        tmem_st_32x16(tmem + COL_DPT + hf * 32 + lane_off, ds);
+        tmem_st_32x16(tmem + COL_DPT + hf * 32 + 16 + lane_off, ds + 16);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->ds_full);
+      }
+      if (strace) dbg[it * 8 + 7] = clock64();
     }
-    (void)phase;
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_done, 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
     if (ok) {
       tc_fence_after();
@@ -281,12 +367,15 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         uint8_t* dst = (which == 0 ? sV : sK) + hf * BIG_HALF;
-        const uint32_t col = (which == 0 ? 256 : 384) + hf * 64;
+        const uint32_t col = (which == 0 ? COL_DV : COL_DK) + hf * 64;
+        const float mult = which == 0 ? 1.f : scale;       // dK = scale * dS^T Q
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[16];
           tmem_ld_32x16(tmem + col + lane_off + c * 16, o);
           tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 16; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * mult);
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             uint4 v4;
@@ -303,7 +392,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
     }
     tc_fence_before();
     named_barrier(1, 256);
-    if (ok && warp == 2 && lane == 0 && !*abort_flag) {
+    if (ok && warp == 4 && lane == 0 && !*abort_flag) {
       const int d = dk_split.rows > 0 ? kv0 / dk_split.rows : 0;
       const int row = dk_split.rows > 0 ? kv0 - d * dk_split.rows : kv0;
       const CUtensorMap* mV = dk_split.rows > 0 ? &dv_split.m[d] : &tmDV;
@@ -324,19 +413,22 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_co
 // ------------------------------------------------------------------------------------------- dQ
 struct BarsQ {
   uint64_t qd_full;
-  uint64_t kv_full[STAGES], kv_empty[STAGES];
-  uint64_t s_full[2], p_full[2];
+  uint64_t k_full[STAGES], k_empty[STAGES];
+  uint64_t v_full[STAGES], v_empty[STAGES];
+  uint64_t s_full, s_free;                       // one completion per block each: parity = block & 1
+  uint64_t dp_full[2], ds_full[2];               // dP / dS are double buffered: parity = (block >> 1) & 1
   uint64_t acc_done, drain;
   uint32_t tmem_base;
   int abort_flag;
 };
 constexpr int Q_SMEM_TILES = 2 * BIG_BYTES + STAGES * 2 * BLK_BYTES;
 constexpr int Q_SMEM_TOTAL = Q_SMEM_TILES + 256 + 1024;
-// TMEM columns: S(b) at b*64 (dS overwrites its first 32 columns), dP(b) at 128 + b*64, dQ at 256
+// TMEM columns: S 0..127, dP(b) at 128 + b * 128 (dS, bf16, overwrites its first 64 columns), dQ 384
+constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 384;
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
-                    const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
+                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const __grid_constant__ CUtensorMap tmDQ, const float* __restrict__ lse2_pad,
                     const float* __restrict__ delta_pad, int Tq, int Tk, int Tq_pad, int H, int Hkv, int causal,
                     float scale, int* __restrict__ err, const __grid_constant__ SplitMaps dq_split) {
@@ -344,7 +436,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sD = smem + BIG_BYTES;
-  uint8_t* sStage = smem + 2 * BIG_BYTES;                 // per stage: K block | V block
+  uint8_t* sKs = smem + 2 * BIG_BYTES;                    // STAGES K blocks
+  uint8_t* sVs = sKs + STAGES * BLK_BYTES;                // STAGES V blocks
   BarsQ* bars = (BarsQ*)(smem + Q_SMEM_TILES);
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -358,8 +451,16 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->qd_full, 1);
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&bars->s_full[b], 1); mbar_init(&bars->p_full[b], 256); }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1);
+    }
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->s_free, 256);
+    mbar_init(&bars->ds_full[0], 256);
+    mbar_init(&bars->ds_full[1], 256);
+    mbar_init(&bars->dp_full[0], 1);
+    mbar_init(&bars->dp_full[1], 1);
     mbar_init(&bars->acc_done, 1);
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
@@ -371,24 +472,28 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 0) {
+  if (warp < 4) {
+   reg_dec<REGS_ISSUE>();
+   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(&bars->qd_full, 2 * BIG_BYTES);
       tma_load_3d(sQ, &tmQ, 0, head, q0, &bars->qd_full);
       tma_load_3d(sQ + BIG_HALF, &tmQ, 64, head, q0, &bars->qd_full);
       tma_load_3d(sD, &tmDO, 0, head, q0, &bars->qd_full);
       tma_load_3d(sD + BIG_HALF, &tmDO, 64, head, q0, &bars->qd_full);
-      int stage = 0; uint32_t phase = 0;
       for (int it = 0; it < total; ++it) {
-        if (!mbar_wait(&bars->kv_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
-        uint8_t* sK = sStage + stage * 2 * BLK_BYTES;
-        uint8_t* sV = sK + BLK_BYTES;
-        mbar_expect_tx(&bars->kv_full[stage], 2 * BLK_BYTES);
-        tma_load_3d(sK, &tmK64, 0, kvh, it * BLK, &bars->kv_full[stage]);
-        tma_load_3d(sK + BLK_HALF, &tmK64, 64, kvh, it * BLK, &bars->kv_full[stage]);
-        tma_load_3d(sV, &tmV64, 0, kvh, it * BLK, &bars->kv_full[stage]);
-        tma_load_3d(sV + BLK_HALF, &tmV64, 64, kvh, it * BLK, &bars->kv_full[stage]);
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        const int stage = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        if (!mbar_wait(&bars->k_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        uint8_t* sK = sKs + stage * BLK_BYTES;
+        mbar_expect_tx(&bars->k_full[stage], BLK_BYTES);
+        tma_load_3d(sK, &tmK, 0, kvh, it * BLK, &bars->k_full[stage]);
+        tma_load_3d(sK + BLK_HALF, &tmK, 64, kvh, it * BLK, &bars->k_full[stage]);
+        if (!mbar_wait(&bars->v_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        uint8_t* sV = sVs + stage * BLK_BYTES;
+        mbar_expect_tx(&bars->v_full[stage], BLK_BYTES);
+        tma_load_3d(sV, &tmV, 0, kvh, it * BLK, &bars->v_full[stage]);
+        tma_load_3d(sV + BLK_HALF, &tmV, 64, kvh, it * BLK, &bars->v_full[stage]);
       }
     }
   } else if (warp == 1) {
@@ -397,38 +502,53 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BIG, HD, 0, 1);
       bool ok = mbar_wait(&bars->qd_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
       const uint64_t qdesc0 = make_smem_desc(smem_u32(sQ), 16, 1024), ddesc0 = make_smem_desc(smem_u32(sD), 16, 1024);
-      const uint64_t stage_k0 = make_smem_desc(smem_u32(sStage), 16, 1024);
-      const uint64_t stage_mn0 = make_smem_desc(smem_u32(sStage), BLK_HALF, 1024);
-      int stage = 0; uint32_t phase = 0;
-      int stage2 = 0;
-      auto issue_s = [&](int it) -> bool {
-        if (!mbar_wait(&bars->kv_full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
+      const uint64_t k_k0 = make_smem_desc(smem_u32(sKs), 16, 1024), v_k0 = make_smem_desc(smem_u32(sVs), 16, 1024);
+      const uint64_t k_mn0 = make_smem_desc(smem_u32(sKs), BLK_HALF, 1024);
+      // S(it) = Q K^T into the single S tile, dP(it) = dO V^T into dP buffer it & 1
+      auto issue_s_dp = [&](int it) -> bool {
+        const int stage = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        if (!mbar_wait(&bars->k_full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const int b = it & 1;
-        const uint64_t k0d = desc_advance(stage_k0, stage * 2 * BLK_BYTES), v0d = desc_advance(k0d, BLK_BYTES);
+        const uint64_t kd = desc_advance(k_k0, stage * BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t offA = (kk >> 2) * BIG_HALF + (kk & 3) * 32, offB = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
-          umma_ss(tmem + b * 64, desc_advance(qdesc0, offA), desc_advance(k0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
-          umma_ss(tmem + 128 + b * 64, desc_advance(ddesc0, offA), desc_advance(v0d, offB), IDESC_S, kk > 0 ? 1u : 0u);
+          const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+          umma_ss(tmem + COL_S, desc_advance(qdesc0, off), desc_advance(kd, off), IDESC_S, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bars->s_full[b]);
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        umma_commit(&bars->s_full);
+        if (!mbar_wait(&bars->v_full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        const uint64_t vd = desc_advance(v_k0, stage * BLK_BYTES);
+        const uint32_t dcol = tmem + COL_DP + (it & 1) * 128;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+          umma_ss(dcol, desc_advance(ddesc0, off), desc_advance(vd, off), IDESC_S, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->v_empty[stage]);
+        umma_commit(&bars->dp_full[it & 1]);
         return true;
       };
-      if (ok && total > 0) ok = issue_s(0);
+      if (ok && total > 0) ok = issue_s_dp(0);
       for (int it = 0; it < total && ok; ++it) {
-        if (it + 1 < total && !issue_s(it + 1)) { ok = false; break; }
-        const int b = it & 1;
-        if (!mbar_wait(&bars->p_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        const int stage = it % STAGES;
+        const uint32_t par = it & 1;
+        if (it + 1 < total) {
+          // S(it+1) overwrites S(it): the softmax warps must hold S(it) in registers.  dP(it+1) goes to the other
+          // dP buffer, whose dS(it-1) the in-order pipe has consumed with dQ(it-1).
+          if (!mbar_wait(&bars->s_free, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          if (!issue_s_dp(it + 1)) { ok = false; break; }
+        }
+        if (!mbar_wait(&bars->ds_full[par], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint64_t kmn = desc_advance(stage_mn0, stage2 * 2 * BLK_BYTES);
+        const uint64_t kmn = desc_advance(k_mn0, stage * BLK_BYTES);
         const uint32_t acc0 = it > 0 ? 1u : 0u;
+        const uint32_t dsa = tmem + COL_DP + par * 128;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)   // dQ += dS K
-          umma_ts(tmem + 256, tmem + b * 64 + kk * 8, desc_advance(kmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
-        umma_commit(&bars->kv_empty[stage2]);
-        if (++stage2 == STAGES) stage2 = 0;
+          umma_ts(tmem + COL_DQ, dsa + kk * 8, desc_advance(kmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        umma_commit(&bars->k_empty[stage]);
       }
       if (ok) umma_commit(&bars->acc_done);
       else {
@@ -437,36 +557,44 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
       }
     }
+   }
   } else {
+    reg_inc<REGS_MATH>();
     const int q = warp & 3;
-    const int hf = (warp - 2) >> 2;                       // which 32 of the block's 64 key columns this warp handles
+    const int hf = (warp - 4) >> 2;                       // which 64 of the block's 128 key columns this warp handles
     const int r = q * 32 + lane;                          // query row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const float sl2 = scale * LOG2E;
     const int64_t srow = (int64_t)head * Tq_pad + q0 + r;  // Tq_pad is a multiple of 128: every tile row has an entry
-    const float my_lse2 = lse2_pad[srow];
-    const float my_delta = delta_pad[srow];
+    const float nlse2 = lse2_pad[srow], ndelta = delta_pad[srow];      // stored negated
+    const uint64_t sl2_2 = pk2(sl2, sl2), nlse2_2 = pk2(nlse2, nlse2), ndelta_2 = pk2(ndelta, ndelta);
     bool ok = true;
     for (int it = 0; it < total; ++it) {
-      const int b = it & 1;
-      const int kvb0 = it * BLK + hf * 32;
-      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
-      uint32_t sv[32], dp[32];
+      const uint32_t par = it & 1;
+      const int kvb0 = it * BLK + hf * 64;
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      uint32_t sv[64];
       if (ok) {
         tc_fence_after();
-        tmem_ld_32x32(tmem + b * 64 + hf * 32 + lane_off, sv);
-        tmem_ld_32x32(tmem + 128 + b * 64 + hf * 32 + lane_off, dp);
+        tmem_ld_32x32(tmem + COL_S + hf * 64 + lane_off, sv);
+        tmem_ld_32x32(tmem + COL_S + hf * 64 + 32 + lane_off, sv + 32);
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->s_free);                       // S(it) is in registers
       }
-      // dS overwrites S's first 32 columns: both warps of the quarter have loaded; they also agree on leaving
-      if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
-      const bool diag = causal && (kvb0 + 31 > q0);
-      const bool tail = kvb0 + 32 > Tk;
-      uint32_t ds[16];
+      const bool diag = causal && (kvb0 + 63 > q0);
+      const bool tail = kvb0 + 64 > Tk;
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - my_lse2);
-        float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - my_lse2);
+      for (int c = 0; c < 32; ++c) {
+        float p0, p1;
+        const uint64_t x2 = fma2(pk2u(sv[2 * c], sv[2 * c + 1]), sl2_2, nlse2_2);
+        if ((c % ODY_BWD_POLY_DEN) < ODY_BWD_POLY_NUM) {
+          exp2_poly2(x2, p0, p1);
+        } else {
+          upk2(x2, p0, p1);
+          p0 = exp2_mufu(p0);
+          p1 = exp2_mufu(p1);
+        }
         if (diag) {
           if (kvb0 + 2 * c > q0 + r) p0 = 0.f;
           if (kvb0 + 2 * c + 1 > q0 + r) p1 = 0.f;
@@ -475,13 +603,33 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (kvb0 + 2 * c >= Tk) p0 = 0.f;
           if (kvb0 + 2 * c + 1 >= Tk) p1 = 0.f;
         }
-        ds[c] = pack_bf16(p0 * (__uint_as_float(dp[2 * c]) - my_delta) * scale,
-                          p1 * (__uint_as_float(dp[2 * c + 1]) - my_delta) * scale);
+        sv[2 * c] = __float_as_uint(p0);
+        sv[2 * c + 1] = __float_as_uint(p1);
       }
-      tmem_st_32x16(tmem + b * 64 + hf * 16 + lane_off, ds);
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->dp_full[par], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      uint32_t dp[64];
+      const uint32_t dcol = tmem + COL_DP + par * 128;
+      if (ok) {
+        tc_fence_after();
+        tmem_ld_32x32(dcol + hf * 64 + lane_off, dp);
+        tmem_ld_32x32(dcol + hf * 64 + 32 + lane_off, dp + 32);
+        tmem_ld_wait();
+      }
+      // dS overwrites dP's first 64 columns: both warps of the quarter have loaded; they also agree on leaving
+      if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
+      uint32_t ds[32];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        // dS = P * (dP - delta); the softmax scale is applied once, to dQ, in the epilogue
+        float d0, d1;
+        upk2(mul2(pk2u(sv[2 * c], sv[2 * c + 1]), add2(pk2u(dp[2 * c], dp[2 * c + 1]), ndelta_2)), d0, d1);
+        ds[c] = pack_bf16(d0, d1);
+      }
+      tmem_st_32x16(dcol + hf * 32 + lane_off, ds);
+      tmem_st_32x16(dcol + hf * 32 + 16 + lane_off, ds + 16);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars->p_full[b]);
+      mbar_arrive(&bars->ds_full[par]);
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_done, 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
     if (ok) {
@@ -489,15 +637,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t o[16];
-        tmem_ld_32x16(tmem + 256 + hf * 64 + lane_off + c * 16, o);
+        tmem_ld_32x16(tmem + COL_DQ + hf * 64 + lane_off + c * 16, o);
         tmem_ld_wait();
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           uint4 v4;
-          v4.x = pack_bf16(__uint_as_float(o[8 * t + 0]), __uint_as_float(o[8 * t + 1]));
-          v4.y = pack_bf16(__uint_as_float(o[8 * t + 2]), __uint_as_float(o[8 * t + 3]));
-          v4.z = pack_bf16(__uint_as_float(o[8 * t + 4]), __uint_as_float(o[8 * t + 5]));
-          v4.w = pack_bf16(__uint_as_float(o[8 * t + 6]), __uint_as_float(o[8 * t + 7]));
+          v4.x = pack_bf16(__uint_as_float(o[8 * t + 0]) * scale, __uint_as_float(o[8 * t + 1]) * scale);
+          v4.y = pack_bf16(__uint_as_float(o[8 * t + 2]) * scale, __uint_as_float(o[8 * t + 3]) * scale);
+          v4.z = pack_bf16(__uint_as_float(o[8 * t + 4]) * scale, __uint_as_float(o[8 * t + 5]) * scale);
+          v4.w = pack_bf16(__uint_as_float(o[8 * t + 6]) * scale, __uint_as_float(o[8 * t + 7]) * scale);
           const int chunk = c * 2 + t;
           *reinterpret_cast<uint4*>(sQ + hf * BIG_HALF + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
         }
@@ -506,7 +654,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     tc_fence_before();
     named_barrier(1, 256);
-    if (ok && warp == 2 && lane == 0 && !*abort_flag) {
+    if (ok && warp == 4 && lane == 0 && !*abort_flag) {
       const int d = dq_split.rows > 0 ? q0 / dq_split.rows : 0;
       const int row = dq_split.rows > 0 ? q0 - d * dq_split.rows : q0;
       const CUtensorMap* mQ = dq_split.rows > 0 ? &dq_split.m[d] : &tmDQ;
@@ -595,24 +743,20 @@ extern "C" int ody_flash_bwd_ex(const void* dO, const void* q, const void* k, co
     prep_kernel<<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)dO, (const __nv_bfloat16*)o, lse, delta_pad,
                                                       lse2_pad, Tq, Tpad, H, do_row, o_row);
   }
-  CUtensorMap tQ, tDO, tK, tV, tQ64, tDO64, tK64, tV64, tDQ, tDK, tDV;
+  CUtensorMap tQ, tDO, tK, tV, tDQ, tDK, tDV;
   int r;
   if ((r = make_tmap_3d_bf16(&tQ, q, HD, H, Tq, HD * 2, q_row * 2, 64, 1, BIG))) return 770000 + r;
   if ((r = make_tmap_3d_bf16(&tDO, dO, HD, H, Tq, HD * 2, do_row * 2, 64, 1, BIG))) return 770000 + r;
-  if ((r = make_tmap_3d_bf16(&tQ64, q, HD, H, Tq, HD * 2, q_row * 2, 64, 1, BLK))) return 770000 + r;
-  if ((r = make_tmap_3d_bf16(&tDO64, dO, HD, H, Tq, HD * 2, do_row * 2, 64, 1, BLK))) return 770000 + r;
   if ((r = make_tmap_3d_bf16(&tK, k, HD, Hkv, Tk, HD * 2, k_row * 2, 64, 1, BIG))) return 780000 + r;
   if ((r = make_tmap_3d_bf16(&tV, v, HD, Hkv, Tk, HD * 2, v_row * 2, 64, 1, BIG))) return 780000 + r;
-  if ((r = make_tmap_3d_bf16(&tK64, k, HD, Hkv, Tk, HD * 2, k_row * 2, 64, 1, BLK))) return 780000 + r;
-  if ((r = make_tmap_3d_bf16(&tV64, v, HD, Hkv, Tk, HD * 2, v_row * 2, 64, 1, BLK))) return 780000 + r;
   if ((r = make_tmap_3d_bf16(&tDQ, dq, HD, H, Tq, HD * 2, dq_row * 2, 64, 1, BIG))) return 790000 + r;
   if ((r = make_tmap_3d_bf16(&tDK, dk, HD, Hkv, Tk, HD * 2, dk_row * 2, 64, 1, BIG))) return 790000 + r;
   if ((r = make_tmap_3d_bf16(&tDV, dv, HD, Hkv, Tk, HD * 2, dv_row * 2, 64, 1, BIG))) return 790000 + r;
   dim3 gkv((Tk + BIG - 1) / BIG, Hkv);
-  flash_bwd_dkdv_kernel<<<gkv, NUM_THREADS, KV_SMEM_TOTAL, st>>>(tQ64, tDO64, tK, tV, tDK, tDV, lse2_pad, delta_pad, Tq, Tk,
+  flash_bwd_dkdv_kernel<<<gkv, NUM_THREADS, KV_SMEM_TOTAL, st>>>(tQ, tDO, tK, tV, tDK, tDV, lse2_pad, delta_pad, Tq, Tk,
                                                                  Tpad, H, Hkv, causal, scale, err, g_bwd_trace, sk, sv);
   dim3 gq((Tq + BIG - 1) / BIG, H);
-  flash_bwd_dq_kernel<<<gq, NUM_THREADS, Q_SMEM_TOTAL, st>>>(tQ, tDO, tK64, tV64, tDQ, lse2_pad, delta_pad, Tq, Tk, Tpad, H,
+  flash_bwd_dq_kernel<<<gq, NUM_THREADS, Q_SMEM_TOTAL, st>>>(tQ, tDO, tK, tV, tDQ, lse2_pad, delta_pad, Tq, Tk, Tpad, H,
                                                              Hkv, causal, scale, err, sq);
   return (int)cudaGetLastError();
 }

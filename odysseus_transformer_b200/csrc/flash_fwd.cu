@@ -23,6 +23,14 @@
 #include "sm100.cuh"
 #include "peer_comm.cuh"
 
+// Of every ODY_FWD_POLY_DEN column pairs, the first ODY_FWD_POLY_NUM take their exponentials on the FMA pipe
+// (exp2_poly2) instead of the special-function unit.  Measured on B200: any mix is a few percent slower than
+// all-MUFU - the softmax warps are bound by the latency of their dependent chains, not by either pipe - so it is off.
+#ifndef ODY_FWD_POLY_NUM
+#define ODY_FWD_POLY_NUM 0
+#define ODY_FWD_POLY_DEN 2
+#endif
+
 namespace ody {
 namespace fwd {
 
@@ -36,6 +44,10 @@ constexpr int SMEM_TOTAL = SMEM_TILES + 2560 + 1024;
 //   0 TMA producer, 1 Q K^T issuer, 2 P V issuer, 3 idle | 4..11 softmax (two per TMEM lane quarter) | 12..15 comm (PUSH only)
 constexpr int NUM_THREADS = 384;
 constexpr int NUM_THREADS_PUSH = NUM_THREADS + gc::COMM_THREADS;
+// Register split of the PUSH variant by setmaxnreg: 512 threads are launched with 128 registers each; the split
+// must fit inside that allocation or the increase never returns.
+constexpr int REGS_ISSUE = 56, REGS_MATH = 176, REGS_COMM = 104;
+static_assert(128 * REGS_ISSUE + 256 * REGS_MATH + 128 * REGS_COMM <= NUM_THREADS_PUSH * 128, "setmaxnreg split exceeds the CTA's registers");
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 
 // Optional second destination of the output: rows [d * rows, (d + 1) * rows) also go to tensor map m[d]
@@ -66,11 +78,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
 }
-
-template <int N>
-__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N>
-__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // PUSH: four extra comm warps in CTAs 0..push_ctas-1 store this rank's K/V shard into the gathered
 // buffers of the ring peers named by `pp` while the attention tiles run (ring attention: the kernel of
@@ -133,12 +140,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp >= 12) {
     // ------------------------------------------------------------------ comm warps (PUSH only)
     if constexpr (PUSH) {
-      reg_dec<104>();
+      reg_dec<REGS_COMM>();
       const int cta = blockIdx.y * gridDim.x + blockIdx.x;
       if (cta < push_ctas) gc::comm_warps_main(pp, cta, push_ctas, 12 * 32, abort_flag, err);
     }
   } else if (warp < 4) {
-   if constexpr (PUSH) reg_dec<56>();
+   if constexpr (PUSH) reg_dec<REGS_ISSUE>();
    if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -218,7 +225,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
    }   // warp 3 idles: it only keeps the warpgroups aligned
   } else {
     // ------------------------------------------------------------------ softmax + epilogue (warps 4..11)
-    if constexpr (PUSH) reg_inc<176>();
+    if constexpr (PUSH) reg_inc<REGS_MATH>();
     const int q = warp & 3;                            // TMEM lane quarter
     const int hf = (warp - 4) >> 2;                    // key columns [hf * 64, hf * 64 + 64) of every block
     const int r = q * 32 + lane;                       // row inside the tile == TMEM lane
@@ -293,16 +300,29 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_wait();
         }
       }
-      float rowsum = 0.f;
+      // packed pairs: x = s * scale * log2(e) - m for two columns per instruction, two running partial sums
+      const uint64_t sl2_2 = pk2(sl2, sl2), nm_2 = pk2(-m_used, -m_used);
+      uint64_t rs2 = pk2(0.f, 0.f);
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        const float p0 = fast_exp2(__uint_as_float(sv[2 * c]) * sl2 - m_used);
-        const float p1 = fast_exp2(__uint_as_float(sv[2 * c + 1]) * sl2 - m_used);
-        rowsum += p0 + p1;
+        float p0, p1;
+        const uint64_t x2 = fma2(pk2u(sv[2 * c], sv[2 * c + 1]), sl2_2, nm_2);
+        if ((c % ODY_FWD_POLY_DEN) < ODY_FWD_POLY_NUM) {
+          exp2_poly2(x2, p0, p1);
+        } else {
+          upk2(x2, p0, p1);
+          p0 = exp2_mufu(p0);
+          p1 = exp2_mufu(p1);
+        }
+        rs2 = add2(rs2, pk2(p0, p1));
         pk[c] = pack_bf16(p0, p1);
       }
-      l += rowsum;
+      {
+        float r0, r1;
+        upk2(rs2, r0, r1);
+        l += r0 + r1;
+      }
       if (ok && j >= 2)   // P buffer b was last read by P V of block j-2
         ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[b], ((j - 2) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
       if (ok) {

@@ -125,6 +125,79 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 }
 // Named barrier that also ANDs a predicate over its participants: used so that the warps sharing a barrier
 // leave a loop together when one of them saw a wait give up (a warp that left alone would strand the others).
+// ---- exponentials for the attention kernels
+// exp2_mufu is the special-function unit's ex2.  exp2_poly / exp2_poly2 evaluate 2^x on the FMA pipe instead:
+// 2^x = 2^n * 2^f with n = round(x) taken from the mantissa of x + 1.5 * 2^23, f in [-0.5, 0.5], a degree-3 minimax
+// polynomial for 2^f (relative error 7.5e-5, far below the bf16 rounding the probabilities get anyway) and n added
+// to the exponent field.  Valid for x <= 127; x below -125 returns 2^-125.
+__device__ __forceinline__ float exp2_mufu(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float exp2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(0.0551716499f, f, 0.2426111251f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+// Packed fp32 pairs (sm_100 executes add / mul / fma on two floats per instruction): the softmax warps are bound
+// by instruction issue, so pairing halves the cost of their elementwise arithmetic.
+__device__ __forceinline__ uint64_t pk2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t pk2u(uint32_t a, uint32_t b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ void upk2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// 2^x for a packed pair on the FMA pipe (same scheme as exp2_poly): about 10 instructions per pair
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& r0, float& r1) {
+  float x0, x1;
+  upk2(x2, x0, x1);
+  x2 = pk2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const uint64_t magic = pk2(12582912.f, 12582912.f), nmagic = pk2(-12582912.f, -12582912.f);
+  const uint64_t t2 = add2(x2, magic);
+  const uint64_t f2 = fma2(add2(t2, nmagic), pk2(-1.f, -1.f), x2);      // x - round(x), in [-0.5, 0.5]
+  uint64_t p2 = fma2(pk2(0.0551716499f, 0.0551716499f), f2, pk2(0.2426111251f, 0.2426111251f));
+  p2 = fma2(p2, f2, pk2(0.6932609677f, 0.6932609677f));
+  p2 = fma2(p2, f2, pk2(0.9999280572f, 0.9999280572f));
+  float p0, p1, t0, t1;
+  upk2(p2, p0, p1);
+  upk2(t2, t0, t1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+}
+
+// Warpgroup register reallocation (all four warps of an aligned warpgroup execute the same instruction):
+// producer / issuer warpgroups give registers away, the math warpgroups take them.
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
 __device__ __forceinline__ bool named_barrier_and(int id, int nthreads, bool ok) {
   uint32_t r;
   asm volatile(

@@ -35,6 +35,12 @@ def test_modes_2gpu(mode, backend):
     _launch(2, mode, "small", 1024, 0, 1, backend)
 
 
+def test_ulysses_4gpu():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    _launch(4, "ulysses", "small", 2048, 0, 1, "fused")
+
+
 def test_ring_4gpu():
     if torch.cuda.device_count() < 4:
         pytest.skip("needs 4 GPUs")
