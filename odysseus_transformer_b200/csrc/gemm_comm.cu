@@ -22,10 +22,11 @@
 // reports through the status word; nothing here can spin forever.
 #include "ody_kernels.h"
 
-// Every wait in this file can depend on a peer (the pipeline stalls while rows are in flight), so all of
-// them use the run-time peer limit instead of the 1 s of the single-GPU kernels.
-// ody_set_peer_wait_limit changes it for the current device.
-#define ODY_SPIN_LIMIT_CYCLES (ody::gc::g_peer_spin_limit)
+// Every wait in this file can depend on a peer (the pipeline stalls while rows are in flight), so the
+// pipeline's own barrier waits get twice the run-time peer limit instead of the 1 s of the single-GPU
+// kernels: a peer that never delivers is then reported as such (the peer wait gives up first and raises
+// the abort flag that ends the others).  ody_set_peer_wait_limit changes the limit for the current device.
+#define ODY_SPIN_LIMIT_CYCLES (2 * ody::gc::g_peer_spin_limit)
 #include "peer_comm.cuh"
 
 namespace ody {
