@@ -43,7 +43,8 @@ constexpr int BIG_HALF = BIG_BYTES / 2;
 constexpr int BLK_BYTES = BLK * HD * 2;          // 32 KB (two halves of [128 x 128 B])
 constexpr int BLK_HALF = BLK_BYTES / 2;
 constexpr int STAGES = 2;
-constexpr int STAT_BYTES = 2 * BLK * 4;          // lse2 + delta of one streamed block
+constexpr int STAT_TILE = BLK * 32;              // one statistics tile: 128 rows x 16 bf16, no swizzle (see prep_kernel)
+constexpr int STAT_BYTES = 2 * STAT_TILE;        // -lse/scale tile and -delta tile of one streamed block
 // warps 0..3: TMA producer, MMA issuer, two idle (they complete the warpgroup whose registers are given away);
 // warps 4..11: softmax / epilogue, two per TMEM lane quarter
 constexpr int NUM_THREADS = 384;
@@ -65,14 +66,22 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
 
 // ------------------------------------------------------------------------------------------- prep
 // delta_pad / lse2_pad: [H, Tpad] fp32 holding -delta and -lse * log2(e); Tpad multiple of 128; rows >= T are zero.
+//
+// stat_tiles: [H, Tpad / 128, 2] tiles of 4 KB for the dK/dV kernel, which adds the per-query-column terms to S^T and
+// dP^T with one extra MMA step each instead of reading them in the softmax loop: D[i][j] += sum_k ONES[i][k] * C[j][k]
+// with C[j][0..15] = {hi, lo, 0 x 6, hi, lo, 0 x 6}, hi + lo the bf16 split of HALF the term (both 16-byte halves are
+// equal, so the operand does not depend on which half the hardware takes as k = 0..7).  Tile 0 carries -lse / scale
+// (so that (S^T + c) * scale * log2 e = s * scale * log2 e - lse * log2 e), tile 1 carries -delta.  Layout: 8-row groups
+// of 256 bytes; inside a group the first 16-byte halves of the 8 rows, then the second halves.
 __global__ void prep_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
                             const float* __restrict__ lse, float* __restrict__ delta_pad, float* __restrict__ lse2_pad,
+                            uint8_t* __restrict__ stat_tiles, float inv_scale,
                             int T, int Tpad, int H, int64_t do_row, int64_t o_row) {
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp_global >= Tpad * H) return;
   const int t = warp_global / H, h = warp_global % H;
-  float s = 0.f, l2 = 0.f;
+  float s = 0.f, l2 = 0.f, l1 = 0.f;
   if (t < T) {
     const uint2 a = *reinterpret_cast<const uint2*>(dO + (int64_t)t * do_row + h * HD + lane * 4);
     const uint2 b = *reinterpret_cast<const uint2*>(O + (int64_t)t * o_row + h * HD + lane * 4);
@@ -85,11 +94,23 @@ __global__ void prep_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfl
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    l2 = lse[(int64_t)h * T + t] * LOG2E;
+    l1 = lse[(int64_t)h * T + t];
+    l2 = l1 * LOG2E;
   }
   if (lane == 0) {
     delta_pad[(int64_t)h * Tpad + t] = -s;
     lse2_pad[(int64_t)h * Tpad + t] = -l2;
+    const int blk = t / BLK, row = t % BLK;
+    uint8_t* tile = stat_tiles + ((int64_t)h * (Tpad / BLK) + blk) * STAT_BYTES + (row >> 3) * 256 + (row & 7) * 16;
+    const float c[2] = {-0.5f * l1 * inv_scale, -0.5f * s};
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+      const __nv_bfloat16 hi = __float2bfloat16_rn(c[w]);
+      const __nv_bfloat16 lo = __float2bfloat16_rn(c[w] - __bfloat162float(hi));
+      const uint4 v = make_uint4((uint32_t)__bfloat16_as_ushort(hi) | ((uint32_t)__bfloat16_as_ushort(lo) << 16), 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(tile + w * STAT_TILE) = v;
+      *reinterpret_cast<uint4*>(tile + w * STAT_TILE + 128) = v;
+    }
   }
 }
 
@@ -103,7 +124,7 @@ struct BarsKV {
   uint32_t tmem_base;
   int abort_flag;
 };
-constexpr int KV_SMEM_TILES = 2 * BIG_BYTES + STAGES * (2 * BLK_BYTES + STAT_BYTES);
+constexpr int KV_SMEM_TILES = 2 * BIG_BYTES + STAGES * (2 * BLK_BYTES + STAT_BYTES) + STAT_TILE;   // + the all-ones operand
 constexpr int KV_SMEM_TOTAL = KV_SMEM_TILES + 256 + 1024;
 // TMEM columns: S^T 0..127 (P^T, bf16, overwrites 0..63), dP^T 128..255 (dS^T overwrites 128..191), dV 256, dK 384
 constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 384;
@@ -119,7 +140,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                       const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
-                      const float* __restrict__ lse2_pad, const float* __restrict__ delta_pad, int Tq, int Tk, int Tq_pad,
+                      const uint8_t* __restrict__ stat_tiles, int Tq, int Tk, int Tq_pad,
                       int H, int Hkv, int causal, float scale, int* __restrict__ err, long long* __restrict__ dbg,
                       const __grid_constant__ SplitMaps dk_split, const __grid_constant__ SplitMaps dv_split) {
   extern __shared__ uint8_t smem_raw[];
@@ -128,7 +149,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint8_t* sV = smem + BIG_BYTES;
   uint8_t* sQs = smem + 2 * BIG_BYTES;                    // STAGES Q blocks
   uint8_t* sDs = sQs + STAGES * BLK_BYTES;                // STAGES dO blocks
-  uint8_t* sStat = sDs + STAGES * BLK_BYTES;              // per stage: lse2[128] | delta[128]
+  uint8_t* sStat = sDs + STAGES * BLK_BYTES;              // per stage: -lse/scale tile | -delta tile
+  uint8_t* sOnes = sStat + STAGES * STAT_BYTES;           // 128 x 16 bf16 ones: the A operand of the statistics step
   BarsKV* bars = (BarsKV*)(smem + KV_SMEM_TILES);
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -157,6 +179,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+  for (int i = threadIdx.x; i < STAT_TILE / 16; i += NUM_THREADS)
+    reinterpret_cast<uint4*>(sOnes)[i] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  fence_proxy_async_smem();       // the tensor core reads sOnes through the async proxy
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -179,12 +204,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         // the Q ring is released by dK, the dO ring (earlier) by dV
         if (!mbar_wait(&bars->q_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
         uint8_t* sQ = sQs + stage * BLK_BYTES;
-        float* st = (float*)(sStat + stage * STAT_BYTES);
         mbar_expect_tx(&bars->q_full[stage], BLK_BYTES + STAT_BYTES);
         tma_load_3d(sQ, &tmQ, 0, head, qrow, &bars->q_full[stage]);
         tma_load_3d(sQ + BLK_HALF, &tmQ, 64, head, qrow, &bars->q_full[stage]);
-        bulk_load_1d(st, lse2_pad + (int64_t)head * Tq_pad + qrow, BLK * 4, &bars->q_full[stage]);
-        bulk_load_1d(st + BLK, delta_pad + (int64_t)head * Tq_pad + qrow, BLK * 4, &bars->q_full[stage]);
+        bulk_load_1d(sStat + stage * STAT_BYTES, stat_tiles + ((int64_t)head * (Tq_pad / BLK) + qrow / BLK) * STAT_BYTES, STAT_BYTES,
+                     &bars->q_full[stage]);
         if (!mbar_wait(&bars->d_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
         uint8_t* sD = sDs + stage * BLK_BYTES;
         mbar_expect_tx(&bars->d_full[stage], BLK_BYTES);
@@ -200,8 +224,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const uint64_t kdesc0 = make_smem_desc(smem_u32(sK), 16, 1024), vdesc0 = make_smem_desc(smem_u32(sV), 16, 1024);
       const uint64_t q_k0 = make_smem_desc(smem_u32(sQs), 16, 1024), d_k0 = make_smem_desc(smem_u32(sDs), 16, 1024);
       const uint64_t q_mn0 = make_smem_desc(smem_u32(sQs), BLK_HALF, 1024), d_mn0 = make_smem_desc(smem_u32(sDs), BLK_HALF, 1024);
+      const uint64_t ones_d = make_smem_desc_noswizzle(smem_u32(sOnes), 128, 256);
+      const uint64_t stat_d0 = make_smem_desc_noswizzle(smem_u32(sStat), 128, 256);
       const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
-      // S^T(it) = K Q^T: waits for the Q block
+      // S^T(it) = K Q^T - lse / scale (per query column): waits for the Q block
       auto issue_s = [&](int it) -> bool {
         const int stage = it % STAGES;
         if (!mbar_wait(&bars->q_full[stage], (it / STAGES) & 1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
@@ -212,6 +238,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
           umma_ss(tmem + COL_ST, desc_advance(kdesc0, off), desc_advance(qd, off), IDESC_S, kk > 0 ? 1u : 0u);
         }
+        umma_ss(tmem + COL_ST, ones_d, desc_advance(stat_d0, stage * STAT_BYTES), IDESC_S, 1u);
         umma_commit(&bars->s_full);
         return true;
       };
@@ -226,6 +253,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
           umma_ss(tmem + COL_DPT, desc_advance(vdesc0, off), desc_advance(dd, off), IDESC_S, kk > 0 ? 1u : 0u);
         }
+        // dP^T - delta: the statistics tile of this block came with its Q block, which S^T(it) already waited for
+        umma_ss(tmem + COL_DPT, ones_d, desc_advance(stat_d0, stage * STAT_BYTES + STAT_TILE), IDESC_S, 1u);
         umma_commit(&bars->dp_full);
         return true;
       };
@@ -275,14 +304,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const uint64_t sl2_2 = pk2(sl2, sl2);
     bool ok = true;
     for (int it = 0; it < total; ++it) {
-      const int stage = it % STAGES;
       const uint32_t par = it & 1;
       const int qrow0 = (i0 + it % per_head) * BLK + hf * 64;
       const bool strace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 128 && it < 48;
       // ---- part 1: S^T -> P^T
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
-      // s_full implies q_full[stage] completed earlier (the MMAs consumed the block); its stats are in smem
-      const float* st = (const float*)(sStat + stage * STAT_BYTES) + hf * 64;
       if (strace) dbg[it * 8 + 2] = clock64();                             // S^T(it) complete
       uint32_t sv[64];
       if (ok) {
@@ -300,8 +326,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         uint32_t pp[32];
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          // x = s * scale * log2(e) - lse2 for two query columns at once (the stats are stored negated)
-          const uint64_t x2 = fma2(pk2u(sv[2 * c], sv[2 * c + 1]), sl2_2, *reinterpret_cast<const uint64_t*>(st + 2 * c));
+          // the accumulator already holds s - lse / scale: x = that * scale * log2(e), two query columns at once
+          const uint64_t x2 = mul2(pk2u(sv[2 * c], sv[2 * c + 1]), sl2_2);
           float p0, p1;
           if ((c % ODY_BWD_POLY_DEN) < ODY_BWD_POLY_NUM) {
             exp2_poly2(x2, p0, p1);
@@ -345,10 +371,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         uint32_t ds[32];
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          // dS = P * (dP - delta); the softmax scale is applied once, to dK, in the epilogue
-          const uint64_t t2 = add2(pk2u(dp[2 * c], dp[2 * c + 1]), *reinterpret_cast<const uint64_t*>(st + BLK + 2 * c));
+          // dS = P * (dP - delta), the accumulator already holding dP - delta; the softmax scale is applied once, to
+          // dK, in the epilogue
           float d0, d1;
-          upk2(mul2(pk2u(sv[2 * c], sv[2 * c + 1]), t2), d0, d1);
+          upk2(mul2(pk2u(sv[2 * c], sv[2 * c + 1]), pk2u(dp[2 * c], dp[2 * c + 1])), d0, d1);
           ds[c] = pack_bf16(d0, d1);
         }
         tmem_st_32x16(tmem + COL_DPT + hf * 32 + lane_off, ds);
@@ -411,9 +437,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 }
 
 // ------------------------------------------------------------------------------------------- dQ
+constexpr int K_STAGES = 3;
 struct BarsQ {
   uint64_t qd_full;
-  uint64_t k_full[STAGES], k_empty[STAGES];
+  uint64_t k_full[K_STAGES], k_empty[K_STAGES];
   uint64_t v_full[STAGES], v_empty[STAGES];
   uint64_t s_full, s_free;                       // one completion per block each: parity = block & 1
   uint64_t dp_full[2], ds_full[2];               // dP / dS are double buffered: parity = (block >> 1) & 1
@@ -421,7 +448,9 @@ struct BarsQ {
   uint32_t tmem_base;
   int abort_flag;
 };
-constexpr int Q_SMEM_TILES = 2 * BIG_BYTES + STAGES * 2 * BLK_BYTES;
+// A K block serves S(i) early and dQ(i) late, so its slot is held for a whole iteration and a half: with two slots the
+// load of K(i+1) could only start when dQ(i-1) had finished and the MMA thread waited ~700 cycles per block for it.
+constexpr int Q_SMEM_TILES = 2 * BIG_BYTES + (K_STAGES + STAGES) * BLK_BYTES;
 constexpr int Q_SMEM_TOTAL = Q_SMEM_TILES + 256 + 1024;
 // TMEM columns: S 0..127, dP(b) at 128 + b * 128 (dS, bf16, overwrites its first 64 columns), dQ 384
 constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 384;
@@ -431,13 +460,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const __grid_constant__ CUtensorMap tmDQ, const float* __restrict__ lse2_pad,
                     const float* __restrict__ delta_pad, int Tq, int Tk, int Tq_pad, int H, int Hkv, int causal,
-                    float scale, int* __restrict__ err, const __grid_constant__ SplitMaps dq_split) {
+                    float scale, int* __restrict__ err, const __grid_constant__ SplitMaps dq_split, long long* __restrict__ dbg) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sD = smem + BIG_BYTES;
-  uint8_t* sKs = smem + 2 * BIG_BYTES;                    // STAGES K blocks
-  uint8_t* sVs = sKs + STAGES * BLK_BYTES;                // STAGES V blocks
+  uint8_t* sKs = smem + 2 * BIG_BYTES;                    // K_STAGES K blocks
+  uint8_t* sVs = sKs + K_STAGES * BLK_BYTES;              // STAGES V blocks
   BarsQ* bars = (BarsQ*)(smem + Q_SMEM_TILES);
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -451,10 +480,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->qd_full, 1);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1);
-      mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1);
-    }
+    for (int s = 0; s < K_STAGES; ++s) { mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1); }
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->s_free, 256);
     mbar_init(&bars->ds_full[0], 256);
@@ -484,11 +511,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int it = 0; it < total; ++it) {
         const int stage = it % STAGES;
         const uint32_t phase = (it / STAGES) & 1;
-        if (!mbar_wait(&bars->k_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
-        uint8_t* sK = sKs + stage * BLK_BYTES;
-        mbar_expect_tx(&bars->k_full[stage], BLK_BYTES);
-        tma_load_3d(sK, &tmK, 0, kvh, it * BLK, &bars->k_full[stage]);
-        tma_load_3d(sK + BLK_HALF, &tmK, 64, kvh, it * BLK, &bars->k_full[stage]);
+        const int kstage = it % K_STAGES;
+        if (!mbar_wait(&bars->k_empty[kstage], ((it / K_STAGES) & 1) ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        uint8_t* sK = sKs + kstage * BLK_BYTES;
+        mbar_expect_tx(&bars->k_full[kstage], BLK_BYTES);
+        tma_load_3d(sK, &tmK, 0, kvh, it * BLK, &bars->k_full[kstage]);
+        tma_load_3d(sK + BLK_HALF, &tmK, 64, kvh, it * BLK, &bars->k_full[kstage]);
         if (!mbar_wait(&bars->v_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
         uint8_t* sV = sVs + stage * BLK_BYTES;
         mbar_expect_tx(&bars->v_full[stage], BLK_BYTES);
@@ -508,9 +536,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       auto issue_s_dp = [&](int it) -> bool {
         const int stage = it % STAGES;
         const uint32_t phase = (it / STAGES) & 1;
-        if (!mbar_wait(&bars->k_full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
+        const int kstage = it % K_STAGES;
+        if (!mbar_wait(&bars->k_full[kstage], (it / K_STAGES) & 1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint64_t kd = desc_advance(k_k0, stage * BLK_BYTES);
+        const uint64_t kd = desc_advance(k_k0, kstage * BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
@@ -531,24 +560,28 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         return true;
       };
       if (ok && total > 0) ok = issue_s_dp(0);
+      const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
       for (int it = 0; it < total && ok; ++it) {
-        const int stage = it % STAGES;
         const uint32_t par = it & 1;
+        if (trace && it < 48) dbg[it * 8 + 0] = clock64();                 // loop start
         if (it + 1 < total) {
           // S(it+1) overwrites S(it): the softmax warps must hold S(it) in registers.  dP(it+1) goes to the other
           // dP buffer, whose dS(it-1) the in-order pipe has consumed with dQ(it-1).
           if (!mbar_wait(&bars->s_free, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          if (trace && it < 48) dbg[it * 8 + 1] = clock64();               // S(it) freed
           if (!issue_s_dp(it + 1)) { ok = false; break; }
+          if (trace && it < 48) dbg[it * 8 + 2] = clock64();               // S, dP(it+1) issued
         }
         if (!mbar_wait(&bars->ds_full[par], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        if (trace && it < 48) dbg[it * 8 + 3] = clock64();                 // dS(it) seen
         tc_fence_after();
-        const uint64_t kmn = desc_advance(k_mn0, stage * BLK_BYTES);
+        const uint64_t kmn = desc_advance(k_mn0, (it % K_STAGES) * BLK_BYTES);
         const uint32_t acc0 = it > 0 ? 1u : 0u;
         const uint32_t dsa = tmem + COL_DP + par * 128;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)   // dQ += dS K
           umma_ts(tmem + COL_DQ, dsa + kk * 8, desc_advance(kmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
-        umma_commit(&bars->k_empty[stage]);
+        umma_commit(&bars->k_empty[it % K_STAGES]);
       }
       if (ok) umma_commit(&bars->acc_done);
       else {
@@ -572,7 +605,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int it = 0; it < total; ++it) {
       const uint32_t par = it & 1;
       const int kvb0 = it * BLK + hf * 64;
+      const bool strace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 128 && it < 48;
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      if (strace) dbg[it * 8 + 4] = clock64();                             // S(it) complete
       uint32_t sv[64];
       if (ok) {
         tc_fence_after();
@@ -606,7 +641,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         sv[2 * c] = __float_as_uint(p0);
         sv[2 * c + 1] = __float_as_uint(p1);
       }
+      if (strace) dbg[it * 8 + 5] = clock64();                             // P computed (as far as the compiler kept it here)
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->dp_full[par], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      if (strace) dbg[it * 8 + 6] = clock64();                             // dP(it) complete
       uint32_t dp[64];
       const uint32_t dcol = tmem + COL_DP + par * 128;
       if (ok) {
@@ -630,6 +667,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->ds_full[par]);
+      if (strace) dbg[it * 8 + 7] = clock64();                             // dS published
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_done, 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
     if (ok) {
@@ -678,7 +716,7 @@ extern "C" void ody_flash_bwd_set_trace(long long* buf) { g_bwd_trace = buf; }
 
 extern "C" int64_t ody_flash_bwd_workspace_bytes(int Tq, int H) {
   const int64_t Tpad = ((int64_t)Tq + 127) / 128 * 128;
-  return 2 * (int64_t)H * Tpad * 4;
+  return 2 * (int64_t)H * Tpad * 4 + (int64_t)H * (Tpad / 128) * ody::bwd::STAT_BYTES;
 }
 
 // workspace: ody_flash_bwd_workspace_bytes(Tq, H) bytes, 16-byte aligned (delta and exp2-domain LSE, padded).
@@ -736,12 +774,13 @@ extern "C" int ody_flash_bwd_ex(const void* dO, const void* q, const void* k, co
   const int Tpad = (Tq + 127) / 128 * 128;
   float* delta_pad = (float*)workspace;
   float* lse2_pad = delta_pad + (int64_t)H * Tpad;
+  uint8_t* stat_tiles = (uint8_t*)(lse2_pad + (int64_t)H * Tpad);
   {
     const int64_t warps = (int64_t)Tpad * H;
     const int threads = 256;
     const int64_t blocks = (warps * 32 + threads - 1) / threads;
     prep_kernel<<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)dO, (const __nv_bfloat16*)o, lse, delta_pad,
-                                                      lse2_pad, Tq, Tpad, H, do_row, o_row);
+                                                      lse2_pad, stat_tiles, 1.f / scale, Tq, Tpad, H, do_row, o_row);
   }
   CUtensorMap tQ, tDO, tK, tV, tDQ, tDK, tDV;
   int r;
@@ -753,10 +792,10 @@ extern "C" int ody_flash_bwd_ex(const void* dO, const void* q, const void* k, co
   if ((r = make_tmap_3d_bf16(&tDK, dk, HD, Hkv, Tk, HD * 2, dk_row * 2, 64, 1, BIG))) return 790000 + r;
   if ((r = make_tmap_3d_bf16(&tDV, dv, HD, Hkv, Tk, HD * 2, dv_row * 2, 64, 1, BIG))) return 790000 + r;
   dim3 gkv((Tk + BIG - 1) / BIG, Hkv);
-  flash_bwd_dkdv_kernel<<<gkv, NUM_THREADS, KV_SMEM_TOTAL, st>>>(tQ, tDO, tK, tV, tDK, tDV, lse2_pad, delta_pad, Tq, Tk,
+  flash_bwd_dkdv_kernel<<<gkv, NUM_THREADS, KV_SMEM_TOTAL, st>>>(tQ, tDO, tK, tV, tDK, tDV, stat_tiles, Tq, Tk,
                                                                  Tpad, H, Hkv, causal, scale, err, g_bwd_trace, sk, sv);
   dim3 gq((Tq + BIG - 1) / BIG, H);
   flash_bwd_dq_kernel<<<gq, NUM_THREADS, Q_SMEM_TOTAL, st>>>(tQ, tDO, tK, tV, tDQ, lse2_pad, delta_pad, Tq, Tk, Tpad, H,
-                                                             Hkv, causal, scale, err, sq);
+                                                             Hkv, causal, scale, err, sq, g_bwd_trace);
   return (int)cudaGetLastError();
 }

@@ -290,6 +290,16 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   d |= (uint64_t)2 << 61;   // SWIZZLE_128B
   return d;
 }
+// Same, without swizzle ("interleaved" core matrices of 8 rows x 16 bytes): K-adjacent core matrices `lbo` bytes
+// apart, 8-row groups `sbo` apart.  Used for the 16-column statistics tiles of the attention backward.
+__device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version for sm_100
+  return d;
+}
 // Advance a descriptor's start address by `bytes` (a multiple of 16).  Only the low word changes - the issuing
 // thread spends one add per MMA instead of rebuilding the descriptor, and a single thread's instruction
 // stream is what bounds how fast small MMAs can be issued.
