@@ -143,7 +143,7 @@ void ody_register_attention(pybind11::module& m) {
     else ody_flash_fwd_set_trace(nullptr);
   });
   m.def("attn_bwd_set_trace", [](const c10::optional<at::Tensor>& t) {
-    if (t.has_value()) { req(t.value().is_cuda() && t.value().scalar_type() == at::kLong && t.value().numel() >= 48 * 8, "trace: int64 [48*8]"); ody_flash_bwd_set_trace((long long*)t.value().data_ptr()); }
+    if (t.has_value()) { req(t.value().is_cuda() && t.value().scalar_type() == at::kLong && t.value().numel() >= 96 * 8, "trace: int64 [96*8] (dK/dV kernel stamps, then dQ kernel stamps)"); ody_flash_bwd_set_trace((long long*)t.value().data_ptr()); }
     else ody_flash_bwd_set_trace(nullptr);
   });
   m.def("attn_bwd", &attn_bwd, py::arg("dO"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("lse"),

@@ -437,36 +437,37 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 }
 
 // ------------------------------------------------------------------------------------------- dQ
+// Q and dO of the tile are the A operands of every S = Q K^T and dP = dO V^T of the kernel, so they live in TMEM (bf16,
+// 64 columns each, written once by the softmax warps straight from global memory) and all 24 MMAs of a block are of the
+// TS kind: only the streamed K / V block is read from shared memory, which is what bounds the rate of SS instructions.
 constexpr int K_STAGES = 3;
 struct BarsQ {
-  uint64_t qd_full;
   uint64_t k_full[K_STAGES], k_empty[K_STAGES];
-  uint64_t v_full[STAGES], v_empty[STAGES];
-  uint64_t s_full, s_free;                       // one completion per block each: parity = block & 1
-  uint64_t dp_full[2], ds_full[2];               // dP / dS are double buffered: parity = (block >> 1) & 1
+  uint64_t v_full[K_STAGES], v_empty[K_STAGES];
+  uint64_t a_ready;                              // Q and dO are in TMEM
+  uint64_t s_full, s_free, dp_full, ds_full;     // one completion per block each: parity = block & 1
   uint64_t acc_done, drain;
   uint32_t tmem_base;
   int abort_flag;
 };
 // A K block serves S(i) early and dQ(i) late, so its slot is held for a whole iteration and a half: with two slots the
 // load of K(i+1) could only start when dQ(i-1) had finished and the MMA thread waited ~700 cycles per block for it.
-constexpr int Q_SMEM_TILES = 2 * BIG_BYTES + (K_STAGES + STAGES) * BLK_BYTES;
+constexpr int Q_SMEM_TILES = BIG_BYTES + 2 * K_STAGES * BLK_BYTES;       // dQ staging + K ring + V ring
 constexpr int Q_SMEM_TOTAL = Q_SMEM_TILES + 256 + 1024;
-// TMEM columns: S 0..127, dP(b) at 128 + b * 128 (dS, bf16, overwrites its first 64 columns), dQ 384
-constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 384;
+// TMEM columns: S 0..127, dP 128..255 (dS, bf16, overwrites its first 64 columns), dQ 256..383, Q 384..447, dO 448..511
+constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 256, COL_QA = 384, COL_DOA = 448;
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+flash_bwd_dq_kernel(const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* __restrict__ dog, int64_t q_row, int64_t do_row,
                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const __grid_constant__ CUtensorMap tmDQ, const float* __restrict__ lse2_pad,
                     const float* __restrict__ delta_pad, int Tq, int Tk, int Tq_pad, int H, int Hkv, int causal,
                     float scale, int* __restrict__ err, const __grid_constant__ SplitMaps dq_split, long long* __restrict__ dbg) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;
-  uint8_t* sD = smem + BIG_BYTES;
-  uint8_t* sKs = smem + 2 * BIG_BYTES;                    // K_STAGES K blocks
-  uint8_t* sVs = sKs + K_STAGES * BLK_BYTES;              // STAGES V blocks
+  uint8_t* sQ = smem;                                     // staging of the dQ tile for its TMA store
+  uint8_t* sKs = smem + BIG_BYTES;                        // K_STAGES K blocks
+  uint8_t* sVs = sKs + K_STAGES * BLK_BYTES;              // K_STAGES V blocks
   BarsQ* bars = (BarsQ*)(smem + Q_SMEM_TILES);
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -479,15 +480,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int total = causal ? min(nk, (q0 + BIG) / BLK) : nk;
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->qd_full, 1);
-    for (int s = 0; s < K_STAGES; ++s) { mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1); }
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1); }
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(&bars->k_full[s], 1); mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1); mbar_init(&bars->v_empty[s], 1);
+    }
+    mbar_init(&bars->a_ready, 256);
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->s_free, 256);
-    mbar_init(&bars->ds_full[0], 256);
-    mbar_init(&bars->ds_full[1], 256);
-    mbar_init(&bars->dp_full[0], 1);
-    mbar_init(&bars->dp_full[1], 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->ds_full, 256);
     mbar_init(&bars->acc_done, 1);
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
@@ -503,20 +504,14 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
    reg_dec<REGS_ISSUE>();
    if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(&bars->qd_full, 2 * BIG_BYTES);
-      tma_load_3d(sQ, &tmQ, 0, head, q0, &bars->qd_full);
-      tma_load_3d(sQ + BIG_HALF, &tmQ, 64, head, q0, &bars->qd_full);
-      tma_load_3d(sD, &tmDO, 0, head, q0, &bars->qd_full);
-      tma_load_3d(sD + BIG_HALF, &tmDO, 64, head, q0, &bars->qd_full);
       for (int it = 0; it < total; ++it) {
-        const int stage = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        const int kstage = it % K_STAGES;
-        if (!mbar_wait(&bars->k_empty[kstage], ((it / K_STAGES) & 1) ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
-        uint8_t* sK = sKs + kstage * BLK_BYTES;
-        mbar_expect_tx(&bars->k_full[kstage], BLK_BYTES);
-        tma_load_3d(sK, &tmK, 0, kvh, it * BLK, &bars->k_full[kstage]);
-        tma_load_3d(sK + BLK_HALF, &tmK, 64, kvh, it * BLK, &bars->k_full[kstage]);
+        const int stage = it % K_STAGES;
+        const uint32_t phase = (it / K_STAGES) & 1;
+        if (!mbar_wait(&bars->k_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        uint8_t* sK = sKs + stage * BLK_BYTES;
+        mbar_expect_tx(&bars->k_full[stage], BLK_BYTES);
+        tma_load_3d(sK, &tmK, 0, kvh, it * BLK, &bars->k_full[stage]);
+        tma_load_3d(sK + BLK_HALF, &tmK, 64, kvh, it * BLK, &bars->k_full[stage]);
         if (!mbar_wait(&bars->v_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
         uint8_t* sV = sVs + stage * BLK_BYTES;
         mbar_expect_tx(&bars->v_full[stage], BLK_BYTES);
@@ -524,64 +519,62 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_3d(sV + BLK_HALF, &tmV, 64, kvh, it * BLK, &bars->v_full[stage]);
       }
     }
-  } else if (warp == 1) {
+   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t IDESC_S = make_idesc_bf16(BIG, BLK, 0, 0);
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BIG, HD, 0, 1);
-      bool ok = mbar_wait(&bars->qd_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
-      const uint64_t qdesc0 = make_smem_desc(smem_u32(sQ), 16, 1024), ddesc0 = make_smem_desc(smem_u32(sD), 16, 1024);
+      bool ok = mbar_wait(&bars->a_ready, 0, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL);
+      tc_fence_after();
       const uint64_t k_k0 = make_smem_desc(smem_u32(sKs), 16, 1024), v_k0 = make_smem_desc(smem_u32(sVs), 16, 1024);
       const uint64_t k_mn0 = make_smem_desc(smem_u32(sKs), BLK_HALF, 1024);
-      // S(it) = Q K^T into the single S tile, dP(it) = dO V^T into dP buffer it & 1
-      auto issue_s_dp = [&](int it) -> bool {
-        const int stage = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        const int kstage = it % K_STAGES;
-        if (!mbar_wait(&bars->k_full[kstage], (it / K_STAGES) & 1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
+      const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+      // S(it) = Q K^T, Q from TMEM
+      auto issue_s = [&](int it) -> bool {
+        const int stage = it % K_STAGES;
+        if (!mbar_wait(&bars->k_full[stage], (it / K_STAGES) & 1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
         tc_fence_after();
-        const uint64_t kd = desc_advance(k_k0, kstage * BLK_BYTES);
+        const uint64_t kd = desc_advance(k_k0, stage * BLK_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
-          umma_ss(tmem + COL_S, desc_advance(qdesc0, off), desc_advance(kd, off), IDESC_S, kk > 0 ? 1u : 0u);
-        }
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_ts(tmem + COL_S, tmem + COL_QA + kk * 8, desc_advance(kd, (kk >> 2) * BLK_HALF + (kk & 3) * 32), IDESC_S, kk > 0 ? 1u : 0u);
         umma_commit(&bars->s_full);
-        if (!mbar_wait(&bars->v_full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
-        tc_fence_after();
-        const uint64_t vd = desc_advance(v_k0, stage * BLK_BYTES);
-        const uint32_t dcol = tmem + COL_DP + (it & 1) * 128;
-#pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
-          umma_ss(dcol, desc_advance(ddesc0, off), desc_advance(vd, off), IDESC_S, kk > 0 ? 1u : 0u);
-        }
-        umma_commit(&bars->v_empty[stage]);
-        umma_commit(&bars->dp_full[it & 1]);
         return true;
       };
-      if (ok && total > 0) ok = issue_s_dp(0);
-      const bool trace = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+      // dP(it) = dO V^T, dO from TMEM
+      auto issue_dp = [&](int it) -> bool {
+        const int stage = it % K_STAGES;
+        if (!mbar_wait(&bars->v_full[stage], (it / K_STAGES) & 1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        const uint64_t vd = desc_advance(v_k0, stage * BLK_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_ts(tmem + COL_DP, tmem + COL_DOA + kk * 8, desc_advance(vd, (kk >> 2) * BLK_HALF + (kk & 3) * 32), IDESC_S, kk > 0 ? 1u : 0u);
+        umma_commit(&bars->v_empty[stage]);
+        umma_commit(&bars->dp_full);
+        return true;
+      };
+      if (ok && total > 0) ok = issue_s(0) && issue_dp(0);
       for (int it = 0; it < total && ok; ++it) {
         const uint32_t par = it & 1;
         if (trace && it < 48) dbg[it * 8 + 0] = clock64();                 // loop start
         if (it + 1 < total) {
-          // S(it+1) overwrites S(it): the softmax warps must hold S(it) in registers.  dP(it+1) goes to the other
-          // dP buffer, whose dS(it-1) the in-order pipe has consumed with dQ(it-1).
+          // S(it+1) overwrites S(it): the softmax warps must hold S(it) in registers
           if (!mbar_wait(&bars->s_free, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
           if (trace && it < 48) dbg[it * 8 + 1] = clock64();               // S(it) freed
-          if (!issue_s_dp(it + 1)) { ok = false; break; }
-          if (trace && it < 48) dbg[it * 8 + 2] = clock64();               // S, dP(it+1) issued
+          if (!issue_s(it + 1)) { ok = false; break; }
+          if (trace && it < 48) dbg[it * 8 + 2] = clock64();               // S(it+1) issued
         }
-        if (!mbar_wait(&bars->ds_full[par], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        if (!mbar_wait(&bars->ds_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         if (trace && it < 48) dbg[it * 8 + 3] = clock64();                 // dS(it) seen
         tc_fence_after();
         const uint64_t kmn = desc_advance(k_mn0, (it % K_STAGES) * BLK_BYTES);
         const uint32_t acc0 = it > 0 ? 1u : 0u;
-        const uint32_t dsa = tmem + COL_DP + par * 128;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)   // dQ += dS K
-          umma_ts(tmem + COL_DQ, dsa + kk * 8, desc_advance(kmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+          umma_ts(tmem + COL_DQ, tmem + COL_DP + kk * 8, desc_advance(kmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
         umma_commit(&bars->k_empty[it % K_STAGES]);
+        // dP(it+1) overwrites dS(it), which the in-order pipe has consumed with dQ(it) by then
+        if (it + 1 < total && !issue_dp(it + 1)) { ok = false; break; }
       }
       if (ok) umma_commit(&bars->acc_done);
       else {
@@ -598,6 +591,24 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int r = q * 32 + lane;                          // query row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const float sl2 = scale * LOG2E;
+    {
+      // Q and dO rows of this thread, columns [hf * 64, hf * 64 + 64), into TMEM as bf16 pairs (rows past Tq are zero)
+      const bool live = q0 + r < Tq;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const __nv_bfloat16* src = (which == 0 ? qg + (int64_t)(q0 + r) * q_row : dog + (int64_t)(q0 + r) * do_row) + head * HD + hf * 64;
+        uint32_t a[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v4 = live ? *reinterpret_cast<const uint4*>(src + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+          a[4 * c] = v4.x; a[4 * c + 1] = v4.y; a[4 * c + 2] = v4.z; a[4 * c + 3] = v4.w;
+        }
+        tmem_st_32x32(tmem + (which == 0 ? COL_QA : COL_DOA) + hf * 32 + lane_off, a);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->a_ready);
+    }
     const int64_t srow = (int64_t)head * Tq_pad + q0 + r;  // Tq_pad is a multiple of 128: every tile row has an entry
     const float nlse2 = lse2_pad[srow], ndelta = delta_pad[srow];      // stored negated
     const uint64_t sl2_2 = pk2(sl2, sl2), nlse2_2 = pk2(nlse2, nlse2), ndelta_2 = pk2(ndelta, ndelta);
@@ -622,14 +633,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         float p0, p1;
-        const uint64_t x2 = fma2(pk2u(sv[2 * c], sv[2 * c + 1]), sl2_2, nlse2_2);
-        if ((c % ODY_BWD_POLY_DEN) < ODY_BWD_POLY_NUM) {
-          exp2_poly2(x2, p0, p1);
-        } else {
-          upk2(x2, p0, p1);
-          p0 = exp2_mufu(p0);
-          p1 = exp2_mufu(p1);
-        }
+        upk2(fma2(pk2u(sv[2 * c], sv[2 * c + 1]), sl2_2, nlse2_2), p0, p1);
+        p0 = exp2_mufu(p0);
+        p1 = exp2_mufu(p1);
         if (diag) {
           if (kvb0 + 2 * c > q0 + r) p0 = 0.f;
           if (kvb0 + 2 * c + 1 > q0 + r) p1 = 0.f;
@@ -642,14 +648,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         sv[2 * c + 1] = __float_as_uint(p1);
       }
       if (strace) dbg[it * 8 + 5] = clock64();                             // P computed (as far as the compiler kept it here)
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->dp_full[par], (it >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->dp_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
       if (strace) dbg[it * 8 + 6] = clock64();                             // dP(it) complete
       uint32_t dp[64];
-      const uint32_t dcol = tmem + COL_DP + par * 128;
       if (ok) {
         tc_fence_after();
-        tmem_ld_32x32(dcol + hf * 64 + lane_off, dp);
-        tmem_ld_32x32(dcol + hf * 64 + 32 + lane_off, dp + 32);
+        tmem_ld_32x32(tmem + COL_DP + hf * 64 + lane_off, dp);
+        tmem_ld_32x32(tmem + COL_DP + hf * 64 + 32 + lane_off, dp + 32);
         tmem_ld_wait();
       }
       // dS overwrites dP's first 64 columns: both warps of the quarter have loaded; they also agree on leaving
@@ -662,11 +667,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         upk2(mul2(pk2u(sv[2 * c], sv[2 * c + 1]), add2(pk2u(dp[2 * c], dp[2 * c + 1]), ndelta_2)), d0, d1);
         ds[c] = pack_bf16(d0, d1);
       }
-      tmem_st_32x16(dcol + hf * 32 + lane_off, ds);
-      tmem_st_32x16(dcol + hf * 32 + 16 + lane_off, ds + 16);
+      tmem_st_32x16(tmem + COL_DP + hf * 32 + lane_off, ds);
+      tmem_st_32x16(tmem + COL_DP + hf * 32 + 16 + lane_off, ds + 16);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars->ds_full[par]);
+      mbar_arrive(&bars->ds_full);
       if (strace) dbg[it * 8 + 7] = clock64();                             // dS published
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_done, 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
@@ -711,6 +716,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 }  // namespace ody
 
 static long long* g_bwd_trace = nullptr;
+// Optional per-block timelines (dK/dV kernel in the first 48 x 8 stamps, dQ kernel in the next 48 x 8)
 // Optional per-block timeline of CTA (0,0) of the dK/dV kernel: 48 x 8 SM-clock stamps (see the kernel).
 extern "C" void ody_flash_bwd_set_trace(long long* buf) { g_bwd_trace = buf; }
 
@@ -795,7 +801,7 @@ extern "C" int ody_flash_bwd_ex(const void* dO, const void* q, const void* k, co
   flash_bwd_dkdv_kernel<<<gkv, NUM_THREADS, KV_SMEM_TOTAL, st>>>(tQ, tDO, tK, tV, tDK, tDV, stat_tiles, Tq, Tk,
                                                                  Tpad, H, Hkv, causal, scale, err, g_bwd_trace, sk, sv);
   dim3 gq((Tq + BIG - 1) / BIG, H);
-  flash_bwd_dq_kernel<<<gq, NUM_THREADS, Q_SMEM_TOTAL, st>>>(tQ, tDO, tK, tV, tDQ, lse2_pad, delta_pad, Tq, Tk, Tpad, H,
-                                                             Hkv, causal, scale, err, sq, g_bwd_trace);
+  flash_bwd_dq_kernel<<<gq, NUM_THREADS, Q_SMEM_TOTAL, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)dO, q_row, do_row, tK, tV, tDQ, lse2_pad, delta_pad, Tq, Tk, Tpad, H,
+                                                             Hkv, causal, scale, err, sq, g_bwd_trace ? g_bwd_trace + 48 * 8 : nullptr);
   return (int)cudaGetLastError();
 }
