@@ -223,6 +223,7 @@ void ody_register_comm(pybind11::module& m) {
   m.def("wait_flags", &wait_flags);
   m.def("signal_flags", &signal_flags);
   m.def("signal_free", &signal_free);
+  m.def("set_push_order", [](bool unit_major) { req(ody_set_push_order(unit_major ? 1 : 0) == 0, "set_push_order failed"); });
   m.def("set_peer_wait_limit", [](int64_t cycles) { req(ody_set_peer_wait_limit(cycles) == 0, "set_peer_wait_limit failed"); });
   m.def("gemm_comm", &gemm_comm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("layout"), py::arg("gather"),
         py::arg("push"), py::arg("scatter"));

@@ -400,6 +400,10 @@ extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* 
                           err, st);
 }
 
+extern "C" int ody_flash_set_push_order(int unit_major) {
+  return (int)cudaMemcpyToSymbol(ody::gc::g_push_unit_major, &unit_major, sizeof(unit_major));
+}
+
 extern "C" int ody_flash_set_peer_wait_limit(long long cycles) {
   if (cycles <= 0) return (int)cudaErrorInvalidValue;
   return (int)cudaMemcpyToSymbol(ody::gc::g_peer_spin_limit, &cycles, sizeof(cycles));

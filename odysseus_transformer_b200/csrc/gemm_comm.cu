@@ -689,6 +689,13 @@ extern "C" int ody_signal_free(const OdyGatherDesc* d, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
+extern "C" int ody_set_push_order(int unit_major) {
+  const int v = unit_major ? 1 : 0;
+  int r = (int)cudaMemcpyToSymbol(ody::gc::g_push_unit_major, &v, sizeof(v));
+  if (r) return r;
+  return ody_flash_set_push_order(v);
+}
+
 extern "C" int ody_set_peer_wait_limit(long long cycles) {
   if (cycles <= 0) return (int)cudaErrorInvalidValue;
   int r = (int)cudaMemcpyToSymbol(ody::gc::g_peer_spin_limit, &cycles, sizeof(cycles));

@@ -127,6 +127,10 @@ int ody_flash_fwd_ex(const void* q, const void* k, const void* v, void* o, float
                      const OdyGatherDesc* push, void* const* o_split, int n_split, int split_rows, int64_t split_row, int* err,
                      cudaStream_t stream);
 int ody_flash_set_peer_wait_limit(long long cycles);
+int ody_flash_set_push_order(int unit_major);
+// schedule of the comm warps' pushes on the current device: 0 destination by destination (default), 1 every unit to all
+// destinations at once
+int ody_set_push_order(int unit_major);
 // bound (SM clock cycles) of every wait inside the fused kernels on the current device; default ~10 s
 int ody_set_peer_wait_limit(long long cycles);
 

@@ -10,7 +10,12 @@
 
 #include "ody_kernels.h"
 
-namespace ody { namespace gc { static __device__ long long g_peer_spin_limit = 20000000000ll; } }
+namespace ody { namespace gc {
+static __device__ long long g_peer_spin_limit = 20000000000ll;
+// 0: serve the destinations one after the other (default); 1: every unit to all destinations at once.  A run-time
+// switch so that the two schedules can be timed against each other (benchmarks/comm_bench.py --push-order).
+static __device__ int g_push_unit_major = 0;
+} }
 
 #include "sm100.cuh"
 
@@ -92,10 +97,9 @@ __device__ __forceinline__ bool wait_word(const uint32_t* p, uint32_t target, vo
 // ------------------------------------------------------------------------------------------- comm warps
 // The comm warps of CTA `cta` (of n_cta) push units cta, cta + n_cta, ... of this rank's shard.
 // unit = unit_rows x unit_cols elements.  Three data warps move 16-byte vectors, 8 loads in flight per
-// thread, and store every vector into all ranks' gathered buffers (own first).  The fourth warp is the
-// signaler: once the data warps have issued a unit (named barrier) it fences at system scope - which
-// waits for those stores to be acknowledged - and bumps that row block's arrival counter on every
-// destination, while the data warps are already moving the next unit.
+// thread.  The fourth warp is the signaler: once the data warps have issued a unit (named barrier) it
+// fences at system scope - which waits for those stores to be acknowledged - and bumps that row block's
+// arrival counter at the destination(s), while the data warps are already moving the next unit.
 constexpr int DATA_THREADS = COMM_THREADS - 32;
 static __device__ void comm_warps_main(const GatherParams& g, int cta, int n_cta, int first_thread, volatile int* abort_flag, int* err) {
   const int ct = threadIdx.x - first_thread;
@@ -118,43 +122,55 @@ static __device__ void comm_warps_main(const GatherParams& g, int cta, int n_cta
                  : "=r"(r) : "r"((uint32_t)ok) : "memory");
     if (!r) return;
   }
-  for (int u = cta; u < total_units; u += n_cta) {
-    const int blk = u / boxes, cb = u % boxes;
-    if (!signaler) {
-      for (int v0 = ct; v0 < nvec; v0 += DATA_THREADS * 8) {
-        uint4 val[8];
-        int64_t dst_off[8];
+  // Schedule.  Destination-major (default): the destinations are served one after the other, every unit of this CTA
+  // to the first before any to the second; when the shard goes to every rank the order is own, rank - 1, rank - 2,
+  // ...  A consumer walks the gathered rows upwards from its own shard, so the first data it needs from another
+  // rank are those of rank + 1, and this way it receives them first, at the full rate of that source, instead of an
+  // equal trickle from all sources that completes everywhere at the same late moment.  Unit-major: every unit is
+  // read once and stored to all destinations.
+  const bool everyone = g.dest_first == 0 && g.dest_count == g.n_ranks;
+  const bool unit_major = g_push_unit_major != 0;
+  auto dest = [&](int s) { return everyone ? (g.rank - s + g.n_ranks) % g.n_ranks : (g.rank + g.dest_first + s) % g.n_ranks; };
+  const int rounds = unit_major ? 1 : g.dest_count;          // destination groups served one after the other
+  const int per_round = unit_major ? g.dest_count : 1;
+  for (int round = 0; round < rounds; ++round) {
+    const int s0 = round * per_round;
+    for (int u = cta; u < total_units; u += n_cta) {
+      const int blk = u / boxes, cb = u % boxes;
+      if (!signaler) {
+        for (int v0 = ct; v0 < nvec; v0 += DATA_THREADS * 8) {
+          uint4 val[8];
+          int64_t dst_off[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int v = v0 + i * DATA_THREADS;
-          const int row = v / vpr, cv = v % vpr;
-          const int64_t rr = (int64_t)blk * UR + row;
-          dst_off[i] = (my_row0 + rr) * g.cols + cb * UC + cv * 8;
-          if (v < nvec) val[i] = *reinterpret_cast<const uint4*>(g.shard + rr * g.shard_ld + cb * UC + cv * 8);
-        }
-        for (int s = 0; s < g.dest_count; ++s) {
-          const int p = (g.rank + g.dest_first + s) % g.n_ranks;
-          __nv_bfloat16* base = g.gathered_peer[p];
+          for (int i = 0; i < 8; ++i) {
+            const int v = v0 + i * DATA_THREADS;
+            const int row = v / vpr, cv = v % vpr;
+            const int64_t rr = (int64_t)blk * UR + row;
+            dst_off[i] = (my_row0 + rr) * g.cols + cb * UC + cv * 8;
+            if (v < nvec) val[i] = *reinterpret_cast<const uint4*>(g.shard + rr * g.shard_ld + cb * UC + cv * 8);
+          }
+          for (int s = s0; s < s0 + per_round; ++s) {
+            __nv_bfloat16* base = g.gathered_peer[dest(s)];
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (v0 + i * DATA_THREADS < nvec) *reinterpret_cast<uint4*>(base + dst_off[i]) = val[i];
+            for (int i = 0; i < 8; ++i)
+              if (v0 + i * DATA_THREADS < nvec) *reinterpret_cast<uint4*>(base + dst_off[i]) = val[i];
+          }
         }
       }
+      named_barrier(3, COMM_THREADS);            // unit u has been issued by every data thread
+      if (ct == DATA_THREADS) {
+        __threadfence_system();
+        for (int s = s0; s < s0 + per_round; ++s) red_release_sys_add(g.flags_peer[dest(s)] + g.rank * nb + blk, 1);
+      }
     }
-    named_barrier(3, COMM_THREADS);            // unit u has been issued by every data thread
     if (ct == DATA_THREADS) {
       __threadfence_system();
-      const int idx = g.rank * nb + blk;
-      for (int s = 0; s < g.dest_count; ++s) red_release_sys_add(g.flags_peer[(g.rank + g.dest_first + s) % g.n_ranks] + idx, 1);
+      for (int s = s0; s < s0 + per_round; ++s) red_release_sys_add(g.counters_peer[dest(s)] + g.rank, 1);
     }
   }
-  if (ct == DATA_THREADS) {
-    __threadfence_system();
-    for (int s = 0; s < g.dest_count; ++s)
-      red_release_sys_add(g.counters_peer[(g.rank + g.dest_first + s) % g.n_ranks] + g.rank, 1);
-    if (g.stats != nullptr) g.stats[cta * 4 + 1] = global_ns();
-  }
+  if (ct == DATA_THREADS && g.stats != nullptr) g.stats[cta * 4 + 1] = global_ns();
 }
+
 
 
 // Host side: translate a description into kernel parameters.
