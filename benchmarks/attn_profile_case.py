@@ -1,5 +1,10 @@
+"""Small attention case for profiler captures: causal forward + backward, T = 16384, 8 heads, head_dim 128, twice.
+
+    python benchmarks/attn_profile_case.py        (used by the ncu command quoted in profiles/flash_attention_ncu.md)
+"""
 import math, torch, sys
-sys.path.insert(0,'.')
+import os
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from odysseus_transformer_b200.ops import native
 native.set_backend("fused"); lib=native.lib()
 T,H=16384,8

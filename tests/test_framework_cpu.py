@@ -195,3 +195,23 @@ def test_global_memory_buffer_reuses_storage():
     assert t1.data_ptr() == t2.data_ptr()
     t3 = b.get_tensor((16, 8), torch.float32, "mpu")
     assert t3.numel() == 128 and b.bytes_held() == 128 * 4
+
+
+def test_fused_paths_decline_on_cpu():
+    """The fused compute+collective paths are CUDA-only: on CPU tensors every gate says no and the modules import."""
+    import types
+
+    import torch
+    from odysseus_transformer_b200.comm import symm
+    from odysseus_transformer_b200.config import get_model_config
+    from odysseus_transformer_b200.ops import fused_comm, fused_ulysses
+
+    x = torch.zeros(128, 8, 128, dtype=torch.bfloat16)
+    assert not fused_comm.enabled(x, None)
+    assert not fused_comm.ring_enabled(x, object())
+    mod = types.SimpleNamespace(pctx=types.SimpleNamespace(inner_size=2, ring_size=1, inner_group=object(), world_group=object()),
+                                head_dim=128)
+    assert not fused_ulysses.available(mod, x)
+    cfg = get_model_config("llama2-7b")
+    small, big = symm.heap_bytes_estimate(cfg, 4096, 2), symm.heap_bytes_estimate(cfg, 8192, 8)
+    assert 0 < small < big < 64 << 30
