@@ -58,12 +58,17 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_k(const bf16* __restrict__ x,
   }
 }
 
+// Two rows per loop iteration and one barrier per iteration (the warps' partial dot products go through a
+// double-buffered shared array that every thread sums itself): the kernel is bound by memory latency, so what
+// matters is how many row loads are in flight between barriers.
 template <int NV>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_k(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                                                      const bf16* __restrict__ w, const float* __restrict__ rstd,
                                                      const bf16* __restrict__ ds, bf16* __restrict__ dx,
                                                      float* __restrict__ dw_partial, int64_t rows, int dim) {
-  __shared__ float red[33];
+  constexpr int R = NV <= 2 ? 2 : 1;      // wider rows would spill
+  __shared__ float red[2][R][8];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   float wv[NV][8], acc[NV][8];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -73,41 +78,66 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(const bf16* __restrict__ dy
     if (c < dim) unpack8(ld8(w + c), wv[i]);
   }
   const float inv_dim = 1.f / (float)dim;
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float rs = rstd[row];
-    float g[NV][8], xh[NV][8];
-    float dot = 0.f;
+  int par = 0;
+  for (int64_t row0 = (int64_t)blockIdx.x * R; row0 < rows; row0 += (int64_t)gridDim.x * R, par ^= 1) {
+    float g[R][NV][8], xh[R][NV][8], rs[R], dot[R];
+    bf16x8 pa[R][NV], px[R][NV];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = (threadIdx.x + i * blockDim.x) * 8;
-      if (c < dim) {
-        float a[8];
-        unpack8(ld8(dy + row * dim + c), a);
-        unpack8(ld8(x + row * dim + c), xh[i]);
+    for (int r = 0; r < R; ++r) {
+      const int64_t row = row0 + r;
+      rs[r] = row < rows ? rstd[row] : 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] *= rs;
-          acc[i][j] += a[j] * xh[i][j];
-          g[i][j] = a[j] * wv[i][j];
-          dot += g[i][j] * xh[i][j];
+      for (int i = 0; i < NV; ++i) {
+        const int c = (threadIdx.x + i * blockDim.x) * 8;
+        if (c < dim && row < rows) {
+          pa[r][i] = ld8(dy + row * dim + c);
+          px[r][i] = ld8(x + row * dim + c);
         }
       }
     }
-    dot = block_sum(dot, red) * inv_dim;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = (threadIdx.x + i * blockDim.x) * 8;
-      if (c < dim) {
-        float o[8];
+    for (int r = 0; r < R; ++r) {
+      dot[r] = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = (g[i][j] - xh[i][j] * dot) * rs;
-        if (ds != nullptr) {
-          float s[8];
-          unpack8(ld8(ds + row * dim + c), s);
+      for (int i = 0; i < NV; ++i) {
+        const int c = (threadIdx.x + i * blockDim.x) * 8;
+        if (c < dim && row0 + r < rows) {
+          float a[8];
+          unpack8(pa[r][i], a);
+          unpack8(px[r][i], xh[r][i]);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += s[j];
+          for (int j = 0; j < 8; ++j) {
+            xh[r][i][j] *= rs[r];
+            acc[i][j] += a[j] * xh[r][i][j];
+            g[r][i][j] = a[j] * wv[i][j];
+            dot[r] += g[r][i][j] * xh[r][i][j];
+          }
         }
-        st8(dx + row * dim + c, pack8(o));
+      }
+      dot[r] = warp_sum(dot[r]);
+      if (lane == 0) red[par][r][wid] = dot[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float4 lo = *reinterpret_cast<const float4*>(&red[par][r][0]), hi = *reinterpret_cast<const float4*>(&red[par][r][4]);
+      dot[r] = ((lo.x + lo.y) + (lo.z + lo.w) + (hi.x + hi.y) + (hi.z + hi.w)) * inv_dim;
+      const int64_t row = row0 + r;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = (threadIdx.x + i * blockDim.x) * 8;
+        if (c < dim && row < rows) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = (g[r][i][j] - xh[r][i][j] * dot[r]) * rs[r];
+          if (ds != nullptr) {
+            float s[8];
+            unpack8(ld8(ds + row * dim + c), s);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += s[j];
+          }
+          st8(dx + row * dim + c, pack8(o));
+        }
       }
     }
   }
@@ -122,12 +152,31 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(const bf16* __restrict__ dy
   }
 }
 
-__global__ void colsum_k(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int dim) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= dim) return;
-  float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(int64_t)b * dim + c];
-  out[c] = s;
+// out[c] = sum over the nblocks rows of partial[nblocks, dim].  Block = 32 columns x 8 row slices, so the grid has
+// dim / 32 blocks (not dim / 256, which left most SMs idle while a few walked all rows one after the other).
+__global__ void __launch_bounds__(256) colsum_k(const float* __restrict__ partial, float* __restrict__ out, int nblocks, int dim) {
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < dim) {
+    int b = slice;
+    for (; b + 24 < nblocks; b += 32) {
+      s0 += partial[(int64_t)b * dim + c];
+      s1 += partial[(int64_t)(b + 8) * dim + c];
+      s2 += partial[(int64_t)(b + 16) * dim + c];
+      s3 += partial[(int64_t)(b + 24) * dim + c];
+    }
+    for (; b < nblocks; b += 8) s0 += partial[(int64_t)b * dim + c];
+  }
+  red[slice][cx] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (slice == 0 && c < dim) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += red[i][cx];
+    out[c] = s;
+  }
 }
 
 // ------------------------------------------------------------------------------------------- RoPE
@@ -449,7 +498,7 @@ extern "C" int ody_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
                                         (bf16*)dx, dw_partial, rows, dim)
   if (nv <= 1) L(1); else if (nv <= 2) L(2); else if (nv <= 4) L(4); else L(8);
 #undef L
-  colsum_k<<<blocks_for(dim, 256), 256, 0, st>>>(dw_partial, dw, nb, dim);
+  colsum_k<<<blocks_for(dim, 32), 256, 0, st>>>(dw_partial, dw, nb, dim);
   return last_err();
 }
 
