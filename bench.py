@@ -2,7 +2,7 @@
 """Headline benchmark: Llama-2-7B training tokens/s in Odysseus mode, weak scaling L = 8K x #GPU.
 
 This is the reference's published weak-scaling benchmark (its README figure "Llama-2-7B, L = 8K x
-#GPU", reference README.md:43-45; the numbers are tabulated in this repo's BASELINE.md): bf16, global
+#GPU", reference README.md:43-45): bf16, global
 batch 1, no activation checkpointing, no offload, AdamW every step, random token ids, random-init
 weights of the Llama-2-7B architecture.  Here AdamW keeps fp32 master weights and moments.
 
@@ -31,7 +31,7 @@ os.environ.setdefault("TORCH_NCCL_AVOID_RECORD_STREAMS", "1")
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# published 8xA100 figures for this benchmark (tokens/s = 7 timed steps x L / elapsed), BASELINE.md table 2
+# published 8xA100 figures for this benchmark (tokens/s = 7 timed steps x L / elapsed; reference README.md:43-45)
 PUBLISHED_TOK_S = {("odysseus", 4): 8556.0, ("odysseus", 8): 12038.0, ("tpsp", 4): 8502.0, ("tpsp", 8): 11640.0}
 
 
