@@ -1,6 +1,6 @@
 """Small attention case for profiler captures: causal forward + backward, T = 16384, 8 heads, head_dim 128, twice.
 
-    python benchmarks/attn_profile_case.py        (used by the ncu command quoted in profiles/flash_attention_ncu.md)
+    python benchmarks/attn_profile_case.py        (small enough for a profiler capture: 3 kernels per pass, a few GB)
 """
 import math, torch, sys
 import os
