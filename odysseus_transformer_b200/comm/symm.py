@@ -325,17 +325,21 @@ class SymmetricHeap:
         return self._scatter[key][t]
 
 
-def heap_bytes_estimate(cfg, tokens_per_rank: int, n: int) -> int:
-    """Room for the activation gather / scatter slots and the largest weight gather / scatter slots."""
+def heap_bytes_estimate(cfg, tokens_per_rank: int, n: int, ring: bool = True, ulysses: bool = True) -> int:
+    """Room for the activation gather / scatter slots and the largest weight gather / scatter slots, plus - when the
+    mode uses them - ring attention's gathered K|V and dK|dV inboxes and the Ulysses receive buffers (two of each)."""
     d, i = cfg.hidden_size, cfg.intermediate_size
     act = n * tokens_per_rank * d * 2
     weights = (2 * i * d + d * i + cfg.vocab_size * d) * 2
-    kv = n * tokens_per_rank * 2 * cfg.num_key_value_heads * cfg.head_dim * 2     # ring attention's gathered K|V
-    a2a = 2 * (2 * (cfg.q_size + 2 * cfg.kv_size) + 2 * cfg.q_size) * tokens_per_rank * 2   # Ulysses receive buffers, two of each
-    return 2 * (2 * act) + 2 * (2 * weights) + 4 * kv + a2a + (64 << 20)     # kv: gathered K|V and dK|dV inboxes, two of each
+    total = 2 * (2 * act) + 2 * (2 * weights) + (64 << 20)
+    if ring:
+        total += 4 * n * tokens_per_rank * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+    if ulysses:
+        total += 2 * (2 * (cfg.q_size + 2 * cfg.kv_size) + 2 * cfg.q_size) * tokens_per_rank * 2
+    return total
 
 
-def setup_fused_comm(ctx, cfg=None, tokens_per_rank: int = 0, data_bytes: int = 0) -> bool:
+def setup_fused_comm(ctx, cfg=None, tokens_per_rank: int = 0, data_bytes: int = 0, mode: Optional[str] = None) -> bool:
     """Create and register the symmetric heaps for ``ctx``'s groups.  Returns False (leaving the NCCL
     composition in place) when the world is a single rank, the device is not CUDA, or peer memory
     cannot be set up."""
@@ -351,7 +355,12 @@ def setup_fused_comm(ctx, cfg=None, tokens_per_rank: int = 0, data_bytes: int = 
         if fused_comm.heap_for(g) is not None:
             ok = True
             continue
-        nbytes = data_bytes or (heap_bytes_estimate(cfg, tokens_per_rank, dist.get_world_size(g)) if cfg is not None else (1 << 30))
+        # ``mode`` (when given) leaves out what that mode never allocates: K|V slots without a ring, receive buffers
+        # outside Ulysses.  (A ring block holds inner_size x more tokens but 1 / inner_size of the heads: same bytes.)
+        want_ring = ctx.ring_size > 1 or mode is None
+        want_ulysses = mode in (None, "ulysses") and ctx.inner_size > 1
+        nbytes = data_bytes or (heap_bytes_estimate(cfg, tokens_per_rank, dist.get_world_size(g), want_ring, want_ulysses)
+                                if cfg is not None else (1 << 30))
         try:
             heap = SymmetricHeap(g, ctx.device, nbytes)
         except Exception as e:  # noqa: BLE001

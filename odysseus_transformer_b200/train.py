@@ -65,7 +65,7 @@ class Trainer:
         set_global_memory_buffer(ctx.device)
         if ctx.world_size > 1 and ctx.device.type == "cuda" and native.get_backend() != "library" and dtype == torch.bfloat16:
             from .comm import symm
-            symm.setup_fused_comm(ctx, cfg, max(1, seq_length // ctx.world_size))
+            symm.setup_fused_comm(ctx, cfg, max(1, seq_length // ctx.world_size), mode=mode)
         self.model = build_model(cfg, mode, ctx, dtype=dtype, device=ctx.device, seed=seed, state_dict=state_dict)
         if grad_checkpoint:
             self.model.gradient_checkpointing_enable()
