@@ -370,4 +370,8 @@ def setup_fused_comm(ctx, cfg=None, tokens_per_rank: int = 0, data_bytes: int = 
         fused_comm.register_heap(g, heap)
         ok = True
     ctx.symm = ok
+    if ok and ctx.wait_acc is None:
+        # the fused kernels add the time they spend waiting on other GPUs here (utils.metrics.exposed_comm_ms)
+        ctx.wait_acc = torch.zeros(4, dtype=torch.int64, device=ctx.device)
+        native.lib().set_wait_accumulator(ctx.wait_acc)
     return ok

@@ -216,14 +216,22 @@ void ce_bwd_(at::Tensor logits, const at::Tensor& targets, const at::Tensor& lse
 
 // ------------------------------------------------------------------------------------------- AdamW
 void adamw_step(at::Tensor master, at::Tensor m, at::Tensor v, const at::Tensor& grad, at::Tensor param, double lr,
-                double beta1, double beta2, double eps, double weight_decay, int64_t step, double grad_scale) {
+                double beta1, double beta2, double eps, double weight_decay, int64_t step, double grad_scale,
+                const c10::optional<at::Tensor>& guard) {
   check_bf16(grad, "grad"); check_bf16(param, "param");
+  const float* gp = nullptr;
+  if (guard.has_value()) {
+    const at::Tensor& g = guard.value();
+    ody_req(g.is_cuda() && g.scalar_type() == at::kFloat && g.numel() >= 1 && g.get_device() == master.get_device(),
+            "adamw guard must be a float32 CUDA tensor on the optimizer's device");
+    gp = g.data_ptr<float>();
+  }
   ody_req(master.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
   ody_req(master.is_contiguous() && m.is_contiguous() && v.is_contiguous() && grad.is_contiguous() && param.is_contiguous());
-  c10::cuda::CUDAGuard guard(master.device());
+  c10::cuda::CUDAGuard dev_guard(master.device());
   ODY_CHECK(ody_adamw(master.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), grad.data_ptr(), param.data_ptr(),
                       master.numel(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)weight_decay, (int)step,
-                      (float)grad_scale, cur_stream()), "adamw");
+                      (float)grad_scale, gp, cur_stream()), "adamw");
   ++g_launches;
 }
 
@@ -290,6 +298,15 @@ int64_t status(int64_t device) {
   return t.cpu().data_ptr<int>()[0];
 }
 
+// The device-resident status words themselves (int32[16], word 0 = first error code), creating them if needed:
+// lets a training step fold the status into a collective or an optimizer guard without a host read.
+at::Tensor status_tensor(const at::Tensor& like) {
+  ody_req(like.is_cuda(), "status_tensor needs a CUDA tensor");
+  status_ptr(like);
+  std::lock_guard<std::mutex> g(g_mu);
+  return g_status.find(like.get_device())->second;
+}
+
 void clear_status(int64_t device) {
   std::lock_guard<std::mutex> g(g_mu);
   auto it = g_status.find((int)device);
@@ -322,12 +339,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd_", &ce_bwd_);
-  m.def("adamw_step", &adamw_step);
+  m.def("adamw_step", &adamw_step, py::arg("master"), py::arg("m"), py::arg("v"), py::arg("grad"), py::arg("param"),
+        py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"),
+        py::arg("grad_scale"), py::arg("guard") = py::none());
   m.def("attn_merge_", &attn_merge_);
   m.def("sum_rows_", &sum_rows_);
   m.def("attn_merge_parts", &attn_merge_parts);
   m.def("status", &status);
   m.def("clear_status", &clear_status);
+  m.def("status_tensor", &status_tensor);
   m.def("launch_count", &launch_count);
   m.def("reset_launch_count", &reset_launch_count);
   m.def("add_launches", &add_launches);

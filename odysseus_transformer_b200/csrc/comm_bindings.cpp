@@ -206,17 +206,10 @@ void push_shard(const py::dict& push) {
 }
 
 // dst / src are raw device addresses (possibly of a peer's symmetric memory)
-void peer_copy(int64_t dst, int64_t src, int64_t bytes, int64_t n_ctas, int64_t threads) {
-  int rc = ody_peer_copy(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src), bytes, (int)n_ctas, (int)threads,
-                         at::cuda::getCurrentCUDAStream().stream());
-  req(rc == 0, "peer_copy failed with code " + std::to_string(rc));
-  ody_count_launches(1);
-}
 
 }  // namespace
 
 void ody_register_comm(pybind11::module& m) {
-  m.def("peer_copy", &peer_copy);
   m.def("push_shard", &push_shard);
   m.def("attn_fwd_push", &attn_fwd_push);
   m.def("wait_shard", &wait_shard);
@@ -224,6 +217,13 @@ void ody_register_comm(pybind11::module& m) {
   m.def("signal_flags", &signal_flags);
   m.def("signal_free", &signal_free);
   m.def("set_push_order", [](bool unit_major) { req(ody_set_push_order(unit_major ? 1 : 0) == 0, "set_push_order failed"); });
+  m.def("set_wait_accumulator", [](const py::object& acc) {
+    if (acc.is_none()) { req(ody_set_wait_accumulator(nullptr) == 0, "set_wait_accumulator failed"); return; }
+    at::Tensor t = acc.cast<at::Tensor>();
+    req(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous() && t.numel() >= 4, "wait accumulator: int64 CUDA tensor [>= 4]");
+    c10::cuda::CUDAGuard guard(t.device());
+    req(ody_set_wait_accumulator(reinterpret_cast<unsigned long long*>(t.data_ptr())) == 0, "set_wait_accumulator failed");
+  });
   m.def("set_peer_wait_limit", [](int64_t cycles) { req(ody_set_peer_wait_limit(cycles) == 0, "set_peer_wait_limit failed"); });
   m.def("gemm_comm", &gemm_comm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("layout"), py::arg("gather"),
         py::arg("push"), py::arg("scatter"));

@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(const bf16* __restrict__ dy
                                                      const bf16* __restrict__ ds, bf16* __restrict__ dx,
                                                      float* __restrict__ dw_partial, int64_t rows, int dim) {
   constexpr int R = NV <= 2 ? 2 : 1;      // wider rows would spill
-  __shared__ float red[2][R][8];
+  __shared__ __align__(16) float red[2][R][8];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   float wv[NV][8], acc[NV][8];
 #pragma unroll
@@ -317,9 +317,13 @@ __global__ void ce_bwd_k(bf16* __restrict__ logits, const int64_t* __restrict__ 
 
 __global__ void adamw_k(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                         const bf16* __restrict__ grad, bf16* __restrict__ param, int64_t n, float decay, float beta1,
-                        float beta2, float step_size, float inv_sqrt_bc2, float eps, float grad_scale) {
+                        float beta2, float step_size, float inv_sqrt_bc2, float eps, float grad_scale,
+                        const float* __restrict__ guard) {
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i >= n) return;
+  // a non-zero guard word (the step's kernel status, summed over ranks) means some gradient is incomplete:
+  // leave master, moments and parameters untouched so the host can stop or restart from here
+  if (guard != nullptr && *guard != 0.f) return;
   float g[8];
   unpack8(ld8(grad + i), g);
   float4 w0 = *reinterpret_cast<float4*>(master + i), w1 = *reinterpret_cast<float4*>(master + i + 4);
@@ -553,14 +557,14 @@ extern "C" int ody_ce_bwd(void* logits, const int64_t* targets, const float* lse
 
 extern "C" int ody_adamw(float* master, float* m, float* v, const void* grad, void* param, int64_t n, float lr,
                          float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale,
-                         cudaStream_t st) {
+                         const float* guard, cudaStream_t st) {
   if (n % 8 != 0) return (int)cudaErrorInvalidValue;
   if (n == 0) return 0;
   const double bc1 = 1.0 - pow((double)beta1, (double)step);
   const double bc2 = 1.0 - pow((double)beta2, (double)step);
   adamw_k<<<blocks_for(n / 8, 256), 256, 0, st>>>(master, m, v, (const bf16*)grad, (bf16*)param, n,
                                                   1.f - lr * weight_decay, beta1, beta2, (float)(lr / bc1),
-                                                  (float)(1.0 / sqrt(bc2)), eps, grad_scale);
+                                                  (float)(1.0 / sqrt(bc2)), eps, grad_scale, guard);
   return last_err();
 }
 

@@ -57,6 +57,7 @@ struct ScatterParams {
   // stage_peer[o] at row a2a_row0 + r, column a2a_col0 + (c - o * a2a_cols), row pitch a2a_ld
   int a2a_cols;
   int64_t a2a_ld, a2a_row0, a2a_col0;
+  unsigned long long* wait_acc;           // optional running totals (ns): [1] += the time owners waited for the sources' tiles
 };
 
 struct Bars {
@@ -197,6 +198,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; int issued = 0; bool ok = true; int last_ok = -1; uint32_t done_mask = 0, ctr_checked = 0;
       unsigned long long waited_ns = 0;
+      const bool timed = GATHER && (gp.stats != nullptr || gp.wait_acc != nullptr);
       const uint32_t all_ranks_mask = GATHER ? ((1u << gp.n_ranks) - 1u) : 0u;
       for (int tile = gemm_idx; tile < num_tiles && ok; tile += n_gemm) {
         int tm, tn;
@@ -211,18 +213,18 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (done_mask == all_ranks_mask) fence_proxy_async_all();
         }
         if (G_ROWS_M || G_ROWS_N) {
-          const unsigned long long t0 = (GATHER && gp.stats) ? global_ns() : 0;
+          const unsigned long long t0 = (GATHER && timed) ? global_ns() : 0;
           if (G_ROWS_M && !wait_rows(gp, m0, BM, last_ok, done_mask, ctr_checked, bars->seen, 1, abort_flag, err)) { ok = false; break; }
           if (G_ROWS_N && !wait_rows(gp, n0, BN, last_ok, done_mask, ctr_checked, bars->seen, 1, abort_flag, err)) { ok = false; break; }
-          if (GATHER && gp.stats) waited_ns += global_ns() - t0;
+          if (GATHER && timed) waited_ns += global_ns() - t0;
         }
         for (int kb = 0; kb < kblocks; ++kb) {
           int kbr = kb + shift_k; if (kbr >= kblocks) kbr -= kblocks;
           const int k0 = kbr * BK;
           if (G_ROWS_K && done_mask != all_ranks_mask) {
-            const unsigned long long t0 = gp.stats ? global_ns() : 0;
+            const unsigned long long t0 = timed ? global_ns() : 0;
             if (!wait_rows(gp, k0, BK, last_ok, done_mask, ctr_checked, bars->seen, 16, abort_flag, err)) { ok = false; break; }
-            if (gp.stats) waited_ns += global_ns() - t0;
+            if (timed) waited_ns += global_ns() - t0;
           }
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) { ok = false; break; }
           uint8_t* sA = smem + stage * STAGE_BYTES;
@@ -245,6 +247,7 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
       if (GATHER && gp.stats) gp.stats[gemm_idx * 4 + 2] = waited_ns;
+      if (GATHER && gp.wait_acc != nullptr && waited_ns) atomicAdd(gp.wait_acc, waited_ns);
       if (!ok || *abort_flag) {
         int n = issued < STAGES ? issued : STAGES;
         for (int i = 0; i < n; ++i) {
@@ -437,8 +440,11 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     } else if (alive) {
       // reduce this rank's rows over the N source slots once every source has delivered all its tiles
       bool ok = true;
+      const unsigned long long tw0 = (sp.wait_acc != nullptr && et == 0) ? global_ns() : 0;
       if (et < sp.n_ranks) ok = wait_word<true>(sp.arrived_local + et, sp.arrived_target, abort_flag, err, ODY_ERR_TIMEOUT_PEER);
-      if (epi_all_ok(ok)) {
+      const bool all_ok = epi_all_ok(ok);
+      if (sp.wait_acc != nullptr && et == 0) atomicAdd(sp.wait_acc + 1, global_ns() - tw0);
+      if (all_ok) {
         const __nv_bfloat16* mine = sp.stage_peer[sp.rank];
         const int vec_per_row = N / 8;
         const int64_t total = (int64_t)sp.chunk_rows * vec_per_row;
@@ -521,6 +527,13 @@ namespace ody {
 namespace gc {
 
 static int g_sms = 0;
+// per-device running totals of time spent waiting on other GPUs (ody_set_wait_accumulator); null = not collected
+static unsigned long long* g_wait_acc[64] = {nullptr};
+static unsigned long long* wait_acc_here() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  return g_wait_acc[dev];
+}
 
 template <int LAYOUT, int GATHER, int SCATTER>
 static int launch(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
@@ -557,6 +570,7 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
   bool has_push = false;
   if (GATHER) {
     if ((r = fill_gather(gp, gd))) return r;
+    gp.wait_acc = wait_acc_here();
     if (pd != nullptr) {
       if ((r = fill_gather(pp, pd))) return r;
       if (pd->shard == nullptr || (pd->shard_ld % 8) || ((uintptr_t)pd->shard & 15)) return (int)cudaErrorInvalidValue;
@@ -582,6 +596,7 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
     sp.out_ld = sd->out_ld;
     sp.n_ranks = sd->n_ranks; sp.rank = sd->rank; sp.chunk_rows = sd->chunk_rows;
     sp.epoch = sd->epoch; sp.prev_epoch = sd->prev_epoch;
+    sp.wait_acc = wait_acc_here();
     // C is only a placeholder for the tensor map in this mode: staging is dense with ld = N
     ldc = N;
     C = sd->stage_peer[sd->rank];
@@ -632,17 +647,22 @@ extern "C" int ody_push_shard(const OdyGatherDesc* pd, int* err, cudaStream_t st
 
 namespace ody {
 namespace gc {
-__global__ void wait_shard_kernel(const uint32_t* counter, uint32_t target, int* err) {
+__global__ void wait_shard_kernel(const uint32_t* counter, uint32_t target, int* err, unsigned long long* acc) {
   __shared__ int abort_flag;
   abort_flag = 0;
+  const unsigned long long t0 = acc ? global_ns() : 0;
   wait_word<true>(counter, target, &abort_flag, err, ODY_ERR_TIMEOUT_PEER);
+  if (acc) atomicAdd(acc + 2, global_ns() - t0);     // the stream does nothing else meanwhile: all of it is exposed
 }
 struct PtrList { uint32_t* p[MAX_RANKS]; };
-__global__ void wait_flags_kernel(const uint32_t* base, uint32_t mask, uint32_t target, int* err) {
+__global__ void wait_flags_kernel(const uint32_t* base, uint32_t mask, uint32_t target, int* err, unsigned long long* acc) {
   __shared__ int abort_flag;
   if (threadIdx.x == 0) abort_flag = 0;
   __syncthreads();
+  const unsigned long long t0 = acc ? global_ns() : 0;
   if ((mask >> threadIdx.x) & 1u) wait_word<true>(base + threadIdx.x, target, &abort_flag, err, ODY_ERR_TIMEOUT_PEER);
+  __syncthreads();
+  if (acc && threadIdx.x == 0) atomicAdd(acc + 2, global_ns() - t0);
 }
 __global__ void signal_flags_kernel(const __grid_constant__ PtrList l, uint32_t mask, int index, uint32_t value) {
   __threadfence_system();
@@ -658,14 +678,14 @@ __global__ void signal_free_kernel(const __grid_constant__ GatherParams g) {
 extern "C" int ody_wait_shard(const OdyGatherDesc* d, int src, int* err, cudaStream_t st) {
   using namespace ody::gc;
   if (d == nullptr || src < 0 || src >= d->n_ranks) return (int)cudaErrorInvalidValue;
-  wait_shard_kernel<<<1, 1, 0, st>>>(d->counters_peer[d->rank] + src, d->push_total, err);
+  wait_shard_kernel<<<1, 1, 0, st>>>(d->counters_peer[d->rank] + src, d->push_total, err, wait_acc_here());
   return (int)cudaGetLastError();
 }
 
 extern "C" int ody_wait_flags(const uint32_t* base, uint32_t mask, uint32_t target, int* err, cudaStream_t st) {
   if (base == nullptr) return (int)cudaErrorInvalidValue;
   if (mask == 0) return 0;
-  ody::gc::wait_flags_kernel<<<1, 32, 0, st>>>(base, mask, target, err);
+  ody::gc::wait_flags_kernel<<<1, 32, 0, st>>>(base, mask, target, err, ody::gc::wait_acc_here());
   return (int)cudaGetLastError();
 }
 
@@ -687,6 +707,18 @@ extern "C" int ody_signal_free(const OdyGatherDesc* d, cudaStream_t st) {
   if (r) return r;
   signal_free_kernel<<<1, 32, 0, st>>>(g);
   return (int)cudaGetLastError();
+}
+
+// acc: device uint64[4] on the current device that the fused kernels add their waiting times to (ns), or NULL to stop:
+// [0] gather GEMMs, summed over CTAs: TMA producers waiting for remote rows; [1] reduce-scatter GEMMs, one thread per
+// CTA: owners waiting for the sources' tiles; [2] the stand-alone wait kernels (the stream is idle for all of it).
+extern "C" int ody_set_wait_accumulator(unsigned long long* acc) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+  ody::gc::g_wait_acc[dev] = acc;
+  return 0;
 }
 
 extern "C" int ody_set_push_order(int unit_major) {

@@ -36,9 +36,11 @@ int ody_ce_fwd(const void* logits, const int64_t* targets, float* loss, float* l
 int ody_ce_bwd(void* logits, const int64_t* targets, const float* lse, const float* scale, int64_t T, int64_t V,
                int64_t ignore_index, cudaStream_t stream);
 
-// ---- AdamW on flat shards: fp32 master / m / v, bf16 grad in, bf16 param out.
+// ---- AdamW on flat shards: fp32 master / m / v, bf16 grad in, bf16 param out.  guard (device, may be null):
+// when *guard != 0 at run time the kernel changes nothing (a failed step must not reach the master weights).
 int ody_adamw(float* master, float* m, float* v, const void* grad, void* param, int64_t n, float lr, float beta1,
-              float beta2, float eps, float weight_decay, int step, float grad_scale, cudaStream_t stream);
+              float beta2, float eps, float weight_decay, int step, float grad_scale, const float* guard,
+              cudaStream_t stream);
 
 // ---- merge of two partial attention results (ring attention): out/lse fp32 running, o bf16 / l fp32 partial
 int ody_attn_merge(float* out, float* lse, const void* o, const float* l, int64_t T, int H, int hd, int64_t row0,
@@ -134,8 +136,9 @@ int ody_set_push_order(int unit_major);
 // bound (SM clock cycles) of every wait inside the fused kernels on the current device; default ~10 s
 int ody_set_peer_wait_limit(long long cycles);
 
-// ---- copy between (peer-mapped) device buffers with plain 16-byte loads/stores on n_ctas x threads threads
-int ody_peer_copy(void* dst, const void* src, int64_t bytes, int n_ctas, int threads, cudaStream_t stream);
+// running totals (ns) of the time the fused kernels of the current device spend waiting on other GPUs; see gemm_comm.cu
+int ody_set_wait_accumulator(unsigned long long* acc);
+
 
 #ifdef __cplusplus
 }

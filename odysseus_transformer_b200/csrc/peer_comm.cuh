@@ -46,6 +46,7 @@ struct GatherParams {
   uint32_t counter_target;      // cumulative: CTAs per launch summed over uses
   uint32_t gemm_done_target;    // same number: every CTA reports once per launch
   unsigned long long* stats;    // optional [n_cta][4] ns: comm begin, comm end, time the producer spent waiting for rows, CTA end
+  unsigned long long* wait_acc; // optional running totals (ns): [0] += the time this launch's producers waited for remote rows
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {

@@ -68,6 +68,7 @@ class ParallelContext:
     ring_group: Optional[object] = None
     backend: str = "library"       # "library": torch ops + torch.distributed ; "fused": sm_100a kernels
     symm: Optional[object] = None  # symmetric-memory heap (comm.symm.SymmetricHeap) when peer access is set up
+    wait_acc: Optional[torch.Tensor] = None   # int64[4] device totals (ns) of the fused kernels' waits on other GPUs
 
     @property
     def inner_rank(self) -> int:

@@ -7,7 +7,8 @@ its checkpoint format but is built directly in the requested parallel mode:
 ====================  ==========================  ===========================
 mode                  attention block             MLP block
 ====================  ==========================  ===========================
-odysseus (+ring)      ``TPSPAttention``           ``OdysseusMLP`` (ZeRO-3)
+odysseus (+ring)      ``TPSPAttention``           ``OdysseusMLP`` (ZeRO-3), or
+                                                  ``ReplicatedMLP`` with ``use_zero3_linear=False``
 tpsp                  ``TPSPAttention``           ``TPSPMLP``
 ulysses (+ring)       ``SequenceParallelAttention`` ``OdysseusMLP`` (ZeRO-3)
 ring                  ``RingAttention``           ``OdysseusMLP`` (ZeRO-3)
@@ -36,7 +37,7 @@ from ..config import ModelConfig
 from ..mesh import ParallelContext, get_context
 from ..ops import functional as F
 from ..parallel.linear import LinearZeRO3, Zero3Schedule, zero3_embedding
-from ..parallel.odysseus import OdysseusMLP
+from ..parallel.odysseus import OdysseusMLP, ReplicatedMLP
 from ..parallel.ring import RingAttention
 from ..parallel.tpsp import TPSPAttention, TPSPMLP
 from ..parallel.ulysses import SequenceParallelAttention
@@ -44,7 +45,7 @@ from ..parallel.ulysses import SequenceParallelAttention
 
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, ctx: ParallelContext, mode: Optional[str], layer_idx: int,
-                 sched: Optional[Zero3Schedule], dtype, device):
+                 sched: Optional[Zero3Schedule], dtype, device, use_zero3_linear: bool = True):
         super().__init__()
         d = cfg.hidden_size
         self.eps = cfg.rms_norm_eps
@@ -58,6 +59,8 @@ class DecoderLayer(nn.Module):
         self.post_attention_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         if mode == "tpsp":
             self.mlp = TPSPMLP(cfg, ctx, dtype=dtype, device=device)
+        elif mode == "odysseus" and not use_zero3_linear:
+            self.mlp = ReplicatedMLP(cfg, ctx, dtype=dtype, device=device)
         else:
             self.mlp = OdysseusMLP(cfg, ctx, sched, dtype=dtype, device=device)
         for p in (self.input_layernorm, self.post_attention_layernorm):
@@ -76,8 +79,9 @@ class DecoderLayer(nn.Module):
 
 class LlamaForCausalLM(nn.Module):
     def __init__(self, cfg: ModelConfig, mode: Optional[str] = None, ctx: Optional[ParallelContext] = None,
-                 dtype: torch.dtype = torch.float32, device=None):
+                 dtype: torch.dtype = torch.float32, device=None, use_zero3_linear: bool = True):
         super().__init__()
+        self.use_zero3_linear = use_zero3_linear
         if cfg.tie_word_embeddings:
             raise NotImplementedError("tied embeddings are not supported (Llama-2/3 do not tie)")
         ctx = ctx if ctx is not None else get_context()
@@ -91,7 +95,8 @@ class LlamaForCausalLM(nn.Module):
         self.zero3 = Zero3Schedule()
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size // n, cfg.hidden_size, dtype=dtype, device=device))
         self.layers = nn.ModuleList(
-            [DecoderLayer(cfg, ctx, mode, i, self.zero3, dtype, device) for i in range(cfg.num_hidden_layers)])
+            [DecoderLayer(cfg, ctx, mode, i, self.zero3, dtype, device, use_zero3_linear)
+             for i in range(cfg.num_hidden_layers)])
         self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
         self.norm.grad_sync_group = ctx.world_group
         self.lm_head = LinearZeRO3(cfg.hidden_size, cfg.vocab_size, ctx.world_group, self.zero3, dtype=dtype, device=device)

@@ -243,11 +243,16 @@ class _FusedZero3Linear(Function):
         ctx.save_for_backward(x, w)
         x = x if x.stride(-1) == 1 else x.contiguous()
         slot, nxt_w, nxt = _chain(sched, heap, idx, +1, w.detach())
-        y, _, nslot = _gather_gemm(heap, w.detach(), 2, x, 0, slot=slot, prefetch=nxt_w)
+        y, full, nslot = _gather_gemm(heap, w.detach(), 2, x, 0, slot=slot, prefetch=nxt_w)
         if nslot is not None:
             sched._fused_prefetched[nxt] = nslot
         if y is None:
-            y = F.gemm_nt(x, C.all_gather_rows(w.detach(), group))
+            full = C.all_gather_rows(w.detach(), group)
+            y = F.gemm_nt(x, full)
+        if sched is not None and sched.keep_gathered and any(ctx.needs_input_grad):
+            # ZeRO-2 style (the reference's --use_zero2, train.py:137-141): the whole weight stays resident until
+            # this layer's backward, which then needs no second gather.  The slot itself is recycled, so copy.
+            sched._kept[idx] = full.clone()
         return y
 
     @staticmethod
@@ -258,6 +263,10 @@ class _FusedZero3Linear(Function):
         group, sched, idx = ctx.group, ctx.sched, ctx.idx
         heap = heap_for(group)
         dy = dy.contiguous()
+        kept = sched._kept.pop(idx, None) if (sched is not None and sched.keep_gathered) else None
+        if kept is not None:
+            dx = F.gemm_nn(dy, kept) if ctx.needs_input_grad[0] else None
+            return dx, zero3_wgrad(heap, group, w, dy, x), None, None, None
         slot, nxt_w, nxt = _chain(sched, heap, idx, -1, w.detach())
         dx = None
         if ctx.needs_input_grad[0] or slot is not None:

@@ -90,6 +90,39 @@ def launch_count() -> int:
     return int(lib().launch_count()) if available() else 0
 
 
+class KernelStatusError(RuntimeError):
+    """A bounded device-side wait gave up (codes in ``csrc/sm100.cuh``: 101-104 pipeline stages of one
+    kernel, 105 a flag another GPU never set, 106 other)."""
+
+    def __init__(self, status: int, where: str = ""):
+        super().__init__(f"odysseus_transformer_b200 kernel reported status {status} "
+                         f"(a bounded device-side wait expired){' ' + where if where else ''}")
+        self.status = status
+
+
+_status_source = None   # test hook: callable(device) -> 1-element tensor standing in for the device status word
+
+
+def set_status_source(fn) -> None:
+    """Replace the device status word by ``fn(device) -> tensor`` (``None`` restores the real one).
+    Tests use it to exercise the failure branch of the training step without a failing kernel."""
+    global _status_source
+    _status_source = fn
+
+
+def status_tensor(device):
+    """The status word of ``device`` as a tensor on that device (first element), or ``None`` when there is
+    none: no extension, or a CPU device without a test hook.  Reading it here costs no synchronisation, so a
+    training step can fold it into a collective or hand it to the optimizer kernel as its guard."""
+    if _status_source is not None:
+        return _status_source(device)
+    import torch
+    device = torch.device(device)
+    if device.type != "cuda" or _backend == "library" or not available():
+        return None
+    return lib().status_tensor(torch.empty(0, device=device))
+
+
 def check_status(device_index: int = 0) -> None:
     """Raise if a bounded in-kernel wait gave up since the last check (codes in csrc/sm100.cuh)."""
     if not available():
@@ -97,4 +130,4 @@ def check_status(device_index: int = 0) -> None:
     st = int(lib().status(device_index))
     if st != 0:
         lib().clear_status(device_index)
-        raise RuntimeError(f"odysseus_transformer_b200 kernel reported status {st} (a bounded device-side wait expired)")
+        raise KernelStatusError(st)

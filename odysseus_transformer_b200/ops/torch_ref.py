@@ -204,8 +204,12 @@ def merge_attn(out_a: torch.Tensor, lse_a: torch.Tensor, out_b: torch.Tensor, ls
 
 def adamw_step_(master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, grad: torch.Tensor,
                 param_out: Optional[torch.Tensor], lr: float, beta1: float, beta2: float, eps: float,
-                weight_decay: float, step: int, grad_scale: float = 1.0) -> None:
-    """Decoupled-weight-decay Adam on an fp32 master shard; writes the low-precision copy."""
+                weight_decay: float, step: int, grad_scale: float = 1.0,
+                guard: Optional[torch.Tensor] = None) -> None:
+    """Decoupled-weight-decay Adam on an fp32 master shard; writes the low-precision copy.
+    A non-zero ``guard`` (first element) leaves everything untouched, like the CUDA kernel's guard word."""
+    if guard is not None and float(guard.reshape(-1)[0]) != 0.0:
+        return
     g = grad.float() * grad_scale
     master.mul_(1.0 - lr * weight_decay)
     m.mul_(beta1).add_(g, alpha=1.0 - beta1)

@@ -11,8 +11,14 @@ slice, or a small replicated norm weight), so the optimizer is purely local:
 * parameters that are replicated over some group (norm weights; attention weights across ring
   blocks in the Odysseus x ring hybrid) are laid out contiguously per group so one all-reduce per
   group sums their gradients before the step;
-* the step is ONE fused kernel over the flat buffers on CUDA (``csrc/adamw.cu``), or the same
-  arithmetic in PyTorch elsewhere.
+* the step is ONE fused kernel over the flat buffers on CUDA (``adamw_k`` in ``csrc/elementwise.cu``), or
+  the same arithmetic in PyTorch elsewhere;
+* ``step(guard=t)`` hands the kernel a device word: when it is non-zero at run time (a kernel of this step
+  reported a failed wait) nothing is updated, without the host having to look first;
+* ``cpu_offload=True`` (the reference's ``--cpu-offload``, reference ``train.py:123-125,142-144``, which asks
+  FSDP for ``CPUOffload(offload_params=True)``) keeps the fp32 master weights and both moments in pinned
+  host memory - 12 of the 16 bytes per parameter - and runs the update on the CPU: gradients go device ->
+  host, the new bf16 parameters host -> device, once per step.
 """
 from __future__ import annotations
 
@@ -27,7 +33,8 @@ from ..parallel.linear import wait_pending_grad_comm
 
 class ShardedAdamW:
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 2e-5, betas=(0.9, 0.999),
-                 eps: float = 1e-8, weight_decay: float = 0.01, master_dtype: torch.dtype = torch.float32):
+                 eps: float = 1e-8, weight_decay: float = 0.01, master_dtype: torch.dtype = torch.float32,
+                 cpu_offload: bool = False):
         params = [p for p in params if p.requires_grad]
         if not params:
             raise ValueError("no parameters")
@@ -65,9 +72,18 @@ class ShardedAdamW:
             p.main_grad = self.flat_grad[o:o + p.numel()].view(p.shape)
             p._grad_written = False
             p.grad = None
-        self.master = self.flat_param.to(master_dtype)
-        self.exp_avg = torch.zeros(off, dtype=master_dtype, device=dev)
-        self.exp_avg_sq = torch.zeros(off, dtype=master_dtype, device=dev)
+        self.cpu_offload = bool(cpu_offload)
+        if self.cpu_offload:
+            pin = dev.type == "cuda"
+            host = lambda dtype: torch.zeros(off, dtype=dtype, device="cpu", pin_memory=pin)   # noqa: E731
+            self.master = host(master_dtype)
+            self.master.copy_(self.flat_param)
+            self.exp_avg, self.exp_avg_sq = host(master_dtype), host(master_dtype)
+            self._host_grad, self._host_param = host(dt), host(dt)
+        else:
+            self.master = self.flat_param.to(master_dtype)
+            self.exp_avg = torch.zeros(off, dtype=master_dtype, device=dev)
+            self.exp_avg_sq = torch.zeros(off, dtype=master_dtype, device=dev)
 
     # ------------------------------------------------------------------ step
     def sync_grads(self) -> None:
@@ -83,16 +99,25 @@ class ShardedAdamW:
         for group, s, e in self.sync_ranges:
             C.all_reduce_(self.flat_grad[s:e], group)
 
-    def step(self, grad_scale: float = 1.0) -> None:
+    def step(self, grad_scale: float = 1.0, guard: Optional[torch.Tensor] = None) -> None:
+        """One AdamW update of every shard.  ``guard``: optional fp32 tensor on the parameters' device; a
+        non-zero first element makes the update a no-op (decided on the device, no host read)."""
         self.sync_grads()
         self.step_count += 1
         b1, b2 = self.betas
-        if native.use_native(self.flat_param):
+        if self.cpu_offload:
+            self._host_grad.copy_(self.flat_grad)          # device -> pinned host (synchronises)
+            host_guard = guard.detach().to("cpu") if guard is not None else None
+            torch_ref.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, self._host_grad, self._host_param,
+                                  self.lr, b1, b2, self.eps, self.weight_decay, self.step_count, grad_scale, host_guard)
+            if host_guard is None or float(host_guard.reshape(-1)[0]) == 0.0:
+                self.flat_param.copy_(self._host_param, non_blocking=True)
+        elif native.use_native(self.flat_param):
             native.lib().adamw_step(self.master, self.exp_avg, self.exp_avg_sq, self.flat_grad, self.flat_param,
-                                    self.lr, b1, b2, self.eps, self.weight_decay, self.step_count, grad_scale)
+                                    self.lr, b1, b2, self.eps, self.weight_decay, self.step_count, grad_scale, guard)
         else:
             torch_ref.adamw_step_(self.master, self.exp_avg, self.exp_avg_sq, self.flat_grad, self.flat_param,
-                                  self.lr, b1, b2, self.eps, self.weight_decay, self.step_count, grad_scale)
+                                  self.lr, b1, b2, self.eps, self.weight_decay, self.step_count, grad_scale, guard)
 
     def zero_grad(self) -> None:
         """Gradients are overwritten by the next backward; only the per-step flags are reset."""
@@ -118,7 +143,7 @@ class ShardedAdamW:
         self.master.copy_(sd["master"])
         self.exp_avg.copy_(sd["exp_avg"])
         self.exp_avg_sq.copy_(sd["exp_avg_sq"])
-        self.flat_param.copy_(self.master.to(self.flat_param.dtype))
+        self.flat_param.copy_(self.master.to(self.flat_param.dtype))   # also host -> device when offloaded
 
     def bytes_held(self) -> int:
         return sum(t.numel() * t.element_size() for t in

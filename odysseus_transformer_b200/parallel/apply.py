@@ -75,11 +75,12 @@ def prepare_attn_inputs(parallel_mode: Optional[str], input_ids: torch.Tensor, p
 
 def build_model(cfg: ModelConfig, mode: Optional[str], ctx: Optional[ParallelContext] = None,
                 dtype: torch.dtype = torch.float32, device=None, seed: Optional[int] = 0,
-                state_dict: Optional[Dict[str, torch.Tensor]] = None):
-    """Create the model directly in ``mode``; weights from ``state_dict`` (HF names) or random."""
+                state_dict: Optional[Dict[str, torch.Tensor]] = None, use_zero3_linear: bool = True):
+    """Create the model directly in ``mode``; weights from ``state_dict`` (HF names) or random.
+    ``use_zero3_linear=False`` (odysseus mode only) keeps the MLP weights whole on every rank."""
     from ..models.llama import LlamaForCausalLM
     ctx = ctx if ctx is not None else get_context()
-    model = LlamaForCausalLM(cfg, mode, ctx, dtype=dtype, device=device)
+    model = LlamaForCausalLM(cfg, mode, ctx, dtype=dtype, device=device, use_zero3_linear=use_zero3_linear)
     if state_dict is not None:
         model.load_hf_state_dict(state_dict)
     elif seed is not None:
@@ -87,7 +88,8 @@ def build_model(cfg: ModelConfig, mode: Optional[str], ctx: Optional[ParallelCon
     return model
 
 
-def apply_seq_parallel(model, mode: Optional[str], ctx: Optional[ParallelContext] = None):
+def apply_seq_parallel(model, mode: Optional[str], ctx: Optional[ParallelContext] = None,
+                       use_zero3_linear: bool = True):
     """Return ``model`` converted to ``mode`` on mesh ``ctx``, keeping its weights.
 
     The weights are exported as a full HF state dict (gathering whatever sharding the model has
@@ -95,7 +97,8 @@ def apply_seq_parallel(model, mode: Optional[str], ctx: Optional[ParallelContext
     from ..models.llama import LlamaForCausalLM
     ctx = ctx if ctx is not None else get_context()
     sd = model.export_hf_state_dict()
-    new = LlamaForCausalLM(model.cfg, mode, ctx, dtype=model.dtype_, device=model.embed_tokens.device)
+    new = LlamaForCausalLM(model.cfg, mode, ctx, dtype=model.dtype_, device=model.embed_tokens.device,
+                           use_zero3_linear=use_zero3_linear)
     new.load_hf_state_dict(sd)
     if getattr(model, "gradient_checkpointing", False):
         new.gradient_checkpointing_enable()
@@ -109,23 +112,21 @@ def default_mode() -> Optional[str]:
     return _DEFAULT_MODE
 
 
-def _apply(mode: str, model=None, **_):
+def _apply(mode: str, model=None, use_zero3_linear: bool = True):
     global _DEFAULT_MODE
     if model is None:
         # the reference's argument-less patches change HF classes globally; the analogue here is a
         # process-wide default picked up by ``train`` / ``build_model`` callers that pass no mode
         _DEFAULT_MODE = mode
         return None
-    return apply_seq_parallel(model, mode)
+    return apply_seq_parallel(model, mode, use_zero3_linear=use_zero3_linear)
 
 
 def apply_odysseus_attn_patch_llama(model=None, use_zero3_linear: bool = True):
-    if not use_zero3_linear:
-        raise NotImplementedError(
-            "Odysseus with a replicated MLP leaves the MLP gradients unsynchronised in the reference "
-            "(train.py:128-132) and its flag cannot be switched off there (train.py:255); only the "
-            "ZeRO-3 MLP is provided")
-    return _apply("odysseus", model)
+    """TP-SP attention + sequence-parallel MLP (reference ``decoder/odysseus.py:298-309``).  With
+    ``use_zero3_linear=False`` the MLP weights stay whole on every rank (``parallel.odysseus.ReplicatedMLP``)
+    and their gradients are all-reduced once per step."""
+    return _apply("odysseus", model, use_zero3_linear)
 
 
 def apply_tpsp_attn_patch_llama(model=None):

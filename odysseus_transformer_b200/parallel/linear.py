@@ -265,9 +265,16 @@ class _Zero3Linear(Function):
             work = dist.reduce_scatter_tensor(mg, gfull, group=group, async_op=True)
             _SLOT_WORK[slot] = work
             _PENDING.append(work)
+            w._grad_work = work
             w._grad_written = True
             dw = None
         else:
+            # a second contribution to the same weight before the optimizer step: the reduce-scatter of the
+            # first one may still be writing main_grad on NCCL's stream - finish it before accumulating
+            first = getattr(w, "_grad_work", None)
+            if first is not None:
+                first.wait()
+                w._grad_work = None
             dw = F.deliver_grad(w, C.reduce_scatter_rows(gfull, group))
         return dx, dw, None, None, None
 

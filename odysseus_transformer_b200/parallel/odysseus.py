@@ -13,6 +13,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
+from ..comm import torch_backend as C
 from ..ops import functional as F
 from .linear import LinearZeRO3
 from .tpsp import TPSPAttention  # noqa: F401  (re-exported: the attention half of the mode)
@@ -47,3 +48,39 @@ class OdysseusMLP(nn.Module):
         out[prefix + "gate_proj.weight"] = gu[:i].clone()
         out[prefix + "up_proj.weight"] = gu[i:].clone()
         out[prefix + "down_proj.weight"] = self.down_proj.get_master_weight().clone()
+
+
+class ReplicatedMLP(nn.Module):
+    """Sequence-parallel MLP with whole weights on every rank: the ``use_zero3_linear=False`` variant of
+    ``apply_odysseus_attn_patch_llama`` (reference ``decoder/odysseus.py:298-309``; its published
+    "Odysseus (FSDP MLP)" rows, reference ``README.md:39-45``).
+
+    Tokens stay local and no weight is gathered; the weight gradients of all ranks are summed by ONE
+    all-reduce per step, issued by the optimizer over the flat gradient range of these parameters.  The
+    reference leaves the plain ``LlamaMLP`` outside FSDP in this setting, so its gradients are never
+    synchronised (reference ``train.py:128-132``); here they are.  Costs ``3 d i`` parameters plus their
+    optimizer state per GPU instead of ``3 d i / N``."""
+
+    def __init__(self, cfg, ctx, dtype=None, device=None):
+        super().__init__()
+        self.cfg, self.pctx = cfg, ctx
+        d, i = cfg.hidden_size, cfg.intermediate_size
+        self.gate_up_proj = nn.Parameter(torch.empty(2 * i, d, dtype=dtype, device=device))
+        self.down_proj = nn.Parameter(torch.empty(d, i, dtype=dtype, device=device))
+        if ctx.world_group is not None and C.group_size(ctx.world_group) > 1:
+            for p in self.parameters():
+                p.grad_sync_group = ctx.world_group
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(F.swiglu(F.linear(x, self.gate_up_proj)), self.down_proj)
+
+    def hf_load(self, get, prefix: str) -> None:
+        with torch.no_grad():
+            self.gate_up_proj.copy_(torch.cat([get(prefix + "gate_proj.weight"), get(prefix + "up_proj.weight")], 0))
+            self.down_proj.copy_(get(prefix + "down_proj.weight"))
+
+    def hf_export(self, prefix: str, out) -> None:
+        i = self.cfg.intermediate_size
+        out[prefix + "gate_proj.weight"] = self.gate_up_proj.detach()[:i].clone()
+        out[prefix + "up_proj.weight"] = self.gate_up_proj.detach()[i:].clone()
+        out[prefix + "down_proj.weight"] = self.down_proj.detach().clone()

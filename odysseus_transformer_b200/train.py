@@ -18,6 +18,7 @@ is tensor-parallel or ZeRO-3 sharded by the model itself and the optimizer keeps
 from __future__ import annotations
 
 import argparse
+import contextlib
 import dataclasses
 import os
 import time
@@ -33,9 +34,10 @@ from .optim.adamw import ShardedAdamW
 from .parallel.apply import build_model, prepare_attn_inputs
 from .utils import checkpoint as ckpt
 from .utils.buffers import set_global_memory_buffer
-from .utils.health import Heartbeat
-from .utils.metrics import DeviceTimer, JsonlWriter, max_over_ranks, memory_gb
-from .utils.profiler import init_prof
+from .utils.health import Heartbeat, guarded_collective
+from .utils.log_utils import get_logger, rank_log
+from .utils.metrics import DeviceTimer, JsonlWriter, PhaseTimers, exposed_comm_ms, max_over_ranks, memory_gb, train_flops_per_token
+from .utils.profiler import init_prof, nvtx_range
 
 
 def set_seed(seed: int) -> None:
@@ -53,25 +55,36 @@ class Trainer:
 
     ``train_step(batch)`` is the call a user makes: ``batch`` is a host tensor ``[1, L+1]`` of token
     ids (pinned memory recommended); it returns the device scalar holding this step's global-mean
-    loss.  ``train_step_device`` takes already-sliced device tensors."""
+    loss.  ``train_step_device`` takes already-sliced device tensors.
+
+    Failure handling: the kernels' bounded waits report into a per-device status word.  Every step
+    sums that word over the ranks together with the loss (one small all-reduce), hands the sum to the
+    optimizer kernel as its guard - a step with a failed wait anywhere updates no weight on any rank -
+    and copies it to pinned host memory without synchronising.  The next ``train_step*`` call (or
+    ``check_status``) raises ``KernelStatusError`` once that copy has landed."""
 
     def __init__(self, cfg: ModelConfig, mode: Optional[str], ctx: ParallelContext, seq_length: int,
                  lr: float = 2e-5, weight_decay: float = 0.01, betas=(0.9, 0.999), eps: float = 1e-8,
                  dtype: torch.dtype = torch.bfloat16, seed: int = 42, ulysses_degree: int = 0,
                  ring_degree: int = 1, state_dict: Optional[Dict[str, torch.Tensor]] = None,
-                 grad_checkpoint: bool = False, use_zero2: bool = False):
+                 grad_checkpoint: bool = False, use_zero2: bool = False, cpu_offload: bool = False,
+                 use_zero3_linear: bool = True, time_phases: bool = False):
         self.cfg, self.mode, self.ctx, self.seq_length = cfg, mode, ctx, seq_length
         self.ulysses_degree, self.ring_degree = ulysses_degree, ring_degree
         set_global_memory_buffer(ctx.device)
         if ctx.world_size > 1 and ctx.device.type == "cuda" and native.get_backend() != "library" and dtype == torch.bfloat16:
             from .comm import symm
             symm.setup_fused_comm(ctx, cfg, max(1, seq_length // ctx.world_size), mode=mode)
-        self.model = build_model(cfg, mode, ctx, dtype=dtype, device=ctx.device, seed=seed, state_dict=state_dict)
+        self.model = build_model(cfg, mode, ctx, dtype=dtype, device=ctx.device, seed=seed, state_dict=state_dict,
+                                 use_zero3_linear=use_zero3_linear)
         if grad_checkpoint:
             self.model.gradient_checkpointing_enable()
         if use_zero2:
             self.model.zero3.keep_gathered = True
-        self.optimizer = ShardedAdamW(self.model.parameters(), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        self.optimizer = ShardedAdamW(self.model.parameters(), lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                                      cpu_offload=cpu_offload)
+        self._status_reads = []          # (step, event or None, host tensor) awaiting a look
+        self.phases = PhaseTimers(ctx.device) if time_phases else None
         self.global_tokens = seq_length * (ctx.world_size if mode in (None, "dp") else 1)
         self.position_ids = torch.arange(seq_length).unsqueeze(0)
         self.steps_done = 0
@@ -86,17 +99,77 @@ class Trainer:
         return out
 
     def train_step_device(self, local_input_ids, local_position_ids, local_target_ids) -> torch.Tensor:
-        loss = self.model(local_input_ids, local_position_ids, labels=local_target_ids,
-                          global_tokens=self.global_tokens)
-        loss.backward()
-        self.optimizer.step()
-        self.optimizer.zero_grad()
-        self.steps_done += 1
-        loss = loss.detach()
+        self.check_status(block=False)
+        with self._phase("forward"):
+            loss = self.model(local_input_ids, local_position_ids, labels=local_target_ids,
+                              global_tokens=self.global_tokens)
+        with self._phase("backward"):
+            loss.backward()
+        # [loss, kernel status] summed over the ranks in one collective, before the optimizer looks at it
+        dev = self.ctx.device
+        status = native.status_tensor(dev)
+        parts = [loss.detach().float().reshape(1)]
+        if status is not None:
+            parts.append(status.reshape(-1)[:1].float())
+        health = torch.cat(parts)
         if self.ctx.world_size > 1:
-            loss = loss.clone()
-            dist.all_reduce(loss, group=self.ctx.world_group)
-        return loss
+            guarded_collective(dist.all_reduce, health, group=self.ctx.world_group,
+                               on_timeout="loss / status all-reduce")
+        guard = health[1:2] if status is not None else None
+        with self._phase("optimizer"):
+            self.optimizer.step(guard=guard)
+            self.optimizer.zero_grad()
+        if guard is not None:
+            self._queue_status_read(guard)
+        self.steps_done += 1
+        return health[0]
+
+    def _phase(self, name: str):
+        """NVTX range around a phase of the step, plus a device timer when ``time_phases`` was asked for."""
+        if self.phases is None:
+            return nvtx_range(name)
+        stack = contextlib.ExitStack()
+        stack.enter_context(nvtx_range(name))
+        stack.enter_context(self.phases.phase(name))
+        return stack
+
+    def phase_summary(self, reset: bool = False) -> Dict[str, float]:
+        """ms per phase since the last reset, each the max over ranks (empty without ``time_phases``)."""
+        if self.phases is None:
+            return {}
+        out = self.phases.summary(self.ctx.world_group)
+        if reset:
+            self.phases = PhaseTimers(self.ctx.device)
+        return out
+
+    def _queue_status_read(self, guard: torch.Tensor) -> None:
+        if guard.is_cuda:
+            host = torch.empty(1, dtype=torch.float32, pin_memory=True)
+            host.copy_(guard, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self._status_reads.append((self.steps_done, ev, host))
+        else:
+            self._status_reads.append((self.steps_done, None, guard.detach().clone()))
+
+    def check_status(self, block: bool = True) -> None:
+        """Raise ``KernelStatusError`` if a finished step reported a failed device-side wait.  ``block=False``
+        looks only at steps whose status has already reached the host (no synchronisation)."""
+        while self._status_reads:
+            step, ev, host = self._status_reads[0]
+            if ev is not None:
+                if block:
+                    ev.synchronize()
+                elif not ev.query():
+                    return
+            self._status_reads.pop(0)
+            st = int(host[0])
+            if st != 0:
+                self._status_reads.clear()
+                if self.ctx.device.type == "cuda" and native.available():
+                    native.lib().clear_status(self.ctx.device.index or 0)
+                raise native.KernelStatusError(
+                    st, f"in training step {step} (sum over ranks); that step's optimizer update was skipped on every rank")
 
     def train_step(self, batch: torch.Tensor) -> torch.Tensor:
         s = self.shard_batch(batch)
@@ -124,8 +197,6 @@ def resolve_model_config(args) -> ModelConfig:
 
 def main(args) -> Dict[str, float]:
     assert args.batch_size == 1, "Only batch size 1 is supported (sequence parallelism folds the batch dim)"
-    if args.cpu_offload:
-        raise NotImplementedError("--cpu-offload: parameters are sharded 1/N by construction; offload is not provided")
     native.set_backend(args.backend)
     ctx = init_parallel_context(args.parallel_mode, args.ulysses_degree, args.ring_degree, backend=args.backend)
     rank, world, dev = ctx.rank, ctx.world_size, ctx.device
@@ -138,10 +209,15 @@ def main(args) -> Dict[str, float]:
         state_dict = ckpt.load_hf_state_dict_file(src)
     trainer = Trainer(cfg, args.parallel_mode, ctx, args.seq_length, lr=args.learning_rate, dtype=_dtype(args.dtype),
                       seed=args.seed, ulysses_degree=args.ulysses_degree, ring_degree=args.ring_degree,
-                      state_dict=state_dict, grad_checkpoint=args.grad_checkpoint, use_zero2=args.use_zero2)
+                      state_dict=state_dict, grad_checkpoint=args.grad_checkpoint, use_zero2=args.use_zero2,
+                      cpu_offload=args.cpu_offload, use_zero3_linear=args.use_ody_zero3, time_phases=bool(args.jsonl))
+    log = get_logger()
     start_step = 0
+    # the data stream is a function of the RNG state: seed it for a fresh run, restore it for a resumed one
+    set_seed(args.seed)
     if args.load and os.path.exists(os.path.join(args.load, f"train_state_rank{rank}.pt")):
         start_step = ckpt.load_train_state(args.load, trainer.optimizer, rank)
+        rank_log(rank, log, f"resumed optimizer, step {start_step} and RNG state from {args.load}")
     if rank == 0:
         print(f"{cfg.num_parameters() / 1e9:.2f}B parameters; mode {args.parallel_mode} on {world} rank(s); "
               f"backend {native.get_backend()}")
@@ -151,7 +227,6 @@ def main(args) -> Dict[str, float]:
     if world > 1 and args.heartbeat_timeout > 0:
         hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world, args.heartbeat_timeout)
     writer = JsonlWriter(args.jsonl, rank)
-    set_seed(args.seed)
     warmup = args.warmup_iterations
     timer = DeviceTimer(dev)
     elapse, timed_steps = 0.0, 0
@@ -160,7 +235,7 @@ def main(args) -> Dict[str, float]:
         for step in range(start_step, args.max_train_steps):
             if hb is not None:
                 hb.barrier(step)
-            timed = step > warmup
+            timed = (step - start_step) > warmup       # a resumed run warms up again
             if timed:
                 t0 = time.time()
                 timer.start()
@@ -171,22 +246,29 @@ def main(args) -> Dict[str, float]:
                 print(f"CUDA memory allocated: {m['allocated']:.2f} GB, reserved: {m['reserved']:.2f} GB")
                 loss_val = loss.item()
                 print(f"step {step}, loss: {loss_val}")
+                trainer.check_status(block=True)       # rank 0 has just synchronised anyway
             if timed:
                 timer.stop()
                 elapse += time.time() - t0
                 timed_steps += 1
             if prof is not None:
                 prof.step()
-            writer.write(step=step, loss=loss_val, **memory_gb(dev))
+            rec = {"step": step, "loss": loss_val}
+            if args.jsonl:      # every rank takes part in the max-over-ranks reductions
+                rec["exposed_comm_ms"] = exposed_comm_ms(ctx, reset=True)
+                rec["phase_ms"] = trainer.phase_summary(reset=True)
+            writer.write(**rec, **memory_gb(dev))
+    trainer.check_status(block=True)
     dev_ms = max_over_ranks(timer.elapsed_ms(), dev)
     tok_s = timed_steps * args.seq_length / (dev_ms / 1e3) if dev_ms > 0 else 0.0
+    flops = train_flops_per_token(cfg, args.seq_length) * tok_s / max(1, world)
     if rank == 0:
         print(f"{args.parallel_mode} {args.seq_length // 1024}K {world} Time taken: {elapse:.2f} seconds")
         m = memory_gb(dev)
         print(f"device time (max over ranks) {dev_ms / 1e3:.3f} s over {timed_steps} steps; {tok_s:.0f} tokens/s; "
               f"peak allocated {m['peak_allocated']:.2f} GB, peak reserved {m['peak_reserved']:.2f} GB")
     writer.write(final=True, mode=args.parallel_mode, seq_length=args.seq_length, world=world, elapsed_s=elapse,
-                 device_s=dev_ms / 1e3, tokens_per_s=tok_s, **memory_gb(dev))
+                 device_s=dev_ms / 1e3, tokens_per_s=tok_s, model_tflops_per_gpu=flops / 1e12, **memory_gb(dev))
     writer.close()
     if args.save:
         ckpt.save_hf_checkpoint(trainer.model, args.save)
@@ -208,6 +290,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--grad-checkpoint", "--grad_checkpoint", action="store_true", default=False)
     p.add_argument("--use_zero2", "--use-zero2", action="store_true", default=False)
     p.add_argument("--use_ody_zero3", "--use-ody-zero3", action="store_true", default=True)
+    p.add_argument("--no_ody_zero3", "--no-ody-zero3", dest="use_ody_zero3", action="store_false",
+                   help="odysseus mode: keep the MLP weights whole on every rank and all-reduce their gradients "
+                        "(the reference's flag is store_true with default True and cannot be switched off, train.py:255)")
     p.add_argument("--use_profiler", "--use-profiler", action="store_true", default=False)
     p.add_argument("--use_cfg_init_model", "--use-cfg-init-model", action="store_true", default=False)
     p.add_argument("--parallel_mode", "--parallel-mode", type=str, choices=list(PARALLEL_MODES))

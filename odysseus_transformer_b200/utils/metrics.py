@@ -3,7 +3,8 @@
 The reference prints allocated / reserved GB and the loss on rank 0 and sums ``time.time()`` deltas
 over the steps after warm-up with no device synchronisation (reference ``train.py:104-107,185-186,
 217-229,237-240``).  The same prints are kept by ``train``; this module adds what they lack:
-device-side timing (CUDA events) reduced as the **max over ranks**, peak memory, and a JSONL sink.
+device-side timing (CUDA events) reduced as the **max over ranks**, peak memory, exposed communication
+time, per-phase timers and a JSONL sink.
 """
 from __future__ import annotations
 
@@ -63,6 +64,52 @@ def memory_gb(device: torch.device) -> Dict[str, float]:
     return {"allocated": torch.cuda.memory_allocated(device) / g, "reserved": torch.cuda.memory_reserved(device) / g,
             "peak_allocated": torch.cuda.max_memory_allocated(device) / g,
             "peak_reserved": torch.cuda.max_memory_reserved(device) / g}
+
+
+def exposed_comm_ms(ctx, reset: bool = False) -> float:
+    """Communication time the step could not hide, in ms, max over ranks, since the last reset.
+
+    The fused kernels time their own waits on other GPUs (``ody_set_wait_accumulator``): the TMA
+    producer of every gather-GEMM CTA while remote rows have not arrived, one thread per
+    reduce-scatter CTA while the other sources' tiles are missing, and the stand-alone wait kernels
+    of the ring and Ulysses paths (during which the stream does nothing else).  The first two are
+    summed over CTAs on the device and divided by the SM count here - the mean time an SM sat idle
+    for data; the third counts in full.  0.0 without a symmetric heap (NCCL composition: the
+    collectives are separate kernels and their cost is visible in the profiler instead).  Synchronises."""
+    acc = getattr(ctx, "wait_acc", None)
+    if acc is None:
+        return 0.0
+    v = acc.tolist()
+    if reset:
+        acc.zero_()
+    sms = torch.cuda.get_device_properties(ctx.device).multi_processor_count
+    ms = (v[0] + v[1]) / max(1, sms) / 1e6 + v[2] / 1e6
+    return max_over_ranks(ms, ctx.device, ctx.world_group)
+
+
+class PhaseTimers:
+    """Named CUDA-event timers (forward / backward / optimizer ...) summed per phase; ``summary`` reduces
+    every phase as the max over ranks.  On CPU it falls back to wall clock."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.timers: Dict[str, DeviceTimer] = {}
+
+    def phase(self, name: str):
+        import contextlib
+
+        @contextlib.contextmanager
+        def cm():
+            t = self.timers.setdefault(name, DeviceTimer(self.device))
+            t.start()
+            try:
+                yield
+            finally:
+                t.stop()
+        return cm()
+
+    def summary(self, group=None) -> Dict[str, float]:
+        return {k: max_over_ranks(t.elapsed_ms(), self.device, group) for k, t in sorted(self.timers.items())}
 
 
 class JsonlWriter:
