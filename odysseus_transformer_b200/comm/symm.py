@@ -20,6 +20,7 @@ writes into the other buffer instead of waiting for the peer to drain the first.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -213,6 +214,10 @@ class SymmetricHeap:
         self.handle = symm_mem.rendezvous(self.local, group)
         self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
         self.local[:FLAG_BYTES].zero_()
+        if os.environ.get("ODY_POISON_HEAP", "0") == "1":
+            # debug aid: staging that is read before its data arrived then shows up as NaN in the result
+            from ..utils.debug import poison_
+            poison_(self.local[FLAG_BYTES:].view(torch.bfloat16))
         torch.cuda.synchronize(device)
         dist.barrier(group=group)
         self._data_top = 0

@@ -41,6 +41,17 @@ std::vector<at::Tensor> attn_fwd(const at::Tensor& q, const at::Tensor& k, const
   return {o, lse};
 }
 
+// The backward launchers build V's tensor map from k's row count and head count: a shorter or narrower v would be
+// read past its end.  Every tensor must also live on q's device, where the kernels run.
+void check_kv_and_devices(const at::Tensor& dO, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                          const at::Tensor& o, const at::Tensor& lse) {
+  req(k.size(0) == v.size(0) && k.size(1) == v.size(1), "k / v shape mismatch");
+  req(k.size(1) > 0 && q.size(1) % k.size(1) == 0, "query heads must be a multiple of kv heads");
+  const auto dev = q.get_device();
+  req(dO.get_device() == dev && k.get_device() == dev && v.get_device() == dev && o.get_device() == dev &&
+          lse.get_device() == dev, "all attention tensors must be on q's device");
+}
+
 std::vector<at::Tensor> attn_bwd(const at::Tensor& dO, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                  const at::Tensor& o, const at::Tensor& lse, bool causal, double scale,
                                  const c10::optional<at::Tensor>& dq_out, const c10::optional<at::Tensor>& dk_out,
@@ -49,6 +60,7 @@ std::vector<at::Tensor> attn_bwd(const at::Tensor& dO, const at::Tensor& q, cons
   req(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous(), "lse must be contiguous fp32");
   req(lse.dim() == 2 && lse.size(0) == q.size(1) && lse.size(1) == q.size(0), "lse must be [H, Tq]");
   req(dO.sizes() == q.sizes() && o.sizes() == q.sizes(), "dO / o shape mismatch");
+  check_kv_and_devices(dO, q, k, v, o, lse);
   req(!causal || q.size(0) == k.size(0), "causal attention needs Tq == Tk");
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t Tq = q.size(0), Tk = k.size(0), H = q.size(1), Hkv = k.size(1);
@@ -111,6 +123,7 @@ void attn_bwd_split(const at::Tensor& dO, const at::Tensor& q, const at::Tensor&
   req(lse.is_cuda() && lse.scalar_type() == at::kFloat && lse.is_contiguous(), "lse must be contiguous fp32");
   req(lse.dim() == 2 && lse.size(0) == q.size(1) && lse.size(1) == q.size(0), "lse must be [H, Tq]");
   req(dO.sizes() == q.sizes() && o.sizes() == q.sizes(), "dO / o shape mismatch");
+  check_kv_and_devices(dO, q, k, v, o, lse);
   const int64_t Tq = q.size(0), Tk = k.size(0), H = q.size(1), Hkv = k.size(1);
   req(Tq == Tk, "split backward needs Tq == Tk");
   const int64_t rows = dq_dests.empty() ? 0 : dq_dests[0].size(0);
@@ -138,12 +151,9 @@ void ody_register_attention(pybind11::module& m) {
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_fwd_split", &attn_fwd_split);
   m.def("attn_bwd_split", &attn_bwd_split);
-  m.def("attn_fwd_set_trace", [](const c10::optional<at::Tensor>& t) {
-    if (t.has_value()) { req(t.value().is_cuda() && t.value().scalar_type() == at::kLong && t.value().numel() >= 48 * 8, "trace: int64 [48*8]"); ody_flash_fwd_set_trace((long long*)t.value().data_ptr()); }
-    else ody_flash_fwd_set_trace(nullptr);
-  });
+  m.def("attn_fwd_ctas", [](int64_t Tq, int64_t H) { return (int64_t)ody_flash_fwd_ctas((int)Tq, (int)H); });
   m.def("attn_bwd_set_trace", [](const c10::optional<at::Tensor>& t) {
-    if (t.has_value()) { req(t.value().is_cuda() && t.value().scalar_type() == at::kLong && t.value().numel() >= 96 * 8, "trace: int64 [96*8] (dK/dV kernel stamps, then dQ kernel stamps)"); ody_flash_bwd_set_trace((long long*)t.value().data_ptr()); }
+    if (t.has_value()) { req(t.value().is_cuda() && t.value().scalar_type() == at::kLong && t.value().numel() >= 96 * 8, "trace: int64 [96*8] (dK/dV kernel stamps, then dQ kernel stamps; only a build with -DODY_ATTN_TRACE records them)"); ody_flash_bwd_set_trace((long long*)t.value().data_ptr()); }
     else ody_flash_bwd_set_trace(nullptr);
   });
   m.def("attn_bwd", &attn_bwd, py::arg("dO"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("lse"),

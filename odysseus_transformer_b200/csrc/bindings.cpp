@@ -117,15 +117,27 @@ std::vector<at::Tensor> add_rmsnorm_fwd(const at::Tensor& x, const at::Tensor& d
 std::vector<at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w,
                                     const at::Tensor& rstd, const c10::optional<at::Tensor>& ds) {
   check_bf16(dy, "dy"); check_bf16(x, "x"); check_bf16(w, "w");
-  ody_req(dy.is_contiguous() && x.is_contiguous(), "rmsnorm_bwd: contiguous inputs required");
-  c10::cuda::CUDAGuard guard(x.device());
+  ody_req(dy.is_contiguous() && x.is_contiguous() && w.is_contiguous(), "rmsnorm_bwd: contiguous inputs required");
+  ody_req(x.dim() >= 1 && x.size(-1) > 0, "rmsnorm_bwd: x must have a non-empty last dim");
   const int64_t dim = x.size(-1), rows = x.numel() / dim;
+  ody_req(dy.sizes() == x.sizes(), "rmsnorm_bwd: dy and x must have the same shape");
+  ody_req(w.numel() == dim, "rmsnorm_bwd: w must have x's last dim");
+  ody_req(rstd.is_cuda() && rstd.scalar_type() == at::kFloat && rstd.is_contiguous() && rstd.numel() == rows,
+          "rmsnorm_bwd: rstd must be a contiguous fp32 CUDA tensor with one entry per row");
+  ody_req(dy.get_device() == x.get_device() && w.get_device() == x.get_device() && rstd.get_device() == x.get_device(),
+          "rmsnorm_bwd: all tensors must be on x's device");
+  c10::cuda::CUDAGuard guard(x.device());
   auto dx = at::empty_like(x);
   auto dw = at::empty({dim}, x.options().dtype(at::kFloat));
   const int nb = ody_rmsnorm_bwd_blocks(rows, (int)dim);
   auto partial = at::empty({nb, dim}, x.options().dtype(at::kFloat));
   const void* dsp = nullptr;
-  if (ds.has_value()) { check_bf16(ds.value(), "ds"); ody_req(ds.value().is_contiguous()); dsp = ds.value().data_ptr(); }
+  if (ds.has_value()) {
+    check_bf16(ds.value(), "ds");
+    ody_req(ds.value().is_contiguous() && ds.value().sizes() == x.sizes() && ds.value().get_device() == x.get_device(),
+            "rmsnorm_bwd: ds must match x");
+    dsp = ds.value().data_ptr();
+  }
   ODY_CHECK(ody_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dsp, dx.data_ptr(),
                             dw.data_ptr<float>(), partial.data_ptr<float>(), rows, (int)dim, cur_stream()), "rmsnorm_bwd");
   g_launches += 2;

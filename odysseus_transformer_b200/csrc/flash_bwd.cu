@@ -143,6 +143,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                       const uint8_t* __restrict__ stat_tiles, int Tq, int Tk, int Tq_pad,
                       int H, int Hkv, int causal, float scale, int* __restrict__ err, long long* __restrict__ dbg,
                       const __grid_constant__ SplitMaps dk_split, const __grid_constant__ SplitMaps dv_split) {
+#ifndef ODY_ATTN_TRACE
+  dbg = nullptr;   // the clock-stamp timeline is a development aid: compiled out of the product kernels
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sK = smem;
@@ -463,6 +466,9 @@ flash_bwd_dq_kernel(const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* _
                     const __grid_constant__ CUtensorMap tmDQ, const float* __restrict__ lse2_pad,
                     const float* __restrict__ delta_pad, int Tq, int Tk, int Tq_pad, int H, int Hkv, int causal,
                     float scale, int* __restrict__ err, const __grid_constant__ SplitMaps dq_split, long long* __restrict__ dbg) {
+#ifndef ODY_ATTN_TRACE
+  dbg = nullptr;   // the clock-stamp timeline is a development aid: compiled out of the product kernels
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;                                     // staging of the dQ tile for its TMA store

@@ -4,18 +4,19 @@
 // _flash_attention_forward (reference decoder/odysseus.py:256-263) and through its ring / Ulysses
 // dependencies.  This kernel is written for the Blackwell execution model instead:
 //
-//   * one CTA per (128-row query tile, head); K/V blocks of 128 rows stream through a 2-stage TMA ring;
-//   * S = Q K^T and O += P V are tcgen05.mma instructions issued by one thread; S (double buffered), the
-//     bf16 probabilities P (double buffered, fed back as the TMEM A operand) and the fp32 O accumulator
-//     live in TMEM (2*128 + 2*64 + 128 = 512 columns);
-//   * eight softmax warps, two threads per query row (64 of the 128 key columns each, so every scheduler
-//     has two warps to interleave), read S straight from TMEM, exchange their partial row maxima through
-//     shared memory, work in the exp2 domain and rescale O lazily: the running maximum used for
-//     exponentiation only moves when it would grow by more than 2^8, so the O read-modify-write is rare;
-//   * S = Q K^T and O += P V are issued by two different warps: a single thread sustains only about one
-//     tcgen05.mma per ~85 cycles, and with 64-cycle instructions one issuer would leave the tensor core
-//     idle a third of the time.  Q K^T of block j+2 goes out as soon as the softmax warps have loaded
-//     S of block j into registers.
+//   * one CTA per (256 query rows, head): TWO 128-row query tiles A and B that take turns on the tensor
+//     core.  While the softmax warpgroup of one tile turns its scores into probabilities, the tensor core
+//     runs P V and the next Q K^T of the other tile, so neither the tensor pipe nor the exponential unit
+//     waits for the other (with a single tile per CTA they alternate and each idles half the time);
+//   * K/V blocks of 128 rows stream through two-stage TMA rings and are used by both tiles;
+//   * every MMA is a tcgen05.mma issued by ONE thread in program order: S_t = Q_t K^T (operands in shared
+//     memory) and O_t += P_t V (P_t read from TMEM).  TMEM holds S_A, S_B, O_A, O_B (4 x 128 fp32 columns);
+//     the bf16 probabilities P_t are written over the first 64 columns of S_t once its thread has S_t in
+//     registers - the in-order tensor pipe runs Q K^T of the next block only after P V has read them;
+//   * two softmax warpgroups, one thread per query row: 128 scores straight from TMEM, no exchange between
+//     threads, exp2 domain, lazy rescaling of O (the running maximum used for exponentiation only moves when
+//     it would grow by more than 2^8, so the O read-modify-write is rare).  A tcgen05.commit after Q K^T of
+//     block j also covers P V of block j-1, so a thread that sees S(j) may touch O without another barrier.
 //
 // q [Tq, H, 128], k/v [Tk, Hkv, 128] with arbitrary row pitch; out [Tq, H, 128] bf16; lse [H, Tq] fp32
 // (natural log).  causal requires Tq == Tk (row i sees keys 0..i).
@@ -24,31 +25,33 @@
 #include "peer_comm.cuh"
 
 // Of every ODY_FWD_POLY_DEN column pairs, the first ODY_FWD_POLY_NUM take their exponentials on the FMA pipe
-// (exp2_poly2) instead of the special-function unit.  Measured on B200: any mix is a few percent slower than
-// all-MUFU - the softmax warps are bound by the latency of their dependent chains, not by either pipe - so it is off.
+// (exp2_poly2) instead of the special-function unit, which otherwise has to deliver 16384 exponentials per
+// 128 x 128 tile at 16 per clock.
 #ifndef ODY_FWD_POLY_NUM
 #define ODY_FWD_POLY_NUM 0
-#define ODY_FWD_POLY_DEN 2
+#define ODY_FWD_POLY_DEN 4
 #endif
 
 namespace ody {
 namespace fwd {
 
 constexpr int BM = 128, BN = 128, HD = 128;
+constexpr int CTA_ROWS = 2 * BM;             // two query tiles per CTA
 constexpr int TILE_BYTES = 128 * HD * 2;     // 32 KB: two 64-column halves of [128 rows x 128 B]
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
-constexpr int SMEM_TILES = TILE_BYTES * (1 + 2 * KV_STAGES);
-constexpr int SMEM_TOTAL = SMEM_TILES + 2560 + 1024;
-// Warp roles, grouped by warpgroup so that the PUSH variant can move registers between them:
-//   0 TMA producer, 1 Q K^T issuer, 2 P V issuer, 3 idle | 4..11 softmax (two per TMEM lane quarter) | 12..15 comm (PUSH only)
+constexpr int SMEM_TILES = TILE_BYTES * (2 + 2 * KV_STAGES);
+constexpr int SMEM_TOTAL = SMEM_TILES + 512 + 1024;
+// Warp roles by warpgroup: 0 TMA producer, 1 MMA issuer, 2-3 idle | 4..7 softmax of tile A | 8..11 softmax of
+// tile B | 12..15 comm (PUSH only).  Registers move between the warpgroups with setmaxnreg; the split must fit
+// inside what the CTA was launched with or the increase never returns.
 constexpr int NUM_THREADS = 384;
 constexpr int NUM_THREADS_PUSH = NUM_THREADS + gc::COMM_THREADS;
-// Register split of the PUSH variant by setmaxnreg: 512 threads are launched with 128 registers each; the split
-// must fit inside that allocation or the increase never returns.
-constexpr int REGS_ISSUE = 56, REGS_MATH = 176, REGS_COMM = 104;
-static_assert(128 * REGS_ISSUE + 256 * REGS_MATH + 128 * REGS_COMM <= NUM_THREADS_PUSH * 128, "setmaxnreg split exceeds the CTA's registers");
-constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
+constexpr int REGS_ISSUE = 56, REGS_MATH = 200;                            // 384 threads launched with 168 registers each
+constexpr int REGS_ISSUE_PUSH = 48, REGS_MATH_PUSH = 184, REGS_COMM = 88;  // 512 threads launched with 128 each
+static_assert(128 * REGS_ISSUE + 256 * REGS_MATH <= NUM_THREADS * 168, "setmaxnreg split exceeds the CTA's registers");
+static_assert(128 * REGS_ISSUE_PUSH + 256 * REGS_MATH_PUSH + 128 * REGS_COMM <= NUM_THREADS_PUSH * 128, "setmaxnreg split exceeds the CTA's registers (push)");
+constexpr uint32_t COL_S = 0, COL_O = 256;   // S_t at COL_S + t * 128 (P_t over its first 64 columns), O_t at COL_O + t * 128
 
 // Optional second destination of the output: rows [d * rows, (d + 1) * rows) also go to tensor map m[d]
 // (another rank's buffer: the Ulysses head->sequence exchange happens in this epilogue).
@@ -58,21 +61,14 @@ struct SplitMaps {
 };
 
 struct Bars {
-  uint64_t q_full;
+  uint64_t q_full[2];
   uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
   uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-  uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
+  uint64_t s_full[2], p_full[2], o_done[2];
   uint64_t drain;
   uint32_t tmem_base;
   int abort_flag;
-  float pmax[2][2][128];      // [parity][column half][row]: partial row maxima (and, at the end, row sums)
 };
-
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
@@ -87,37 +83,42 @@ __global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                  float* __restrict__ lse, int Tq, int Tk, int H, int Hkv, int causal, float scale,
-                 int* __restrict__ err, long long* __restrict__ dbg, const __grid_constant__ gc::GatherParams pp,
+                 int* __restrict__ err, const __grid_constant__ gc::GatherParams pp,
                  int push_ctas, const __grid_constant__ SplitMaps osplit) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;
-  uint8_t* sK = smem + TILE_BYTES;
+  uint8_t* sQ = smem;                               // tile t at sQ + t * TILE_BYTES (reused as output staging)
+  uint8_t* sK = smem + 2 * TILE_BYTES;
   uint8_t* sV = sK + KV_STAGES * TILE_BYTES;
   Bars* bars = (Bars*)(smem + SMEM_TILES);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_q_tiles = (Tq + BM - 1) / BM;
-  const int qt = causal ? (num_q_tiles - 1 - (int)blockIdx.x) : (int)blockIdx.x;   // heavy tiles first
+  const int num_pairs = (Tq + CTA_ROWS - 1) / CTA_ROWS;
+  const int pair = causal ? (num_pairs - 1 - (int)blockIdx.x) : (int)blockIdx.x;    // heavy tiles first
   const int head = blockIdx.y;
   const int kv_head = head / (H / Hkv);
-  const int q0 = qt * BM;
-  const int nblk = causal ? (qt + 1) : (Tk + BN - 1) / BN;
+  const int q0 = pair * CTA_ROWS;
+  const bool has_b = q0 + BM < Tq;
+  const int kv_blocks = (Tk + BN - 1) / BN;
+  // blocks each tile attends to: causal tile A ends on its diagonal block q0 / 128, tile B one block later
+  const int nA = causal ? (q0 / BN + 1) : kv_blocks;
+  const int nB = has_b ? (causal ? nA + 1 : kv_blocks) : 0;
+  const int nblk = nA > nB ? nA : nB;
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->q_full[0], 1);
+    mbar_init(&bars->q_full[1], 1);
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(&bars->k_full[s], 1);
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_full[s], 1);
       mbar_init(&bars->v_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&bars->s_full[b], 1);
-      mbar_init(&bars->s_free[b], 256);
-      mbar_init(&bars->p_full[b], 256);
-      mbar_init(&bars->pv_done[b], 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_full[t], 128);
+      mbar_init(&bars->o_done[t], 1);
     }
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
@@ -136,7 +137,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  // PUSH: 512 threads start with 128 registers each; the softmax warpgroups need more, everyone else far less
   if (warp >= 12) {
     // ------------------------------------------------------------------ comm warps (PUSH only)
     if constexpr (PUSH) {
@@ -145,232 +145,254 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (cta < push_ctas) gc::comm_warps_main(pp, cta, push_ctas, 12 * 32, abort_flag, err);
     }
   } else if (warp < 4) {
-   if constexpr (PUSH) reg_dec<REGS_ISSUE>();
-   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      mbar_expect_tx(&bars->q_full, TILE_BYTES);
-      tma_load_3d(sQ, &tmQ, 0, head, q0, &bars->q_full);
-      tma_load_3d(sQ + HALF_BYTES, &tmQ, 64, head, q0, &bars->q_full);
-      for (int j = 0; j < nblk; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
-        tma_load_3d(sK + s * TILE_BYTES, &tmK, 0, kv_head, j * BN, &bars->k_full[s]);
-        tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, 64, kv_head, j * BN, &bars->k_full[s]);
-        if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
-        mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
-        tma_load_3d(sV + s * TILE_BYTES, &tmV, 0, kv_head, j * BN, &bars->v_full[s]);
-        tma_load_3d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, 64, kv_head, j * BN, &bars->v_full[s]);
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ Q K^T issuer
-    if (lane == 0) {
-      constexpr uint32_t IDESC_QK = make_idesc_bf16(BM, BN, 0, 0);
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
-      const uint64_t qdesc0 = make_smem_desc(smem_u32(sQ), 16, 1024);
-      const uint64_t kdesc0 = make_smem_desc(smem_u32(sK), 16, 1024);
-      for (int j = 0; j < nblk && ok; ++j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const bool tr = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && j < 48;
-        if (tr) dbg[j * 8 + 0] = clock64();
-        if (!mbar_wait(&bars->k_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
-        // S buffer b was last read by the softmax of block j-2
-        if (j >= 2 && !mbar_wait(&bars->s_free[b], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
-        if (tr) dbg[j * 8 + 1] = clock64();
-        tc_fence_after();
-        const uint64_t k0 = desc_advance(kdesc0, b * TILE_BYTES);
-        umma_ss(tmem + COL_S + b * BN, qdesc0, k0, IDESC_QK, 0u);
-#pragma unroll
-        for (int kk = 1; kk < HD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          umma_ss(tmem + COL_S + b * BN, desc_advance(qdesc0, off), desc_advance(k0, off), IDESC_QK, 1u);
+    reg_dec<PUSH ? REGS_ISSUE_PUSH : REGS_ISSUE>();
+    if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        mbar_expect_tx(&bars->q_full[0], TILE_BYTES);
+        tma_load_3d(sQ, &tmQ, 0, head, q0, &bars->q_full[0]);
+        tma_load_3d(sQ + HALF_BYTES, &tmQ, 64, head, q0, &bars->q_full[0]);
+        if (has_b) {
+          mbar_expect_tx(&bars->q_full[1], TILE_BYTES);
+          tma_load_3d(sQ + TILE_BYTES, &tmQ, 0, head, q0 + BM, &bars->q_full[1]);
+          tma_load_3d(sQ + TILE_BYTES + HALF_BYTES, &tmQ, 64, head, q0 + BM, &bars->q_full[1]);
         }
-        umma_commit(&bars->k_empty[b]);
-        umma_commit(&bars->s_full[b]);
-        if (tr) dbg[j * 8 + 2] = clock64();
+        int issued_k = 0, issued_v = 0;
+        for (int j = 0; j < nblk; ++j) {
+          const int s = j & 1;
+          const uint32_t ph = (j >> 1) & 1;
+          if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+          mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
+          tma_load_3d(sK + s * TILE_BYTES, &tmK, 0, kv_head, j * BN, &bars->k_full[s]);
+          tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, 64, kv_head, j * BN, &bars->k_full[s]);
+          ++issued_k;
+          if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+          mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
+          tma_load_3d(sV + s * TILE_BYTES, &tmV, 0, kv_head, j * BN, &bars->v_full[s]);
+          tma_load_3d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, 64, kv_head, j * BN, &bars->v_full[s]);
+          ++issued_v;
+        }
+        if (*abort_flag) {
+          // somebody gave up: nobody may be consuming any more, so let the copies still in flight land before the
+          // CTA's shared memory goes away (bounded)
+          const long long t0 = clock64();
+          for (int b = 0; b < 2; ++b) {
+            const int jk = issued_k - 1 - b, jv = issued_v - 1 - b;
+            while (jk >= 0 && !mbar_try_wait(&bars->k_full[jk & 1], (jk >> 1) & 1) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+            while (jv >= 0 && !mbar_try_wait(&bars->v_full[jv & 1], (jv >> 1) & 1) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+          }
+        }
       }
-      if (!ok) {
-        umma_commit(&bars->drain);
-        const long long t0 = clock64();
-        while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
-      }
-    }
-  } else if (warp == 2) {
-    // ------------------------------------------------------------------ P V issuer
-    if (lane == 0) {
-      constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
-      const uint64_t vdesc0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
-      for (int j = 0; j < nblk; ++j) {
-        const int b = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&bars->p_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) break;
-        if (!mbar_wait(&bars->v_full[b], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) break;
-        const bool tr = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && j < 48;
-        if (tr) dbg[j * 8 + 3] = clock64();
-        tc_fence_after();
-        const uint64_t v0 = desc_advance(vdesc0, b * TILE_BYTES);
-        const uint32_t pa = tmem + COL_P + b * 64;
-        umma_ts(tmem + COL_O, pa, v0, IDESC_PV, j > 0 ? 1u : 0u);
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ MMA issuer
+      if (lane == 0) {
+        constexpr uint32_t IDESC_QK = make_idesc_bf16(BM, BN, 0, 0);
+        constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
+        const uint64_t qdesc0 = make_smem_desc(smem_u32(sQ), 16, 1024);
+        const uint64_t kdesc0 = make_smem_desc(smem_u32(sK), 16, 1024);
+        const uint64_t vdesc0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
+        bool ok = true;
+        // S_t = Q_t K(j)^T
+        auto issue_qk = [&](int t, int j) {
+          const uint64_t q = desc_advance(qdesc0, t * TILE_BYTES);
+          const uint64_t k = desc_advance(kdesc0, (j & 1) * TILE_BYTES);
+          const uint32_t d = tmem + COL_S + t * BN;
+          umma_ss(d, q, k, IDESC_QK, 0u);
 #pragma unroll
-        for (int kk = 1; kk < BN / 16; ++kk) umma_ts(tmem + COL_O, pa + kk * 8, desc_advance(v0, kk * 2048), IDESC_PV, 1u);
-        umma_commit(&bars->v_empty[b]);
-        umma_commit(&bars->pv_done[b]);
-        if (tr) dbg[j * 8 + 4] = clock64();
+          for (int kk = 1; kk < HD / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+            umma_ss(d, desc_advance(q, off), desc_advance(k, off), IDESC_QK, 1u);
+          }
+          umma_commit(&bars->s_full[t]);
+        };
+        // O_t (+)= P_t V(j)
+        auto issue_pv = [&](int t, int j) {
+          const uint64_t v = desc_advance(vdesc0, (j & 1) * TILE_BYTES);
+          const uint32_t pa = tmem + COL_S + t * BN;
+          const uint32_t d = tmem + COL_O + t * HD;
+          umma_ts(d, pa, v, IDESC_PV, j > 0 ? 1u : 0u);
+#pragma unroll
+          for (int kk = 1; kk < BN / 16; ++kk) umma_ts(d, pa + kk * 8, desc_advance(v, kk * 2048), IDESC_PV, 1u);
+        };
+        ok = mbar_wait(&bars->q_full[0], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL) &&
+             mbar_wait(&bars->k_full[0], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
+        if (ok) {
+          tc_fence_after();
+          issue_qk(0, 0);
+          if (nB > 0) {
+            ok = mbar_wait(&bars->q_full[1], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
+            if (ok) issue_qk(1, 0);
+          }
+          umma_commit(&bars->k_empty[0]);
+        }
+        for (int j = 0; j < nblk && ok; ++j) {
+          const int s = j & 1, s1 = (j + 1) & 1;
+          const uint32_t ph = (j >> 1) & 1, ph1 = ((j + 1) >> 1) & 1;
+          bool have_v = false, have_k1 = false;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int nt = t == 0 ? nA : nB;
+            if (j >= nt) continue;
+            if (!mbar_wait(&bars->p_full[t], j & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+            if (!have_v) {
+              if (!mbar_wait(&bars->v_full[s], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
+              have_v = true;
+            }
+            tc_fence_after();
+            issue_pv(t, j);
+            if (j + 1 < nt) {
+              if (!have_k1) {
+                if (!mbar_wait(&bars->k_full[s1], ph1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
+                have_k1 = true;
+              }
+              issue_qk(t, j + 1);      // its commit on s_full[t] also covers the P V just issued
+            } else {
+              umma_commit(&bars->o_done[t]);
+            }
+          }
+          if (!ok) break;
+          umma_commit(&bars->v_empty[s]);
+          if (have_k1) umma_commit(&bars->k_empty[s1]);
+        }
+        if (!ok) {
+          umma_commit(&bars->drain);
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+        }
       }
-    }
-   }   // warp 3 idles: it only keeps the warpgroups aligned
+    }   // warps 2, 3 idle: they only keep the warpgroups aligned
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue (warps 4..11)
-    if constexpr (PUSH) reg_inc<REGS_MATH>();
+    // ------------------------------------------------------------------ softmax + epilogue (warpgroup t handles tile t)
+    reg_inc<PUSH ? REGS_MATH_PUSH : REGS_MATH>();
+    const int t = (warp - 4) >> 2;                     // 0 = tile A, 1 = tile B
     const int q = warp & 3;                            // TMEM lane quarter
-    const int hf = (warp - 4) >> 2;                    // key columns [hf * 64, hf * 64 + 64) of every block
     const int r = q * 32 + lane;                       // row inside the tile == TMEM lane
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const uint32_t col_s = tmem + COL_S + t * BN + lane_off;
+    const uint32_t col_o = tmem + COL_O + t * HD + lane_off;
+    const int nt = t == 0 ? nA : nB;
+    const int qt0 = q0 + t * BM;                       // first query row of this tile
+    const int diag = causal ? qt0 / BN : -1;           // block holding this tile's diagonal
     const float sl2 = scale * 1.4426950408889634f;
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
-    // `ok` is kept warp-uniform; the two warps of a lane quarter agree on it at their exchange barrier, so
-    // they always leave the loop in the same iteration
-    for (int j = 0; j < nblk; ++j) {
-      const int b = j & 1;
-      const bool str_ = dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 128 && j < 48;
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[b], (j >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
-      if (str_) dbg[j * 8 + 5] = clock64();
-      uint32_t sv[64];
-      float mx = -INFINITY;
-      if (ok) {
-        tc_fence_after();
-        tmem_ld_32x32(tmem + COL_S + b * BN + hf * 64 + lane_off, sv);
-        tmem_ld_32x32(tmem + COL_S + b * BN + hf * 64 + 32 + lane_off, sv + 32);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(&bars->s_free[b]);                 // S(j) is in registers: Q K^T of block j+2 may overwrite it
-        const int kv0 = j * BN + hf * 64;
-        if (causal && j == qt) {
+    for (int j = 0; j < nt; ++j) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[t], j & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[128];
+      tmem_ld_32x32(col_s, sv);
+      tmem_ld_32x32(col_s + 32, sv + 32);
+      tmem_ld_32x32(col_s + 64, sv + 64);
+      tmem_ld_32x32(col_s + 96, sv + 96);
+      tmem_ld_wait();
+      const int kv0 = j * BN;
+      if (j == diag) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if (hf * 64 + c > r) sv[c] = 0xff800000u;   // -inf
-        }
-        if (kv0 + 64 > Tk) {
-#pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if (kv0 + c >= Tk) sv[c] = 0xff800000u;
-        }
-        // partial row maximum over our 64 columns, four independent chains
-        float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]), m2 = __uint_as_float(sv[2]), m3 = __uint_as_float(sv[3]);
-#pragma unroll
-        for (int c = 4; c < 64; c += 4) {
-          m0 = fmaxf(m0, __uint_as_float(sv[c]));
-          m1 = fmaxf(m1, __uint_as_float(sv[c + 1]));
-          m2 = fmaxf(m2, __uint_as_float(sv[c + 2]));
-          m3 = fmaxf(m3, __uint_as_float(sv[c + 3]));
-        }
-        mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-        // the two threads of a row swap partial maxima (double-buffered on the block parity)
-        bars->pmax[b][hf][r] = mx;
+        for (int c = 0; c < 128; ++c)
+          if (c > r) sv[c] = 0xff800000u;               // -inf
       }
-      if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
-      if (str_) dbg[j * 8 + 6] = clock64();
-      mx = fmaxf(mx, bars->pmax[b][hf ^ 1][r]);
-      const float m_new = fmaxf(m_used, mx * sl2);
-      const bool need = (m_new - m_used) > 8.f;      // true on the first block (m_used = -inf)
+      if (kv0 + BN > Tk) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (kv0 + c >= Tk) sv[c] = 0xff800000u;
+      }
+      // row maximum, four independent chains
+      float mx[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) mx[i] = __uint_as_float(sv[i]);
+#pragma unroll
+      for (int c = 4; c < 128; c += 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx[i] = fmaxf(mx[i], __uint_as_float(sv[c + i]));
+      }
+      const float rmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float m_new = fmaxf(m_used, rmax * sl2);
+      const bool need = (m_new - m_used) > 8.f;        // true on the first block (m_used = -inf)
       if (j == 0) {
         m_used = m_new;
       } else if (__any_sync(0xffffffffu, need)) {
-        // the running maximum moved by more than 2^8 for some row of this warp: rescale O (our 64 columns) and l
-        ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
-        if (ok) {
-          tc_fence_after();
-          const float alpha = need ? fast_exp2(m_used - m_new) : 1.f;
-          if (need) m_used = m_new;
-          l *= alpha;
+        // the running maximum moved by more than 2^8 for some row of this warp: rescale O and l.  P V of block j-1
+        // completed before S(j) was announced and P V of block j waits for this thread, so O is ours now.
+        const float alpha = need ? exp2_mufu(m_used - m_new) : 1.f;
+        if (need) m_used = m_new;
+        l *= alpha;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t o[16];
+          tmem_ld_32x16(col_o + c * 16, o);
+          tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[16];
-            tmem_ld_32x16(tmem + COL_O + hf * 64 + lane_off + c * 16, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int t = 0; t < 16; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * alpha);
-            tmem_st_32x16(tmem + COL_O + hf * 64 + lane_off + c * 16, o);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x16(col_o + c * 16, o);
         }
       }
-      // packed pairs: x = s * scale * log2(e) - m for two columns per instruction, two running partial sums
+      // packed pairs: x = s * scale * log2(e) - m for two columns per instruction; P goes back over S in four
+      // 32-column pieces (16 packed registers each)
       const uint64_t sl2_2 = pk2(sl2, sl2), nm_2 = pk2(-m_used, -m_used);
       uint64_t rs2 = pk2(0.f, 0.f);
-      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float p0, p1;
-        const uint64_t x2 = fma2(pk2u(sv[2 * c], sv[2 * c + 1]), sl2_2, nm_2);
-        if ((c % ODY_FWD_POLY_DEN) < ODY_FWD_POLY_NUM) {
-          exp2_poly2(x2, p0, p1);
-        } else {
-          upk2(x2, p0, p1);
-          p0 = exp2_mufu(p0);
-          p1 = exp2_mufu(p1);
+      for (int g = 0; g < 4; ++g) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          float p0, p1;
+          const uint64_t x2 = fma2(pk2u(sv[32 * g + 2 * c], sv[32 * g + 2 * c + 1]), sl2_2, nm_2);
+          if ((c % ODY_FWD_POLY_DEN) < ODY_FWD_POLY_NUM) {
+            exp2_poly2(x2, p0, p1);
+          } else {
+            upk2(x2, p0, p1);
+            p0 = exp2_mufu(p0);
+            p1 = exp2_mufu(p1);
+          }
+          rs2 = add2(rs2, pk2(p0, p1));
+          pk[c] = pack_bf16(p0, p1);
         }
-        rs2 = add2(rs2, pk2(p0, p1));
-        pk[c] = pack_bf16(p0, p1);
+        tmem_st_32x16(col_s + g * 16, pk);
       }
       {
         float r0, r1;
         upk2(rs2, r0, r1);
         l += r0 + r1;
       }
-      if (ok && j >= 2)   // P buffer b was last read by P V of block j-2
-        ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[b], ((j - 2) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
-      if (ok) {
-        tmem_st_32x16(tmem + COL_P + b * 64 + hf * 32 + lane_off, pk);
-        tmem_st_32x16(tmem + COL_P + b * 64 + hf * 32 + 16 + lane_off, pk + 16);
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(&bars->p_full[b]);
-        if (str_) dbg[j * 8 + 7] = clock64();
-      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[t]);
     }
-    // epilogue: O / l -> bf16 -> swizzled smem (the Q tile is dead by now) -> TMA store; lse
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
-    // the row sum is split over the two threads of a row
-    bars->pmax[0][hf][r] = l;
-    named_barrier(4 + q, 64);
-    l += bars->pmax[0][hf ^ 1][r];
-    if (ok) {
+    // epilogue: O / l -> bf16 -> swizzled smem (this tile's Q is dead by now) -> TMA store; lse
+    if (ok && nt > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_done[t], 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
+    uint8_t* stage = sQ + t * TILE_BYTES;
+    if (ok && nt > 0) {
       tc_fence_after();
       const float inv_l = 1.f / l;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {                   // our 64 output columns = staging half `hf`
-        uint32_t o[16];
-        tmem_ld_32x16(tmem + COL_O + hf * 64 + lane_off + c * 16, o);
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(col_o + c * 32, o);
         tmem_ld_wait();
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
+        for (int i = 0; i < 4; ++i) {
           uint4 v4;
-          v4.x = pack_bf16(__uint_as_float(o[8 * t + 0]) * inv_l, __uint_as_float(o[8 * t + 1]) * inv_l);
-          v4.y = pack_bf16(__uint_as_float(o[8 * t + 2]) * inv_l, __uint_as_float(o[8 * t + 3]) * inv_l);
-          v4.z = pack_bf16(__uint_as_float(o[8 * t + 4]) * inv_l, __uint_as_float(o[8 * t + 5]) * inv_l);
-          v4.w = pack_bf16(__uint_as_float(o[8 * t + 6]) * inv_l, __uint_as_float(o[8 * t + 7]) * inv_l);
-          const int chunk = c * 2 + t;                // 16-byte chunk inside the 128-byte row of this half
-          *reinterpret_cast<uint4*>(sQ + hf * HALF_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
+          v4.x = pack_bf16(__uint_as_float(o[8 * i + 0]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l);
+          v4.y = pack_bf16(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
+          v4.z = pack_bf16(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
+          v4.w = pack_bf16(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
+          const int chunk = (c & 1) * 4 + i;            // 16-byte chunk inside the 128-byte row of half c / 2
+          *reinterpret_cast<uint4*>(stage + (c >> 1) * HALF_BYTES + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
         }
       }
-      if (hf == 0 && q0 + r < Tq) lse[(int64_t)head * Tq + q0 + r] = (m_used + log2f(l)) * 0.6931471805599453f;
+      if (qt0 + r < Tq) lse[(int64_t)head * Tq + qt0 + r] = (m_used + log2f(l)) * 0.6931471805599453f;
       fence_proxy_async_smem();
     }
     tc_fence_before();
-    named_barrier(1, 256);
-    if (ok && warp == 4 && lane == 0 && !*abort_flag) {
-      tma_store_3d(&tmO, sQ, 0, head, q0);
-      tma_store_3d(&tmO, sQ + HALF_BYTES, 64, head, q0);
+    const bool all_ok = named_barrier_and(1 + t, 128, ok);
+    if (all_ok && nt > 0 && q == 0 && lane == 0 && !*abort_flag) {
+      tma_store_3d(&tmO, stage, 0, head, qt0);
+      tma_store_3d(&tmO, stage + HALF_BYTES, 64, head, qt0);
       if (osplit.rows > 0) {
-        const int d = q0 / osplit.rows;
-        tma_store_3d(&osplit.m[d], sQ, 0, head, q0 - d * osplit.rows);
-        tma_store_3d(&osplit.m[d], sQ + HALF_BYTES, 64, head, q0 - d * osplit.rows);
+        const int d = qt0 / osplit.rows;
+        tma_store_3d(&osplit.m[d], stage, 0, head, qt0 - d * osplit.rows);
+        tma_store_3d(&osplit.m[d], stage + HALF_BYTES, 64, head, qt0 - d * osplit.rows);
       }
       tma_store_commit();
       tma_store_wait<0>();
@@ -388,16 +410,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }  // namespace fwd
 }  // namespace ody
 
-static long long* g_fwd_trace = nullptr;
-// Optional per-block timeline (48 x 8 SM-clock stamps) of the CTA with blockIdx (0, 0).
-extern "C" void ody_flash_fwd_set_trace(long long* buf) { g_fwd_trace = buf; }
-
 // q/k/v/o: bf16, head_dim 128, element strides: *_row (token pitch), heads packed (pitch 128).
 extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int Tq, int Tk, int H,
                              int Hkv, int64_t q_row, int64_t k_row, int64_t v_row, int64_t o_row, int causal,
                              float scale, int* err, cudaStream_t st) {
   return ody_flash_fwd_ex(q, k, v, o, lse, Tq, Tk, H, Hkv, q_row, k_row, v_row, o_row, causal, scale, nullptr, nullptr, 0, 0, 0,
                           err, st);
+}
+
+// CTAs of the forward grid for Tq query rows and H heads: what a push description's n_cta may not exceed.
+extern "C" int ody_flash_fwd_ctas(int Tq, int H) {
+  return ((Tq + ody::fwd::CTA_ROWS - 1) / ody::fwd::CTA_ROWS) * H;
 }
 
 extern "C" int ody_flash_set_push_order(int unit_major) {
@@ -451,20 +474,18 @@ extern "C" int ody_flash_fwd_ex(const void* q, const void* k, const void* v, voi
     }
     sm.rows = split_rows;
   }
-  dim3 grid((Tq + BM - 1) / BM, H);
+  dim3 grid((Tq + CTA_ROWS - 1) / CTA_ROWS, H);
+  gc::GatherParams pp;
+  memset(&pp, 0, sizeof(pp));
   if (push != nullptr) {
-    gc::GatherParams pp;
-    memset(&pp, 0, sizeof(pp));
     if ((r = gc::fill_gather(pp, push))) return r;
     const int ctas = (int)(grid.x * grid.y);
     if (push->n_cta <= 0 || push->n_cta > ctas) return (int)cudaErrorInvalidValue;
     flash_fwd_kernel<true><<<grid, NUM_THREADS_PUSH, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
-                                                                       g_fwd_trace, pp, push->n_cta, sm);
+                                                                       pp, push->n_cta, sm);
   } else {
-    gc::GatherParams pp;
-    memset(&pp, 0, sizeof(pp));
     flash_fwd_kernel<false><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
-                                                                    g_fwd_trace, pp, 0, sm);
+                                                                    pp, 0, sm);
   }
   return (int)cudaGetLastError();
 }

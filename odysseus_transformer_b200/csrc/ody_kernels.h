@@ -68,8 +68,10 @@ int ody_flash_fwd(const void* q, const void* k, const void* v, void* o, float* l
 // ---- attention backward.  workspace: ody_flash_bwd_workspace_bytes(Tq, H) bytes of scratch, 16-byte aligned.
 // dq/dk/dv may be row-pitched views (e.g. slices of one packed gradient tensor).
 int64_t ody_flash_bwd_workspace_bytes(int Tq, int H);
-void ody_flash_fwd_set_trace(long long* buf);
-void ody_flash_bwd_set_trace(long long* buf);   /* optional 48 x 8 int64 timeline of one CTA; NULL switches it off */
+/* CTAs of the forward grid (one per 256 query rows and head): the upper bound of a push description's n_cta */
+int ody_flash_fwd_ctas(int Tq, int H);
+/* optional 96 x 8 int64 timeline of one CTA of each backward kernel; recorded only by a build with -DODY_ATTN_TRACE */
+void ody_flash_bwd_set_trace(long long* buf);
 int ody_flash_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,
                   void* dk, void* dv, void* workspace, int Tq, int Tk, int H, int Hkv, int64_t do_row, int64_t q_row,
                   int64_t k_row, int64_t v_row, int64_t o_row, int64_t dq_row, int64_t dk_row, int64_t dv_row, int causal,

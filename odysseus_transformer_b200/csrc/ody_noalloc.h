@@ -15,6 +15,11 @@
 // Limits and rules:
 //   * dim must be a multiple of 8 and at most ODY_NOALLOC_RMSNORM_MAX_DIM; larger sizes are refused
 //     with ODY_NOALLOC_ERR_TOO_LARGE before anything is launched (ody_noalloc_strerror explains codes).
+//   * Pointers: dy, x, w, dx (and ds when given) must be non-null device pointers aligned to 16 bytes, rstd and dw
+//     non-null and aligned to 4 bytes (rows are dim * 2 bytes apart with dim a multiple of 8, so every row then
+//     starts on a 16-byte boundary too).  Anything else is refused with ODY_NOALLOC_ERR_BAD_POINTER before a
+//     launch - the kernels use 16-byte accesses and would otherwise fault on the device.  With rows == 0 only dw
+//     is touched (set to zero); the other pointers may then be null.
 //   * The first call on each device looks up the scratch array's device address (one
 //     cudaGetSymbolAddress with that device current).  Make that first call outside of any stream
 //     capture; later calls only launch kernels.
@@ -30,6 +35,7 @@
 #define ODY_NOALLOC_RMSNORM_SCRATCH_BYTES (ODY_NOALLOC_RMSNORM_MAX_BLOCKS * ODY_NOALLOC_RMSNORM_MAX_DIM * 4)
 #define ODY_NOALLOC_ERR_TOO_LARGE 9001
 #define ODY_NOALLOC_ERR_BAD_SHAPE 9002
+#define ODY_NOALLOC_ERR_BAD_POINTER 9003
 
 #ifdef __cplusplus
 extern "C" {

@@ -117,6 +117,17 @@ extern "C" int ody_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   using namespace ody::noalloc;
   if (rows < 0 || dim <= 0 || (dim % 8) != 0) return ODY_NOALLOC_ERR_BAD_SHAPE;
   if (dim > ODY_NOALLOC_RMSNORM_MAX_DIM) return ODY_NOALLOC_ERR_TOO_LARGE;
+  // the kernels move 16 bytes per access on dy / x / w / ds / dx and 4 on rstd / dw: a null or misaligned pointer
+  // would fault on the device, so it is refused here instead
+  if (dw == nullptr || ((uintptr_t)dw & 3)) return ODY_NOALLOC_ERR_BAD_POINTER;
+  if (rows > 0) {
+    if (dy == nullptr || x == nullptr || w == nullptr || rstd == nullptr || dx == nullptr) return ODY_NOALLOC_ERR_BAD_POINTER;
+    if ((((uintptr_t)dy | (uintptr_t)x | (uintptr_t)w | (uintptr_t)dx | (uintptr_t)ds) & 15) || ((uintptr_t)rstd & 3))
+      return ODY_NOALLOC_ERR_BAD_POINTER;
+  } else {
+    // no rows: the sum over nothing.  dw is cleared with a plain asynchronous memset; nothing else is touched.
+    return (int)cudaMemsetAsync(dw, 0, (size_t)dim * sizeof(float), stream);
+  }
   float* scratch = nullptr;
   const int rc = scratch_for_current_device(&scratch);
   if (rc != 0) return rc;
@@ -138,6 +149,9 @@ extern "C" const char* ody_noalloc_strerror(int code) {
       return "ody_rmsnorm_bwd_noalloc: dim exceeds ODY_NOALLOC_RMSNORM_MAX_DIM (8192); the built-in scratch array cannot hold it";
     case ODY_NOALLOC_ERR_BAD_SHAPE:
       return "ody_rmsnorm_bwd_noalloc: rows must be >= 0 and dim a positive multiple of 8";
+    case ODY_NOALLOC_ERR_BAD_POINTER:
+      return "ody_rmsnorm_bwd_noalloc: dy, x, w, dx (and ds when given) must be non-null and 16-byte aligned; rstd and dw "
+             "non-null and 4-byte aligned";
     default: return cudaGetErrorString((cudaError_t)code);
   }
 }

@@ -339,7 +339,7 @@ def ring_attn_fwd(q, k, v, group, scale):
     Tb, hq = q.shape[0], q.shape[1]
     half = Tb // 2
     # the push is spread over every CTA of the smaller step grid: a CTA's comm warps then finish with its tiles
-    n_push = min(((half + 127) // 128) * hq, 4096)
+    n_push = min(int(lib.attn_fwd_ctas(half, hq)), 4096)
     base = slot.push_desc(shard, n_push)
     gathered = slot.view().view(R, Tb, 2, k.shape[1], 128)
 

@@ -311,5 +311,10 @@ def build_parser() -> argparse.ArgumentParser:
     return p
 
 
-if __name__ == "__main__":
+def cli() -> None:
+    """Console entry point (``odysseus-train``): the same flags as ``python train.py``."""
     main(build_parser().parse_args())
+
+
+if __name__ == "__main__":
+    cli()

@@ -158,6 +158,51 @@ def test_adamw(lib):
     torch.testing.assert_close(p.float(), p2.float(), rtol=1e-2, atol=1e-3)
 
 
+def test_adamw_guard_word_blocks_the_update(lib):
+    """A non-zero guard word (the step's kernel status) must leave master, moments and parameters untouched; zero lets it run."""
+    n = 8 * 4099
+    master, m, v = torch.randn(n, device="cuda"), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    g = _rand(n, scale=0.01)
+    p = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    keep = [t.clone() for t in (master, m, v, p)]
+    guard = torch.tensor([105.0], device="cuda")
+    lib.adamw_step(master, m, v, g, p, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, guard)
+    for t, k in zip((master, m, v, p), keep):
+        assert torch.equal(t, k)
+    guard.zero_()
+    lib.adamw_step(master, m, v, g, p, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, guard)
+    assert not torch.equal(master, keep[0]) and not torch.equal(m, keep[1])
+    with pytest.raises(RuntimeError):
+        lib.adamw_step(master, m, v, g, p, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, torch.zeros(1))   # guard not on the device
+
+
+def test_launchers_reject_mismatched_shapes_before_launching(lib):
+    """Host-side checks only: every call below must raise without a kernel being launched (the launchers build tensor
+    maps from the shapes they are told, so a mismatch would otherwise read past an allocation)."""
+    lib.reset_launch_count()
+    T, H = 256, 2
+    q, k, v, o, do = (_rand(T, H, 128) for _ in range(5))
+    lse = torch.zeros(H, T, device="cuda")
+    bad = [
+        lambda: lib.attn_bwd(do, q, k, _rand(T // 2, H, 128), o, lse, True, 0.1),          # v shorter than k
+        lambda: lib.attn_bwd(do, q, k, _rand(T, 1, 128), o, lse, True, 0.1),               # v with fewer heads
+        lambda: lib.attn_bwd(do, _rand(T, 3, 128), _rand(T, 2, 128), _rand(T, 2, 128), _rand(T, 3, 128),
+                             torch.zeros(3, T, device="cuda"), True, 0.1),                   # 3 query heads on 2 kv heads
+        lambda: lib.attn_bwd(do, q, k, v, o, torch.zeros(H, T), True, 0.1),                  # lse on the host
+        lambda: lib.attn_bwd_split(do, q, k, _rand(T // 2, H, 128), o, lse, True, 0.1, [q], [k], [v]),
+        lambda: lib.rmsnorm_bwd(_rand(8, 64), _rand(16, 64), _rand(64), torch.ones(16, device="cuda"), None),   # dy != x
+        lambda: lib.rmsnorm_bwd(_rand(16, 64), _rand(16, 64), _rand(32), torch.ones(16, device="cuda"), None),  # short w
+        lambda: lib.rmsnorm_bwd(_rand(16, 64), _rand(16, 64), _rand(64), torch.ones(8, device="cuda"), None),   # short rstd
+        lambda: lib.rmsnorm_bwd(_rand(16, 64), _rand(16, 64), _rand(64), torch.ones(16), None),                 # rstd on host
+        lambda: lib.rmsnorm_bwd(_rand(16, 64), _rand(16, 64), _rand(64), torch.ones(16, device="cuda"), _rand(8, 64)),
+    ]
+    for i, f in enumerate(bad):
+        with pytest.raises(RuntimeError):
+            f()
+    assert lib.launch_count() == 0
+    _check_status(lib)
+
+
 def test_attn_merge(lib):
     from odysseus_transformer_b200.ops import torch_ref as R
     Tt, T, H, hd, row0 = 96, 48, 3, 128, 48
@@ -241,6 +286,8 @@ def test_model_step_fused_vs_library():
 ATTN_CASES = [  # Tq, Tk, H, Hkv, causal
     (128, 128, 2, 2, True), (512, 512, 4, 2, True), (1000, 1000, 2, 1, True), (2048, 2048, 8, 8, True),
     (256, 384, 2, 2, False), (300, 200, 4, 1, False), (128, 1024, 2, 2, False),
+    # the forward works on pairs of 128-row query tiles: an odd number of tiles, a ragged second tile, long loops
+    (384, 384, 2, 2, True), (1408, 1408, 2, 1, True), (4096, 4096, 2, 2, True), (384, 520, 2, 2, False),
 ]
 
 
@@ -255,6 +302,25 @@ def test_attention_fwd(lib, Tq, Tk, H, Hkv, causal):
     orf, lser = R.attn_fwd(q, k, v, causal, scale)
     torch.testing.assert_close(lse, lser, rtol=1e-3, atol=2e-3)
     torch.testing.assert_close(o.float(), orf.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_attention_fwd_growing_scores_rescale(lib):
+    """Keys whose scores grow along the sequence move the running row maximum by more than 2^8 again and again,
+    so the lazy rescaling of the output accumulator runs in (almost) every block."""
+    from odysseus_transformer_b200.ops import torch_ref as R
+    torch.manual_seed(5)
+    T, H = 1024, 2
+    q = _rand(T, H, 128).abs()
+    ramp = torch.linspace(0.2, 6.0, T, device="cuda").view(T, 1, 1)
+    k = (_rand(T, H, 128).abs().float() * ramp).to(torch.bfloat16)
+    v = _rand(T, H, 128)
+    scale = 1.0 / math.sqrt(128)
+    for causal in (True, False):
+        o, lse = lib.attn_fwd(q, k, v, causal, scale)
+        _check_status(lib)
+        orf, lser = R.attn_fwd(q, k, v, causal, scale)
+        torch.testing.assert_close(o.float(), orf.float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(lse, lser, rtol=1e-3, atol=2e-2)
 
 
 def test_attention_fwd_packed_views(lib):

@@ -2,9 +2,10 @@
 
 ``ody_rmsnorm_bwd_noalloc`` serves callers that cannot (or may not) allocate device memory: its scratch
 is a fixed array inside the library.  The test goes through the exported C symbol with raw pointers,
-twice in a row with different shapes and inputs, and checks each result against the regular entry point
-(which takes its workspace from PyTorch's allocator) within the tolerances of the other kernel tests.
-It runs last so that a failure here cannot hide results of any other test."""
+several times in a row with different shapes and inputs, and checks each result against the regular entry
+point (which takes its workspace from PyTorch's allocator) and against a plain fp32 PyTorch evaluation of the
+same formula, within the tolerances of the other kernel tests.  Bad pointers and sizes must come back as error
+codes without a launch.  It runs last so that a failure here cannot hide results of any other test."""
 import ctypes
 import math
 import os
@@ -48,6 +49,13 @@ def _one_call(lib, fn, rows, dim, with_ds):
     torch.cuda.synchronize()
     torch.testing.assert_close(dx.float(), dx_ref.float(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(dw, dw_ref, rtol=1e-3, atol=1e-2 * math.sqrt(rows))
+    # the same op in plain fp32 PyTorch (ops/torch_ref.py is the oracle of every kernel test)
+    from odysseus_transformer_b200.ops import torch_ref
+    dx32, dw32 = torch_ref.rmsnorm_bwd(dy.float(), x.float(), w.float(), rstd)
+    if with_ds:
+        dx32 = dx32 + ds.float()
+    torch.testing.assert_close(dx.float(), dx32, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(dw, dw32.float(), rtol=1e-3, atol=1e-2 * math.sqrt(rows))
 
 
 def test_noalloc_rmsnorm_bwd_matches_regular_entry_point_twice():
@@ -73,3 +81,37 @@ def test_noalloc_rejects_sizes_beyond_the_built_in_scratch():
     assert b"exceeds" in err(rc)
     assert fn(x.data_ptr(), x.data_ptr(), x.data_ptr(), rstd.data_ptr(), None, x.data_ptr(), dw.data_ptr(), 8, 12,
               torch.cuda.current_stream().cuda_stream) == 9002
+
+
+def test_noalloc_refuses_bad_pointers_and_handles_zero_rows():
+    """Null or misaligned buffers are answered with an error code on the host (the kernels use 16-byte accesses and
+    would fault on them); zero rows is a valid call that only clears dw."""
+    torch.cuda.set_device(0)
+    lib, fn, err = _load()
+    rows, dim = 16, 256
+    dy, x, w = _rand(rows, dim), _rand(rows, dim), _rand(dim)
+    rstd = torch.ones(rows, device="cuda")
+    dx = torch.empty_like(x)
+    dw = torch.full((dim,), 7.0, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    good = [dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), None, dx.data_ptr(), dw.data_ptr()]
+    for i in (0, 1, 2, 3, 5, 6):                      # each required pointer null in turn
+        a = list(good)
+        a[i] = None
+        assert fn(*a, rows, dim, st) == 9003, i
+    for i in (0, 1, 2, 4, 5):                         # 2 bytes off a 16-byte boundary
+        a = list(good)
+        a[i] = x.data_ptr() + 2
+        assert fn(*a, rows, dim, st) == 9003, i
+    a = list(good)
+    a[6] = dw.data_ptr() + 2
+    assert fn(*a, rows, dim, st) == 9003
+    assert b"aligned" in err(9003)
+    torch.cuda.synchronize()
+    assert torch.all(dw == 7.0)                        # nothing ran
+    assert fn(None, None, None, None, None, None, dw.data_ptr(), 0, dim, st) == 0
+    torch.cuda.synchronize()
+    assert torch.all(dw == 0.0)
+    assert fn(*good, rows, dim, st) == 0               # and the entry point still works afterwards
+    torch.cuda.synchronize()
+    assert torch.isfinite(dx.float()).all() and torch.isfinite(dw).all()
