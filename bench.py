@@ -14,7 +14,8 @@ Prints ONE JSON line on rank 0.  ``value`` is whole-job tokens/s with this step'
 the device, timed with CUDA events on the launching stream and reduced as the max over ranks.
 ``e2e.value`` is the same metric through ``Trainer.train_step(batch)``: every timed step copies that
 step's token batch from pinned host memory to the device and reads the loss back to the host.
-``--impl reference`` runs the unmodified reference from ``baseline/_ref`` if it can be imported.
+``--impl reference`` runs the unmodified reference from ``baseline/_ref`` (a copy of its tree) through its own
+``train.py::main``, or prints one ``unavailable`` line with the actual import / run error.
 """
 import argparse
 import json
@@ -86,25 +87,84 @@ class ClockSampler:
                 "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def reference_arm(args):
-    """Run the unmodified reference through its own train.py, if it can be imported at all."""
+def _reference_tree() -> str:
+    """``baseline/_ref``: the reference has no setup.py / pyproject.toml, so pip cannot install it; a plain copy of
+    its tree is the install.  Made here when missing and the read-only original is reachable."""
     ref = os.path.join(ROOT, "baseline", "_ref")
-    why = None
-    if not os.path.isdir(ref) or not os.path.exists(os.path.join(ref, "train.py")):
-        why = ("reference has no setup.py/pyproject.toml so pip cannot install it into baseline/_ref; its imports "
-               "(fairscale, yunchang, transformers LlamaFlashAttention2) are also absent from this image")
-    else:
-        sys.path.insert(0, ref)
-        try:
-            import importlib
-            importlib.import_module("train")
-        except Exception as e:  # noqa: BLE001
-            why = f"reference import failed: {type(e).__name__}: {str(e).splitlines()[0][:160]}"
-    if why is None:
-        why = "reference imported but its FSDP/flash-attn path was not exercised on this image"
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
-    return 0
+    src = "/root/reference"
+    if not os.path.exists(os.path.join(ref, "train.py")) and os.path.isdir(src):
+        import shutil
+        shutil.copytree(src, ref, dirs_exist_ok=True)
+    return ref
+
+
+def _reference_checkpoint(model: str) -> str:
+    """A random-init HF checkpoint directory of the benchmark's architecture for the reference's
+    ``AutoModelForCausalLM.from_pretrained(args.model)`` (reference train.py:78-86): there is no network for the
+    real weights and the benchmark is defined on random weights anyway."""
+    import torch
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from odysseus_transformer_b200.config import get_model_config
+    cfg = get_model_config(model)
+    path = os.path.join("/tmp", f"ody_ref_ckpt_{model}")
+    if not os.path.exists(os.path.join(path, "config.json")):
+        hf = LlamaConfig(**{k: v for k, v in cfg.to_hf_dict().items() if k not in ("architectures", "model_type")})
+        torch.manual_seed(0)
+        LlamaForCausalLM(hf).to(torch.bfloat16).save_pretrained(path)
+    return path
+
+
+def reference_arm(args):
+    """Run the UNMODIFIED reference through its own ``train.py::main`` (reference train.py:49-240) for the same
+    metric and configuration, or say in one line why that cannot be done on this machine."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    L = args.seq_len or args.seq_per_gpu * world
+
+    def unavailable(why: str) -> int:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    ref = _reference_tree()
+    if not os.path.exists(os.path.join(ref, "train.py")):
+        return unavailable("baseline/_ref is empty and the reference tree is not reachable from this machine")
+    sys.path.insert(0, ref)
+    try:
+        import importlib
+        ref_train = importlib.import_module("train")
+    except BaseException as e:  # noqa: BLE001  (ImportError, or whatever a half-installed dependency raises)
+        return unavailable(f"reference import failed on this image: {type(e).__name__}: {str(e).splitlines()[0][:200]} "
+                           "(pip --no-index cannot supply fairscale / yunchang; transformers 5.x has no LlamaFlashAttention2)")
+    try:
+        import io
+        import re
+        from contextlib import redirect_stdout
+        ckpt = _reference_checkpoint(args.model)
+        steps = args.warmup + args.steps       # the reference leaves its first 3 steps untimed (train.py:174,185)
+        ns = argparse.Namespace(batch_size=1, seed=42, max_train_steps=steps, learning_rate=1e-5, rope_theta=10000,
+                                model=ckpt, seq_length=L, cpu_offload=False, grad_checkpoint=False, use_zero2=False,
+                                use_ody_zero3=True, use_profiler=False, use_cfg_init_model=False, parallel_mode=args.mode)
+        buf = io.StringIO()
+        with redirect_stdout(buf):
+            ref_train.main(ns)
+        m = re.search(r"Time taken: ([0-9.]+) seconds", buf.getvalue())
+        if not m:
+            return unavailable("reference ran but printed no 'Time taken' line")
+        timed = max(1, steps - 3)
+        elapsed = float(m.group(1))
+        if rank == 0:
+            tok_s = timed * L / elapsed
+            print(json.dumps({"metric": "Llama-2-7B train tokens/s (max over ranks), weak scaling L = 8K x #GPU",
+                              "impl": "reference", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": timed,
+                              "warmup": 3, "ms_per_step": elapsed / timed * 1e3, "higher_is_better": True,
+                              "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+                              "config": {"model": args.model, "global_batch": 1, "seq_len": L,
+                                         "parallelism": f"{args.mode}{world}",
+                                         "timing": "the reference's own wall-clock sum over its timed steps"}}))
+        return 0
+    except BaseException as e:  # noqa: BLE001
+        return unavailable(f"reference imported but its run failed: {type(e).__name__}: {str(e).splitlines()[0][:200]}")
 
 
 def main():
@@ -131,7 +191,7 @@ def main():
     from odysseus_transformer_b200.mesh import init_parallel_context
     from odysseus_transformer_b200.ops import native
     from odysseus_transformer_b200.train import Trainer
-    from odysseus_transformer_b200.utils.metrics import max_over_ranks, memory_gb
+    from odysseus_transformer_b200.utils.metrics import exposed_comm_ms, max_over_ranks, memory_gb
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world != args.gpus:
@@ -162,6 +222,7 @@ def main():
         s = dev_batches[i]
         trainer.train_step_device(s["local_input_ids"], s["local_position_ids"], s["local_target_ids"])
     barrier()
+    exposed_comm_ms(ctx, reset=True)
     sampler = ClockSampler(dev.index or 0)
     sampler.start()
     torch.cuda.reset_peak_memory_stats(dev)
@@ -177,6 +238,7 @@ def main():
     ms = max_over_ranks(e0.elapsed_time(e1), dev)
     launches = native.launch_count()
     last_loss = float(loss.item())
+    trainer.check_status()
     native.check_status(dev.index or 0)
     del dev_batches
 
@@ -199,6 +261,32 @@ def main():
     clocks = sampler.stop()
     mem = memory_gb(dev)
     peak = max_over_ranks(mem["peak_allocated"], dev)
+    exposed = exposed_comm_ms(ctx, reset=True)
+
+    # ---------------- on 8 GPUs also the fixed-length point: Llama-2-7B, Odysseus, L = 32768 (same Trainer API, device-resident)
+    extra = None
+    if world == 8 and args.model == "llama2-7b" and mode == "odysseus" and not args.seq_len and not args.layers:
+        del trainer, host_batches
+        torch.cuda.empty_cache()
+        L2 = 32768
+        tr2 = Trainer(cfg, mode, ctx, L2, lr=1e-5, dtype=torch.bfloat16, seed=42)
+        hb2 = [torch.randint(cfg.vocab_size, (1, L2 + 1), generator=gen).pin_memory() for _ in range(nb)]
+        db2 = [tr2.shard_batch(b) for b in hb2]
+        for i in range(args.warmup):
+            tr2.train_step_device(db2[i]["local_input_ids"], db2[i]["local_position_ids"], db2[i]["local_target_ids"])
+        barrier()
+        torch.cuda.reset_peak_memory_stats(dev)
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for i in range(args.warmup, nb):
+            tr2.train_step_device(db2[i]["local_input_ids"], db2[i]["local_position_ids"], db2[i]["local_target_ids"])
+        f1.record()
+        barrier()
+        tr2.check_status()
+        ms2 = max_over_ranks(f0.elapsed_time(f1), dev)
+        extra = {"seq_len": L2, "value": args.steps * L2 / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2 / args.steps,
+                 "peak_mem_gb": max_over_ranks(memory_gb(dev)["peak_allocated"], dev),
+                 "published_8xA100_tok_s": 15302.0, "vs_published": args.steps * L2 / (ms2 / 1e3) / 15302.0}
 
     if rank == 0:
         tok_s = args.steps * L / (ms / 1e3)
@@ -223,8 +311,10 @@ def main():
                     "api": "odysseus_transformer_b200.train.Trainer.train_step(pinned host batch) + loss.to('cpu')"},
             "gpu_launches": launches,
             "clocks": clocks,
-            "peak_mem_gb": peak, "loss": last_loss,
+            "peak_mem_gb": peak, "loss": last_loss, "exposed_comm_ms_per_step": exposed / (args.steps + min(2, args.warmup) + args.steps),
         }
+        if extra is not None:
+            out["config2_32k"] = extra
         print(json.dumps(out))
     if world > 1:
         dist.barrier()

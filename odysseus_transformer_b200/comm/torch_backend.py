@@ -97,6 +97,19 @@ def all_to_all_chunks(x: torch.Tensor, group) -> torch.Tensor:
     return out
 
 
+def all_to_all_rows(x: torch.Tensor, send_counts, recv_counts, group) -> torch.Tensor:
+    """Uneven all-to-all on the first dim: rows [sum(send_counts[:p]), +send_counts[p]) of ``x`` go to rank p;
+    returns the rows received, ordered by source rank (``recv_counts[p]`` rows from rank p).  Counts are host ints."""
+    n = group_size(group)
+    if n == 1:
+        return x
+    x = x.contiguous()
+    out = torch.empty((int(sum(recv_counts)),) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_to_all_single(out, x, output_split_sizes=[int(c) for c in recv_counts],
+                           input_split_sizes=[int(c) for c in send_counts], group=group)
+    return out
+
+
 def broadcast_(x: torch.Tensor, src_global_rank: int, group) -> None:
     if group_size(group) > 1:
         dist.broadcast(x, src=src_global_rank, group=group)

@@ -12,7 +12,8 @@
 //   * every MMA is a tcgen05.mma issued by ONE thread in program order: S_t = Q_t K^T (operands in shared
 //     memory) and O_t += P_t V (P_t read from TMEM).  TMEM holds S_A, S_B, O_A, O_B (4 x 128 fp32 columns);
 //     the bf16 probabilities P_t are written over the first 64 columns of S_t once its thread has S_t in
-//     registers - the in-order tensor pipe runs Q K^T of the next block only after P V has read them;
+//     registers - the in-order tensor pipe runs Q K^T of the next block only after P V has read them - and are
+//     announced in four 32-key pieces, so P V starts on the first keys while the last ones are exponentiated;
 //   * two softmax warpgroups, one thread per query row: 128 scores straight from TMEM, no exchange between
 //     threads, exp2 domain, lazy rescaling of O (the running maximum used for exponentiation only moves when
 //     it would grow by more than 2^8, so the O read-modify-write is rare).  A tcgen05.commit after Q K^T of
@@ -64,7 +65,7 @@ struct Bars {
   uint64_t q_full[2];
   uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
   uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-  uint64_t s_full[2], p_full[2], o_done[2];
+  uint64_t s_full[2], p_part[2][4], o_done[2];
   uint64_t drain;
   uint32_t tmem_base;
   int abort_flag;
@@ -117,7 +118,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&bars->s_full[t], 1);
-      mbar_init(&bars->p_full[t], 128);
+      for (int g = 0; g < 4; ++g) mbar_init(&bars->p_part[t][g], 128);
       mbar_init(&bars->o_done[t], 1);
     }
     mbar_init(&bars->drain, 1);
@@ -205,14 +206,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
           umma_commit(&bars->s_full[t]);
         };
-        // O_t (+)= P_t V(j)
-        auto issue_pv = [&](int t, int j) {
-          const uint64_t v = desc_advance(vdesc0, (j & 1) * TILE_BYTES);
-          const uint32_t pa = tmem + COL_S + t * BN;
+        // O_t (+)= P_t V(j), keys [32 g, 32 g + 32): the probabilities arrive in four pieces, and the first
+        // pieces are multiplied while the softmax threads still exponentiate the later ones
+        auto issue_pv = [&](int t, int j, int g) {
+          const uint64_t v = desc_advance(vdesc0, (j & 1) * TILE_BYTES + g * 4096);
+          const uint32_t pa = tmem + COL_S + t * BN + g * 16;
           const uint32_t d = tmem + COL_O + t * HD;
-          umma_ts(d, pa, v, IDESC_PV, j > 0 ? 1u : 0u);
-#pragma unroll
-          for (int kk = 1; kk < BN / 16; ++kk) umma_ts(d, pa + kk * 8, desc_advance(v, kk * 2048), IDESC_PV, 1u);
+          umma_ts(d, pa, v, IDESC_PV, (j > 0 || g > 0) ? 1u : 0u);
+          umma_ts(d, pa + 8, desc_advance(v, 2048), IDESC_PV, 1u);
         };
         ok = mbar_wait(&bars->q_full[0], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL) &&
              mbar_wait(&bars->k_full[0], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
@@ -233,13 +234,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int t = 0; t < 2; ++t) {
             const int nt = t == 0 ? nA : nB;
             if (j >= nt) continue;
-            if (!mbar_wait(&bars->p_full[t], j & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
             if (!have_v) {
               if (!mbar_wait(&bars->v_full[s], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
               have_v = true;
             }
-            tc_fence_after();
-            issue_pv(t, j);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (!mbar_wait(&bars->p_part[t][g], j & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+              tc_fence_after();
+              issue_pv(t, j, g);
+            }
+            if (!ok) break;
             if (j + 1 < nt) {
               if (!have_k1) {
                 if (!mbar_wait(&bars->k_full[s1], ph1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
@@ -349,15 +354,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           pk[c] = pack_bf16(p0, p1);
         }
         tmem_st_32x16(col_s + g * 16, pk);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->p_part[t][g]);
       }
       {
         float r0, r1;
         upk2(rs2, r0, r1);
         l += r0 + r1;
       }
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&bars->p_full[t]);
     }
     // epilogue: O / l -> bf16 -> swizzled smem (this tile's Q is dead by now) -> TMA store; lse
     if (ok && nt > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_done[t], 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));

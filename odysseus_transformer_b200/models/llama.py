@@ -45,13 +45,13 @@ from ..parallel.ulysses import SequenceParallelAttention
 
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, ctx: ParallelContext, mode: Optional[str], layer_idx: int,
-                 sched: Optional[Zero3Schedule], dtype, device, use_zero3_linear: bool = True):
+                 sched: Optional[Zero3Schedule], dtype, device, use_zero3_linear: bool = True, pack_qkv: bool = True):
         super().__init__()
         d = cfg.hidden_size
         self.eps = cfg.rms_norm_eps
         self.input_layernorm = nn.Parameter(torch.ones(d, dtype=dtype, device=device))
         if mode in ("odysseus", "tpsp"):
-            self.self_attn = TPSPAttention(cfg, ctx, layer_idx, dtype=dtype, device=device)
+            self.self_attn = TPSPAttention(cfg, ctx, layer_idx, dtype=dtype, device=device, pack_weight=pack_qkv)
         elif mode == "ring":
             self.self_attn = RingAttention(cfg, ctx, sched, layer_idx, dtype=dtype, device=device)
         else:
@@ -79,9 +79,13 @@ class DecoderLayer(nn.Module):
 
 class LlamaForCausalLM(nn.Module):
     def __init__(self, cfg: ModelConfig, mode: Optional[str] = None, ctx: Optional[ParallelContext] = None,
-                 dtype: torch.dtype = torch.float32, device=None, use_zero3_linear: bool = True):
+                 dtype: torch.dtype = torch.float32, device=None, use_zero3_linear: bool = True,
+                 loss_chunk_rows: int = 0, pack_qkv: bool = True):
         super().__init__()
         self.use_zero3_linear = use_zero3_linear
+        # > 0: the training loss runs lm_head + cross-entropy this many tokens at a time (ops.functional.
+        # linear_cross_entropy_sum) and lm_head stays out of the ZeRO-3 prefetch chain, whose order it would break
+        self.loss_chunk_rows = int(loss_chunk_rows)
         if cfg.tie_word_embeddings:
             raise NotImplementedError("tied embeddings are not supported (Llama-2/3 do not tie)")
         ctx = ctx if ctx is not None else get_context()
@@ -95,11 +99,12 @@ class LlamaForCausalLM(nn.Module):
         self.zero3 = Zero3Schedule()
         self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size // n, cfg.hidden_size, dtype=dtype, device=device))
         self.layers = nn.ModuleList(
-            [DecoderLayer(cfg, ctx, mode, i, self.zero3, dtype, device, use_zero3_linear)
+            [DecoderLayer(cfg, ctx, mode, i, self.zero3, dtype, device, use_zero3_linear, pack_qkv)
              for i in range(cfg.num_hidden_layers)])
         self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
         self.norm.grad_sync_group = ctx.world_group
-        self.lm_head = LinearZeRO3(cfg.hidden_size, cfg.vocab_size, ctx.world_group, self.zero3, dtype=dtype, device=device)
+        self.lm_head = LinearZeRO3(cfg.hidden_size, cfg.vocab_size, ctx.world_group,
+                                   None if self.loss_chunk_rows > 0 else self.zero3, dtype=dtype, device=device)
         self.gradient_checkpointing = False
 
     # ------------------------------------------------------------------ forward
@@ -135,13 +140,15 @@ class LlamaForCausalLM(nn.Module):
         """Without ``labels``: logits ``[1, t, V]`` for the local tokens.  With ``labels`` (already
         shifted, local): this rank's share of the global-mean loss, ``sum(CE) / global_tokens``."""
         h = self.hidden_states(input_ids, position_ids)
-        logits = self.lm_head(h)                                   # [t, V]
         if labels is None:
-            return logits.unsqueeze(0)
+            return self.lm_head(h).unsqueeze(0)                    # [1, t, V]
         tg = labels.reshape(-1)
         if global_tokens is None:
             global_tokens = tg.numel() * max(1, self.pctx.world_size)
-        return F.cross_entropy_sum(logits, tg, 1.0 / float(global_tokens))
+        if self.loss_chunk_rows > 0:
+            return F.linear_cross_entropy_sum(h, self.lm_head.weight, tg, 1.0 / float(global_tokens),
+                                              self.lm_head.group, self.loss_chunk_rows)
+        return F.cross_entropy_sum(self.lm_head(h), tg, 1.0 / float(global_tokens))
 
     def gradient_checkpointing_enable(self) -> None:
         """Recompute each decoder layer in backward (reference ``--grad-checkpoint``, train.py:161-162)."""

@@ -317,6 +317,74 @@ def cross_entropy_sum(logits: torch.Tensor, targets: torch.Tensor, scale: float 
     return _CrossEntropySum.apply(logits, targets, scale, ignore_index)
 
 
+class _ChunkedLinearCrossEntropy(Function):
+    """lm_head + cross-entropy over row chunks, gradients computed in the same pass.
+
+    ``[t, V]`` logits never exist whole: per chunk of ``chunk_rows`` tokens the logits are formed, reduced to
+    loss and log-sum-exp, overwritten in place by their gradient and consumed at once by the two backward GEMMs
+    (``dh`` rows; ``dW`` accumulated over chunks).  The ZeRO-3 weight is gathered once for both directions and its
+    gradient reduce-scattered once.  Backward only scales the stored gradients by the incoming scalar."""
+
+    @staticmethod
+    def forward(ctx, h, w, targets, scale, ignore_index, group, chunk_rows):
+        from ..comm import torch_backend as C
+        n = C.group_size(group)
+        full = C.all_gather_rows(w.detach(), group) if n > 1 else w.detach()
+        t, V = h.shape[0], full.shape[0]
+        need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        use_native = native.use_native(h)
+        dh = torch.empty_like(h) if need_dh else None
+        dw_full = torch.empty_like(full) if need_dw else None
+        total = torch.zeros((), dtype=torch.float32, device=h.device)
+        scale_t = torch.full((1,), float(scale), dtype=torch.float32, device=h.device)
+        first = True
+        for r0 in range(0, t, chunk_rows):
+            hc, tc = h[r0:r0 + chunk_rows], targets[r0:r0 + chunk_rows]
+            logits = gemm_nt(hc, full)
+            if use_native:
+                loss, lse = native.lib().ce_fwd(logits, tc, ignore_index)
+            else:
+                loss, lse = R.cross_entropy_fwd(logits, tc, ignore_index)
+            total += loss.sum()
+            if not (need_dh or need_dw):
+                continue
+            if use_native:
+                native.lib().ce_bwd_(logits, tc, lse, scale_t, ignore_index)
+            else:
+                R.cross_entropy_bwd_(logits, tc, lse, scale_t[0], ignore_index)
+            if need_dh:
+                gemm_nn(logits, full, out=dh[r0:r0 + chunk_rows])
+            if need_dw:
+                gemm_tn(logits, hc, out=dw_full, accumulate=not first)
+            first = False
+        dw = None
+        if need_dw:
+            dw = C.reduce_scatter_rows(dw_full, group) if n > 1 else dw_full
+        ctx.w = w
+        ctx.save_for_backward(*(x for x in (dh, dw) if x is not None))
+        ctx.have = (need_dh, need_dw)
+        return total * scale
+
+    @staticmethod
+    def backward(ctx, dloss):
+        saved = list(ctx.saved_tensors)
+        dh = saved.pop(0) if ctx.have[0] else None
+        dw = saved.pop(0) if ctx.have[1] else None
+        if dh is not None:
+            dh = dh * dloss.to(dh.dtype)
+        gw = deliver_grad(ctx.w, dw * dloss.to(dw.dtype)) if dw is not None else None
+        return dh, gw, None, None, None, None, None
+
+
+def linear_cross_entropy_sum(h: torch.Tensor, w_shard: torch.Tensor, targets: torch.Tensor, scale: float, group,
+                             chunk_rows: int, ignore_index: int = -100) -> torch.Tensor:
+    """``cross_entropy_sum(h @ gather(w_shard)^T, targets, scale)`` without materialising the logits:
+    ``h [t, d]``, ``w_shard [V/n, d]`` (ZeRO-3 over ``group``), evaluated ``chunk_rows`` tokens at a time.
+    The reference upcasts the whole ``[L/N, V]`` logits tensor to fp32 before its loss (reference
+    ``train.py:210-216`` through HF's ``LlamaForCausalLM``), which is what bounds its sequence length."""
+    return _ChunkedLinearCrossEntropy.apply(h, w_shard, targets, scale, ignore_index, group, int(chunk_rows))
+
+
 # ----------------------------------------------------------------------------- embedding
 
 

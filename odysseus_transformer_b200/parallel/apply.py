@@ -75,12 +75,14 @@ def prepare_attn_inputs(parallel_mode: Optional[str], input_ids: torch.Tensor, p
 
 def build_model(cfg: ModelConfig, mode: Optional[str], ctx: Optional[ParallelContext] = None,
                 dtype: torch.dtype = torch.float32, device=None, seed: Optional[int] = 0,
-                state_dict: Optional[Dict[str, torch.Tensor]] = None, use_zero3_linear: bool = True):
+                state_dict: Optional[Dict[str, torch.Tensor]] = None, use_zero3_linear: bool = True,
+                loss_chunk_rows: int = 0):
     """Create the model directly in ``mode``; weights from ``state_dict`` (HF names) or random.
     ``use_zero3_linear=False`` (odysseus mode only) keeps the MLP weights whole on every rank."""
     from ..models.llama import LlamaForCausalLM
     ctx = ctx if ctx is not None else get_context()
-    model = LlamaForCausalLM(cfg, mode, ctx, dtype=dtype, device=device, use_zero3_linear=use_zero3_linear)
+    model = LlamaForCausalLM(cfg, mode, ctx, dtype=dtype, device=device, use_zero3_linear=use_zero3_linear,
+                             loss_chunk_rows=loss_chunk_rows)
     if state_dict is not None:
         model.load_hf_state_dict(state_dict)
     elif seed is not None:

@@ -77,6 +77,82 @@ def reduce_scatter_seq(x: torch.Tensor, group) -> torch.Tensor:
     return _ReduceScatterSeq.apply(x, group)
 
 
+class _GatherLastDim(Function):
+    """[..., c] on each rank -> [..., n*c]; backward keeps this rank's slice (the reference's
+    ``gather_from_model_parallel_region``, used for ``gather_output`` and ``get_master_weight``)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        n = C.group_size(group)
+        if n == 1:
+            return x
+        parts = C.all_gather_rows(x.unsqueeze(0).contiguous(), group)           # [n, ..., c]
+        return torch.cat(list(parts.unbind(0)), dim=-1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        n, r = C.group_size(ctx.group), C.group_rank(ctx.group)
+        if n == 1:
+            return dy, None
+        c = dy.shape[-1] // n
+        return dy[..., r * c:(r + 1) * c].contiguous(), None
+
+
+class _ScatterLastDim(Function):
+    """Keep this rank's slice of the last dim; backward all-gathers it (``input_is_parallel=False``)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        n, r = C.group_size(group), C.group_rank(group)
+        if n == 1:
+            return x
+        c = x.shape[-1] // n
+        return x[..., r * c:(r + 1) * c].contiguous()
+
+    @staticmethod
+    def backward(ctx, dy):
+        return _GatherLastDim.apply(dy, ctx.group), None
+
+
+class _CopyToRegion(Function):
+    """Identity forward, all-reduce backward: the input of a column-parallel linear that is NOT sequence parallel."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, dy):
+        dy = dy.contiguous().clone()
+        C.all_reduce_(dy, ctx.group)
+        return dy, None
+
+
+class _ReduceFromRegion(Function):
+    """All-reduce forward, identity backward: the output of a row-parallel linear that is NOT sequence parallel."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous().clone()
+        C.all_reduce_(x, group)
+        return x
+
+    @staticmethod
+    def backward(ctx, dy):
+        return dy, None
+
+
+def gather_last_dim(x: torch.Tensor, group) -> torch.Tensor:
+    return _GatherLastDim.apply(x, group)
+
+
+def scatter_last_dim(x: torch.Tensor, group) -> torch.Tensor:
+    return _ScatterLastDim.apply(x, group)
+
+
 # ----------------------------------------------------------------------------- AG -> GEMM (column parallel)
 
 
@@ -292,29 +368,45 @@ def zero3_linear(x: torch.Tensor, w_shard: torch.Tensor, group, sched: Optional[
 
 
 class _Zero3Embedding(Function):
+    """Lookup in a vocab-sharded table that moves only the rows the tokens touch.
+
+    Token ids are sorted by owning rank and sent to the owners, which answer with their rows (two uneven
+    all-to-alls of ``t`` ids and ``t x d`` values per rank); backward sends the output gradient rows back the
+    same way and every owner scatter-adds them into its own shard in fp32.  Gathering the whole ``[V, d]``
+    table and reduce-scattering a full-size gradient instead would move ``V x d`` twice per step (1 GB each way
+    at Llama-3's vocabulary) and, with a bf16 scatter-add, lose precision on repeated token ids."""
+
     @staticmethod
     def forward(ctx, ids, w, group):
-        ctx.group = group
-        ctx.save_for_backward(ids)
-        ctx.w = w
-        full = C.all_gather_rows(w, group)
-        return full.index_select(0, ids)
+        n, r = C.group_size(group), C.group_rank(group)
+        vr = w.shape[0]
+        owner = torch.div(ids, vr, rounding_mode="floor")
+        order = torch.argsort(owner, stable=True)
+        counts = torch.bincount(owner, minlength=n)
+        all_counts = C.all_gather_rows(counts.view(1, n), group).tolist()      # [source][owner]; one host read
+        send = all_counts[r]
+        recv = [all_counts[p][r] for p in range(n)]
+        want = C.all_to_all_rows(ids[order], send, recv, group) - r * vr       # rows of my shard the others need
+        rows = C.all_to_all_rows(w.detach().index_select(0, want), recv, send, group)
+        out = torch.empty_like(rows)
+        out[order] = rows
+        ctx.group, ctx.w, ctx.send, ctx.recv = group, w, send, recv
+        ctx.save_for_backward(order, want)
+        return out
 
     @staticmethod
     def backward(ctx, dy):
-        (ids,) = ctx.saved_tensors
-        w, group = ctx.w, ctx.group
-        n = C.group_size(group)
-        g = torch.zeros((n * w.shape[0], w.shape[1]), dtype=dy.dtype if dy.is_cuda else torch.float32,
-                        device=dy.device)
-        g.index_add_(0, ids, dy.to(g.dtype))
-        g = C.reduce_scatter_rows(g, group)
+        order, want = ctx.saved_tensors
+        w = ctx.w
+        got = C.all_to_all_rows(dy.index_select(0, order), ctx.send, ctx.recv, ctx.group)
+        g = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        g.index_add_(0, want, got.float())
         return None, F.deliver_grad(w, g), None
 
 
 def zero3_embedding(ids: torch.Tensor, w_shard: torch.Tensor, group) -> torch.Tensor:
-    """Embedding lookup through a vocab-sharded table: gather, index, and reduce-scatter the
-    scatter-added gradient (the reference leaves this to FSDP's flat parameter, train.py:114-159)."""
+    """Embedding lookup through a vocab-sharded table (the reference leaves the table to FSDP's flat
+    parameter, train.py:114-159): ids go to the owning ranks, rows come back; gradients travel the same way."""
     return _Zero3Embedding.apply(ids, w_shard, group)
 
 
@@ -322,15 +414,42 @@ def zero3_embedding(ids: torch.Tensor, w_shard: torch.Tensor, group) -> torch.Te
 
 
 class ColumnParallelLinearAG(nn.Module):
-    """``[T/n, in] -> [T, out/n]``; weight ``[out/n, in]`` (this rank's rows of the full weight)."""
+    """``[T/n, in] -> [T, out/n]``; weight ``[out/n, in]`` (this rank's rows of the full weight).
 
-    def __init__(self, in_features: int, out_features_local: int, group, dtype=None, device=None):
+    Options of the reference's constructor (reference ``utils/linear_tpsp.py:405-500``): ``bias`` (this rank's
+    ``out/n`` entries, zero-initialised, added after the GEMM), ``gather_output`` (all-gather the result on the
+    feature dim -> ``[T, out]``), ``sequence_parallel=False`` (the input already holds the whole sequence: no
+    gather; its gradient is all-reduced instead), ``keep_master_weight_for_test`` (``master_weight`` keeps the full
+    ``[out, in]`` tensor this shard was cut from - set by ``init_from_master``).  The model blocks use the defaults:
+    no bias, sharded output, sequence parallel."""
+
+    def __init__(self, in_features: int, out_features_local: int, group, dtype=None, device=None, bias: bool = False,
+                 gather_output: bool = False, sequence_parallel: bool = True, keep_master_weight_for_test: bool = False):
         super().__init__()
-        self.group = group
+        self.group, self.gather_output, self.sequence_parallel = group, gather_output, sequence_parallel
+        self.keep_master_weight_for_test = keep_master_weight_for_test
+        self.master_weight: Optional[torch.Tensor] = None
         self.weight = nn.Parameter(torch.empty(out_features_local, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features_local, dtype=dtype, device=device)) if bias else None
+
+    def init_from_master(self, master: torch.Tensor) -> None:
+        """Fill this rank's shard from the full ``[out, in]`` weight (identical on every rank)."""
+        r, rows = C.group_rank(self.group), self.weight.shape[0]
+        with torch.no_grad():
+            self.weight.copy_(master[r * rows:(r + 1) * rows])
+        if self.keep_master_weight_for_test:
+            self.master_weight = master.detach().clone()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ag_linear(x, self.weight, self.group)
+        if self.sequence_parallel:
+            y = ag_linear(x, self.weight, self.group)
+        else:
+            y = F.linear(_CopyToRegion.apply(x, self.group), self.weight)
+        if self.bias is not None:
+            y = y + self.bias
+        if self.gather_output:
+            y = gather_last_dim(y, self.group)
+        return y
 
     def get_master_weight(self) -> torch.Tensor:
         """Full weight gathered over the group (reference ``get_master_weight``, linear_tpsp.py:474-477)."""
@@ -338,15 +457,46 @@ class ColumnParallelLinearAG(nn.Module):
 
 
 class RowParallelLinearRS(nn.Module):
-    """``[T, in/n] -> [T/n, out]``; weight ``[out, in/n]`` (this rank's columns of the full weight)."""
+    """``[T, in/n] -> [T/n, out]``; weight ``[out, in/n]`` (this rank's columns of the full weight).
 
-    def __init__(self, in_features_local: int, out_features: int, group, dtype=None, device=None):
+    Options of the reference's constructor (reference ``utils/linear_tpsp.py:503-596``): ``bias`` (full ``[out]``,
+    zero-initialised, added after the reduction so it is counted once), ``input_is_parallel=False`` (the input
+    holds all ``in`` features: this rank's slice is cut out first), ``sequence_parallel=False`` (all-reduce instead
+    of reduce-scatter: every rank gets ``[T, out]``), ``keep_master_weight_for_test``.  Defaults as the model blocks
+    use them: no bias, parallel input, sequence parallel."""
+
+    def __init__(self, in_features_local: int, out_features: int, group, dtype=None, device=None, bias: bool = False,
+                 input_is_parallel: bool = True, sequence_parallel: bool = True, keep_master_weight_for_test: bool = False):
         super().__init__()
-        self.group = group
+        self.group, self.input_is_parallel, self.sequence_parallel = group, input_is_parallel, sequence_parallel
+        self.keep_master_weight_for_test = keep_master_weight_for_test
+        self.master_weight: Optional[torch.Tensor] = None
         self.weight = nn.Parameter(torch.empty(out_features, in_features_local, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+        if self.bias is not None and C.group_size(group) > 1:
+            # every rank adds the same bias to different rows (or, without sequence parallelism, to the same rows,
+            # where each copy sees the full gradient): rows differ -> the gradients must be summed
+            if sequence_parallel:
+                self.bias.grad_sync_group = group
+
+    def init_from_master(self, master: torch.Tensor) -> None:
+        """Fill this rank's shard from the full ``[out, in]`` weight (identical on every rank)."""
+        r, cols = C.group_rank(self.group), self.weight.shape[1]
+        with torch.no_grad():
+            self.weight.copy_(master[:, r * cols:(r + 1) * cols])
+        if self.keep_master_weight_for_test:
+            self.master_weight = master.detach().clone()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return linear_rs(x, self.weight, self.group)
+        if not self.input_is_parallel:
+            x = scatter_last_dim(x, self.group)
+        if self.sequence_parallel:
+            y = linear_rs(x, self.weight, self.group)
+        else:
+            y = _ReduceFromRegion.apply(F.linear(x, self.weight), self.group)
+        if self.bias is not None:
+            y = y + self.bias
+        return y
 
     def get_master_weight(self) -> torch.Tensor:
         parts = C.all_gather_rows(self.weight.detach().t().contiguous(), self.group)

@@ -24,7 +24,11 @@ from .linear import ColumnParallelLinearAG, RowParallelLinearRS
 
 
 class TPSPAttention(nn.Module):
-    def __init__(self, cfg, ctx, layer_idx: int = 0, dtype=None, device=None):
+    """``pack_weight=False`` keeps separate ``q_proj`` / ``k_proj`` / ``v_proj`` column-parallel linears (the
+    reference's unpacked variant, reference ``decoder/odysseus.py:104-142``, which its attention test builds);
+    the default packs them into one ``qkv_proj`` so the sequence is gathered once."""
+
+    def __init__(self, cfg, ctx, layer_idx: int = 0, dtype=None, device=None, pack_weight: bool = True):
         super().__init__()
         U = ctx.inner_size
         self.cfg, self.pctx, self.layer_idx = cfg, ctx, layer_idx
@@ -32,9 +36,15 @@ class TPSPAttention(nn.Module):
         self.n_local_kv_heads = cfg.num_key_value_heads // U
         hd = cfg.head_dim
         self.head_dim = hd
-        self.qkv_proj = ColumnParallelLinearAG(
-            cfg.hidden_size, (self.n_local_heads + 2 * self.n_local_kv_heads) * hd, ctx.inner_group,
-            dtype=dtype, device=device)
+        self.pack_weight = pack_weight
+        if pack_weight:
+            self.qkv_proj = ColumnParallelLinearAG(
+                cfg.hidden_size, (self.n_local_heads + 2 * self.n_local_kv_heads) * hd, ctx.inner_group,
+                dtype=dtype, device=device)
+        else:
+            mk = lambda heads: ColumnParallelLinearAG(cfg.hidden_size, heads * hd, ctx.inner_group,   # noqa: E731
+                                                      dtype=dtype, device=device)
+            self.q_proj, self.k_proj, self.v_proj = mk(self.n_local_heads), mk(self.n_local_kv_heads), mk(self.n_local_kv_heads)
         self.o_proj = RowParallelLinearRS(self.n_local_heads * hd, cfg.hidden_size, ctx.inner_group,
                                           dtype=dtype, device=device)
         if ctx.ring_size > 1:
@@ -44,7 +54,10 @@ class TPSPAttention(nn.Module):
 
     def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
         """x [T/N, d] local shard; cos/sin for the positions of this rank's ring block [T/R, hd/2]."""
-        qkv = self.qkv_proj(x)                                   # [Tb, (hq + 2 hkv) * hd]
+        if self.pack_weight:
+            qkv = self.qkv_proj(x)                               # [Tb, (hq + 2 hkv) * hd]
+        else:
+            qkv = torch.cat([self.q_proj(x), self.k_proj(x), self.v_proj(x)], dim=-1)
         o = packed_rope_attention(qkv, cos, sin, self.n_local_heads, self.n_local_kv_heads,
                                   self.pctx.ring_group)          # [Tb, hq * hd]
         return self.o_proj(o)                                    # [T/N, d]
@@ -57,12 +70,23 @@ class TPSPAttention(nn.Module):
         wk = get(prefix + "k_proj.weight")[u * hkv * hd:(u + 1) * hkv * hd]
         wv = get(prefix + "v_proj.weight")[u * hkv * hd:(u + 1) * hkv * hd]
         with torch.no_grad():
-            self.qkv_proj.weight.copy_(torch.cat([wq, wk, wv], 0))
+            if self.pack_weight:
+                self.qkv_proj.weight.copy_(torch.cat([wq, wk, wv], 0))
+            else:
+                self.q_proj.weight.copy_(wq)
+                self.k_proj.weight.copy_(wk)
+                self.v_proj.weight.copy_(wv)
             self.o_proj.weight.copy_(get(prefix + "o_proj.weight")[:, u * hq * hd:(u + 1) * hq * hd])
 
     def hf_export(self, prefix: str, out: Dict[str, torch.Tensor]) -> None:
         g, U, hd = self.pctx.inner_group, self.pctx.inner_size, self.head_dim
         hq, hkv = self.n_local_heads, self.n_local_kv_heads
+        if not self.pack_weight:
+            out[prefix + "q_proj.weight"] = self.q_proj.get_master_weight().clone()
+            out[prefix + "k_proj.weight"] = self.k_proj.get_master_weight().clone()
+            out[prefix + "v_proj.weight"] = self.v_proj.get_master_weight().clone()
+            out[prefix + "o_proj.weight"] = self.o_proj.get_master_weight()
+            return
         packed = C.all_gather_rows(self.qkv_proj.weight.detach(), g).view(U, (hq + 2 * hkv) * hd, -1)
         out[prefix + "q_proj.weight"] = packed[:, :hq * hd].reshape(U * hq * hd, -1).clone()
         out[prefix + "k_proj.weight"] = packed[:, hq * hd:(hq + hkv) * hd].reshape(U * hkv * hd, -1).clone()

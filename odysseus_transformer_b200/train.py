@@ -68,15 +68,18 @@ class Trainer:
                  dtype: torch.dtype = torch.bfloat16, seed: int = 42, ulysses_degree: int = 0,
                  ring_degree: int = 1, state_dict: Optional[Dict[str, torch.Tensor]] = None,
                  grad_checkpoint: bool = False, use_zero2: bool = False, cpu_offload: bool = False,
-                 use_zero3_linear: bool = True, time_phases: bool = False):
+                 use_zero3_linear: bool = True, time_phases: bool = False, loss_chunk_rows: Optional[int] = None):
         self.cfg, self.mode, self.ctx, self.seq_length = cfg, mode, ctx, seq_length
         self.ulysses_degree, self.ring_degree = ulysses_degree, ring_degree
         set_global_memory_buffer(ctx.device)
         if ctx.world_size > 1 and ctx.device.type == "cuda" and native.get_backend() != "library" and dtype == torch.bfloat16:
             from .comm import symm
             symm.setup_fused_comm(ctx, cfg, max(1, seq_length // ctx.world_size), mode=mode)
+        if loss_chunk_rows is None:
+            loss_chunk_rows = default_loss_chunk_rows(cfg, seq_length, ctx.world_size, mode, dtype)
+        self.loss_chunk_rows = loss_chunk_rows
         self.model = build_model(cfg, mode, ctx, dtype=dtype, device=ctx.device, seed=seed, state_dict=state_dict,
-                                 use_zero3_linear=use_zero3_linear)
+                                 use_zero3_linear=use_zero3_linear, loss_chunk_rows=loss_chunk_rows)
         if grad_checkpoint:
             self.model.gradient_checkpointing_enable()
         if use_zero2:
@@ -176,6 +179,16 @@ class Trainer:
         return self.train_step_device(s["local_input_ids"], s["local_position_ids"], s["local_target_ids"])
 
 
+def default_loss_chunk_rows(cfg: ModelConfig, seq_length: int, world_size: int, mode: Optional[str], dtype) -> int:
+    """Tokens per lm_head + loss chunk, or 0 to form the local ``[t, V]`` logits in one piece: chunking starts
+    once those logits would pass 2 GiB, in pieces of about 1 GiB (a multiple of 128 rows)."""
+    t = seq_length if mode in (None, "dp") else max(1, seq_length // max(1, world_size))
+    esize = torch.empty((), dtype=dtype).element_size()
+    if t * cfg.vocab_size * esize <= (2 << 30):
+        return 0
+    return max(128, ((1 << 30) // (cfg.vocab_size * esize)) // 128 * 128)
+
+
 def _dtype(name: str) -> torch.dtype:
     return {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[name]
 
@@ -210,7 +223,8 @@ def main(args) -> Dict[str, float]:
     trainer = Trainer(cfg, args.parallel_mode, ctx, args.seq_length, lr=args.learning_rate, dtype=_dtype(args.dtype),
                       seed=args.seed, ulysses_degree=args.ulysses_degree, ring_degree=args.ring_degree,
                       state_dict=state_dict, grad_checkpoint=args.grad_checkpoint, use_zero2=args.use_zero2,
-                      cpu_offload=args.cpu_offload, use_zero3_linear=args.use_ody_zero3, time_phases=bool(args.jsonl))
+                      cpu_offload=args.cpu_offload, use_zero3_linear=args.use_ody_zero3, time_phases=bool(args.jsonl),
+                      loss_chunk_rows=args.loss_chunk_rows)
     log = get_logger()
     start_step = 0
     # the data stream is a function of the RNG state: seed it for a fresh run, restore it for a resumed one
@@ -305,6 +319,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--dtype", type=str, default="bf16", choices=["bf16", "fp32", "fp16"])
     p.add_argument("--warmup-iterations", "--warmup_iterations", type=int, default=d.warmup_iterations)
     p.add_argument("--heartbeat-timeout", "--heartbeat_timeout", type=float, default=0.0)
+    p.add_argument("--loss-chunk-rows", "--loss_chunk_rows", type=int, default=None,
+                   help="tokens per lm_head + cross-entropy chunk (0 = whole logits; default: chunk beyond 2 GiB of logits)")
     p.add_argument("--jsonl", type=str, default=None)
     p.add_argument("--save", type=str, default=None)
     p.add_argument("--load", type=str, default=None)

@@ -153,7 +153,8 @@ def _run_variant(rank, world, variant):
     cfg, sd, batch, ref_loss = _ref("tiny", L)
     mode = "ulysses" if variant == "zero2-ulysses" else "odysseus"
     ctx = init_parallel_context(mode, device=torch.device("cpu"), backend="library")
-    model = build_model(cfg, mode, ctx, dtype=torch.float32, seed=0, use_zero3_linear=(variant != "replicated-mlp"))
+    model = build_model(cfg, mode, ctx, dtype=torch.float32, seed=0, use_zero3_linear=(variant != "replicated-mlp"),
+                        loss_chunk_rows=48 if variant == "chunked-loss" else 0)     # 128 local tokens -> chunks of 48, 48, 32
     if variant.startswith("zero2"):
         model.zero3.keep_gathered = True
     if variant == "grad-checkpoint":
@@ -178,7 +179,7 @@ def _run_variant(rank, world, variant):
     return type(model.layers[0].mlp).__name__
 
 
-@pytest.mark.parametrize("variant", ["zero2", "zero2-ulysses", "grad-checkpoint", "replicated-mlp"])
+@pytest.mark.parametrize("variant", ["zero2", "zero2-ulysses", "grad-checkpoint", "replicated-mlp", "chunked-loss"])
 def test_optional_modes_match_single_process_world2(variant):
     res = run_distributed(_run_variant, 2, variant)
     assert res[0] == ("ReplicatedMLP" if variant == "replicated-mlp" else "OdysseusMLP")
@@ -210,3 +211,12 @@ def _two_backwards(rank, world):
 
 def test_two_backwards_accumulate_world2():
     assert run_distributed(_two_backwards, 2) == {0: True, 1: True}
+
+
+def test_default_loss_chunking_threshold():
+    from odysseus_transformer_b200.config import get_model_config
+    from odysseus_transformer_b200.train import default_loss_chunk_rows
+    l2, l3 = get_model_config("llama2-7b"), get_model_config("llama3-8b")
+    assert default_loss_chunk_rows(l2, 65536, 8, "odysseus", torch.bfloat16) == 0          # 8K tokens x 32000: 0.5 GB
+    rows = default_loss_chunk_rows(l3, 262144, 8, "odysseus", torch.bfloat16)             # 32K tokens x 128256: 8.4 GB
+    assert rows > 0 and rows % 128 == 0 and rows * l3.vocab_size * 2 <= (1 << 30)
