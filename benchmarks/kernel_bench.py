@@ -147,10 +147,12 @@ def main():
     ap.add_argument("--full", action="store_true", help="non-causal attention")
     ap.add_argument("--no-lib", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--fwd-poly", type=int, default=0, help="attention forward: exponential pairs per four on the FMA pipe (0..2)")
     a = ap.parse_args()
     from odysseus_transformer_b200.ops import native
     native.set_backend("fused")
     lib = native.lib()
+    lib.attn_fwd_set_poly(a.fwd_poly)
     wl = not a.no_lib
     if a.what == "gemm":
         bench_gemm(lib, a.m, a.n, a.k, a.layout, wl, a.iters)

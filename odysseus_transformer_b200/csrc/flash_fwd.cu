@@ -12,8 +12,8 @@
 //   * every MMA is a tcgen05.mma issued by ONE thread in program order: S_t = Q_t K^T (operands in shared
 //     memory) and O_t += P_t V (P_t read from TMEM).  TMEM holds S_A, S_B, O_A, O_B (4 x 128 fp32 columns);
 //     the bf16 probabilities P_t are written over the first 64 columns of S_t once its thread has S_t in
-//     registers - the in-order tensor pipe runs Q K^T of the next block only after P V has read them - and are
-//     announced in four 32-key pieces, so P V starts on the first keys while the last ones are exponentiated;
+//     registers - the in-order tensor pipe runs Q K^T of the next block only after P V has read them (announcing
+//     P in 32-key pieces so that P V could start early measured slower: four store waits instead of one);
 //   * two softmax warpgroups, one thread per query row: 128 scores straight from TMEM, no exchange between
 //     threads, exp2 domain, lazy rescaling of O (the running maximum used for exponentiation only moves when
 //     it would grow by more than 2^8, so the O read-modify-write is rare).  A tcgen05.commit after Q K^T of
@@ -25,13 +25,8 @@
 #include "sm100.cuh"
 #include "peer_comm.cuh"
 
-// Of every ODY_FWD_POLY_DEN column pairs, the first ODY_FWD_POLY_NUM take their exponentials on the FMA pipe
-// (exp2_poly2) instead of the special-function unit, which otherwise has to deliver 16384 exponentials per
-// 128 x 128 tile at 16 per clock.
-#ifndef ODY_FWD_POLY_NUM
-#define ODY_FWD_POLY_NUM 0
-#define ODY_FWD_POLY_DEN 4
-#endif
+// POLY: of every 4 column pairs, the first POLY take their exponentials on the FMA pipe (exp2_poly2) instead of the
+// special-function unit, which otherwise has to deliver 16384 exponentials per 128 x 128 tile at 16 per clock.
 
 namespace ody {
 namespace fwd {
@@ -48,7 +43,7 @@ constexpr int SMEM_TOTAL = SMEM_TILES + 512 + 1024;
 // inside what the CTA was launched with or the increase never returns.
 constexpr int NUM_THREADS = 384;
 constexpr int NUM_THREADS_PUSH = NUM_THREADS + gc::COMM_THREADS;
-constexpr int REGS_ISSUE = 56, REGS_MATH = 200;                            // 384 threads launched with 168 registers each
+constexpr int REGS_ISSUE = 56, REGS_MATH = 216;                            // 384 threads launched with 168 registers each
 constexpr int REGS_ISSUE_PUSH = 48, REGS_MATH_PUSH = 184, REGS_COMM = 88;  // 512 threads launched with 128 each
 static_assert(128 * REGS_ISSUE + 256 * REGS_MATH <= NUM_THREADS * 168, "setmaxnreg split exceeds the CTA's registers");
 static_assert(128 * REGS_ISSUE_PUSH + 256 * REGS_MATH_PUSH + 128 * REGS_COMM <= NUM_THREADS_PUSH * 128, "setmaxnreg split exceeds the CTA's registers (push)");
@@ -65,7 +60,7 @@ struct Bars {
   uint64_t q_full[2];
   uint64_t k_full[KV_STAGES], k_empty[KV_STAGES];
   uint64_t v_full[KV_STAGES], v_empty[KV_STAGES];
-  uint64_t s_full[2], p_part[2][4], o_done[2];
+  uint64_t s_full[2], p_full[2], o_done[2];
   uint64_t drain;
   uint32_t tmem_base;
   int abort_flag;
@@ -79,7 +74,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 // PUSH: four extra comm warps in CTAs 0..push_ctas-1 store this rank's K/V shard into the gathered
 // buffers of the ring peers named by `pp` while the attention tiles run (ring attention: the kernel of
 // ring step s delivers the shard that the peer s+1 places downstream needs for its step s+1).
-template <bool PUSH>
+template <bool PUSH, int POLY>
 __global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -118,7 +113,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&bars->s_full[t], 1);
-      for (int g = 0; g < 4; ++g) mbar_init(&bars->p_part[t][g], 128);
+      mbar_init(&bars->p_full[t], 128);
       mbar_init(&bars->o_done[t], 1);
     }
     mbar_init(&bars->drain, 1);
@@ -206,14 +201,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
           umma_commit(&bars->s_full[t]);
         };
-        // O_t (+)= P_t V(j), keys [32 g, 32 g + 32): the probabilities arrive in four pieces, and the first
-        // pieces are multiplied while the softmax threads still exponentiate the later ones
-        auto issue_pv = [&](int t, int j, int g) {
-          const uint64_t v = desc_advance(vdesc0, (j & 1) * TILE_BYTES + g * 4096);
-          const uint32_t pa = tmem + COL_S + t * BN + g * 16;
+        // O_t (+)= P_t V(j)
+        auto issue_pv = [&](int t, int j) {
+          const uint64_t v = desc_advance(vdesc0, (j & 1) * TILE_BYTES);
+          const uint32_t pa = tmem + COL_S + t * BN;
           const uint32_t d = tmem + COL_O + t * HD;
-          umma_ts(d, pa, v, IDESC_PV, (j > 0 || g > 0) ? 1u : 0u);
-          umma_ts(d, pa + 8, desc_advance(v, 2048), IDESC_PV, 1u);
+          umma_ts(d, pa, v, IDESC_PV, j > 0 ? 1u : 0u);
+#pragma unroll
+          for (int kk = 1; kk < BN / 16; ++kk) umma_ts(d, pa + kk * 8, desc_advance(v, kk * 2048), IDESC_PV, 1u);
         };
         ok = mbar_wait(&bars->q_full[0], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL) &&
              mbar_wait(&bars->k_full[0], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
@@ -234,17 +229,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int t = 0; t < 2; ++t) {
             const int nt = t == 0 ? nA : nB;
             if (j >= nt) continue;
+            if (!mbar_wait(&bars->p_full[t], j & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
             if (!have_v) {
               if (!mbar_wait(&bars->v_full[s], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
               have_v = true;
             }
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (!mbar_wait(&bars->p_part[t][g], j & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
-              tc_fence_after();
-              issue_pv(t, j, g);
-            }
-            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, j);
             if (j + 1 < nt) {
               if (!have_k1) {
                 if (!mbar_wait(&bars->k_full[s1], ph1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
@@ -343,7 +334,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 0; c < 16; ++c) {
           float p0, p1;
           const uint64_t x2 = fma2(pk2u(sv[32 * g + 2 * c], sv[32 * g + 2 * c + 1]), sl2_2, nm_2);
-          if ((c % ODY_FWD_POLY_DEN) < ODY_FWD_POLY_NUM) {
+          if ((c % 4) < POLY) {
             exp2_poly2(x2, p0, p1);
           } else {
             upk2(x2, p0, p1);
@@ -354,15 +345,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           pk[c] = pack_bf16(p0, p1);
         }
         tmem_st_32x16(col_s + g * 16, pk);
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(&bars->p_part[t][g]);
       }
       {
         float r0, r1;
         upk2(rs2, r0, r1);
         l += r0 + r1;
       }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[t]);
     }
     // epilogue: O / l -> bf16 -> swizzled smem (this tile's Q is dead by now) -> TMA store; lse
     if (ok && nt > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_done[t], 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
@@ -428,6 +419,14 @@ extern "C" int ody_flash_fwd_ctas(int Tq, int H) {
   return ((Tq + ody::fwd::CTA_ROWS - 1) / ody::fwd::CTA_ROWS) * H;
 }
 
+static int g_fwd_poly = 0;
+// 0..2: how many of every four exponential pairs the forward evaluates on the FMA pipe (see POLY above)
+extern "C" int ody_flash_fwd_set_poly(int n) {
+  if (n < 0 || n > 2) return (int)cudaErrorInvalidValue;
+  g_fwd_poly = n;
+  return 0;
+}
+
 extern "C" int ody_flash_set_push_order(int unit_major) {
   return (int)cudaMemcpyToSymbol(ody::gc::g_push_unit_major, &unit_major, sizeof(unit_major));
 }
@@ -458,8 +457,10 @@ extern "C" int ody_flash_fwd_ex(const void* q, const void* k, const void* v, voi
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<false, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -486,11 +487,14 @@ extern "C" int ody_flash_fwd_ex(const void* q, const void* k, const void* v, voi
     if ((r = gc::fill_gather(pp, push))) return r;
     const int ctas = (int)(grid.x * grid.y);
     if (push->n_cta <= 0 || push->n_cta > ctas) return (int)cudaErrorInvalidValue;
-    flash_fwd_kernel<true><<<grid, NUM_THREADS_PUSH, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
-                                                                       pp, push->n_cta, sm);
+    flash_fwd_kernel<true, 0><<<grid, NUM_THREADS_PUSH, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
+                                                                          pp, push->n_cta, sm);
+  } else if (g_fwd_poly == 1) {
+    flash_fwd_kernel<false, 1><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, 0, sm);
+  } else if (g_fwd_poly == 2) {
+    flash_fwd_kernel<false, 2><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, 0, sm);
   } else {
-    flash_fwd_kernel<false><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
-                                                                    pp, 0, sm);
+    flash_fwd_kernel<false, 0><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, 0, sm);
   }
   return (int)cudaGetLastError();
 }
