@@ -136,7 +136,7 @@ def bench_elementwise(lib, T=8192, d=4096, I=11008, V=32000):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "elementwise", "all"])
+    ap.add_argument("what", choices=["gemm", "gemm_all", "attn_fwd", "attn_bwd", "elementwise", "all"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -147,12 +147,14 @@ def main():
     ap.add_argument("--full", action="store_true", help="non-causal attention")
     ap.add_argument("--no-lib", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--gemm-variant", type=int, default=0, help="0 automatic, 1 one-CTA kernel, 2 CTA-pair kernel")
     ap.add_argument("--fwd-poly", type=int, default=0, help="attention forward: exponential pairs per four on the FMA pipe (0..2)")
     a = ap.parse_args()
     from odysseus_transformer_b200.ops import native
     native.set_backend("fused")
     lib = native.lib()
     lib.attn_fwd_set_poly(a.fwd_poly)
+    lib.gemm_set_variant(a.gemm_variant)
     wl = not a.no_lib
     if a.what == "gemm":
         bench_gemm(lib, a.m, a.n, a.k, a.layout, wl, a.iters)
@@ -166,6 +168,12 @@ def main():
                                (T, d, 3 * d, 1), (T, d, 2 * I, 1), (T, I, d, 1),
                                (3 * d, d, T, 2), (2 * I, d, T, 2), (d, I, T, 2)]:
             bench_gemm(lib, M, N, K, lay, wl, a.iters)
+        if a.what == "gemm_all":
+            # the skinny 8-GPU shapes of the TP-SP attention linears: [65536, 1536, 4096] and K = 512
+            for (M, N, K, lay) in [(65536, 1536, d, 0), (65536, d, 512, 0), (65536, d, 1536, 1), (1536, d, 65536, 2)]:
+                bench_gemm(lib, M, N, K, lay, wl, a.iters)
+            native.check_status(0)
+            return
         bench_attn(lib, T, 32, 32, True, "fwd", wl, a.iters)
         bench_attn(lib, T, 32, 32, True, "bwd", wl, a.iters)
         bench_attn(lib, 32768, 4, 4, True, "fwd", wl, 5)

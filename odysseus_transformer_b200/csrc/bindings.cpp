@@ -341,6 +341,7 @@ void ody_register_comm(pybind11::module& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out") = py::none(), py::arg("layout") = 0,
         py::arg("accumulate") = false);
+  m.def("gemm_set_variant", [](int64_t v) { ODY_CHECK(ody_gemm_set_variant((int)v), "gemm_set_variant (0 auto, 1 one CTA, 2 CTA pairs)"); });
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

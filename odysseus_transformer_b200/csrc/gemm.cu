@@ -12,6 +12,7 @@
 // two 256-column fp32 accumulators in TMEM (all 512 columns) so the epilogue of tile i overlaps the
 // main loop of tile i+1.  The epilogue converts to bf16, stages 128 x 64 blocks in swizzled smem and
 // writes them with TMA stores (edges are clipped by the tensor map).  No cluster multicast anywhere.
+// gemm_2cta.cu holds the same GEMM on CTA pairs (cta_group::2); ody_gemm_bf16 at the end of this file chooses.
 #include "ody_kernels.h"
 #include "sm100.cuh"
 
@@ -296,9 +297,29 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
 
 }  // namespace ody
 
+static int g_gemm_variant = 0;
+// 0: choose per problem (the pair kernel of gemm_2cta.cu once there are two row blocks to pair up), 1: always the
+// one-CTA kernel of this file, 2: always the pair kernel
+extern "C" int ody_gemm_set_variant(int v) {
+  if (v < 0 || v > 2) return (int)cudaErrorInvalidValue;
+  g_gemm_variant = v;
+  return 0;
+}
+
 extern "C" int ody_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
                              int64_t ldc, int layout, int accumulate, int* err, cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0) return (int)cudaErrorInvalidValue;
+  bool pairs = g_gemm_variant == 2;
+  if (g_gemm_variant == 0 && M > 128) {
+    // Both kernels are persistent; what differs per problem is how full their last wave is.  The pair kernel is
+    // the faster one per tile (measured ~6 %), so it is chosen unless its tail costs more than that.
+    const int sms = ody::g_num_sms > 0 ? ody::g_num_sms : 148;
+    const int64_t t1 = (int64_t)((M + 127) / 128) * ((N + 255) / 256), t2 = (int64_t)((M + 255) / 256) * ((N + 255) / 256);
+    const int64_t s1 = sms, s2 = sms / 2;
+    const double e1 = (double)t1 / (double)(((t1 + s1 - 1) / s1) * s1), e2 = (double)t2 / (double)(((t2 + s2 - 1) / s2) * s2);
+    pairs = e2 * 1.06 >= e1;
+  }
+  if (pairs) return ody_gemm_bf16_2cta(A, B, C, M, N, K, lda, ldb, ldc, layout, accumulate, err, st);
   if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15))
     return (int)cudaErrorInvalidValue;
   switch (layout) {

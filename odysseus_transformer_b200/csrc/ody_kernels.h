@@ -58,6 +58,11 @@ int ody_attn_merge_parts(void* out, float* lse, int64_t T, int H, int hd, const 
 // err: device int that receives a non-zero code if a bounded wait inside the kernel gave up.
 int ody_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                   int layout, int accumulate, int* err, cudaStream_t stream);
+// the same GEMM on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles, clusters of two); ody_gemm_bf16 picks between
+// the two kernels per problem unless ody_gemm_set_variant(1 = one-CTA only, 2 = pairs only, 0 = automatic) says otherwise
+int ody_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                       int layout, int accumulate, int* err, cudaStream_t stream);
+int ody_gemm_set_variant(int variant);
 
 // ---- attention forward (head_dim 128): q [Tq,H,128], k/v [Tk,Hkv,128], row pitches in elements; out bf16, lse [H,Tq]
 // fp32 natural log.  causal needs Tq == Tk.

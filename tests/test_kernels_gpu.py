@@ -27,9 +27,17 @@ GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (304, 264, 200)
                (2048, 4096, 1024), (8, 8, 8)]
 
 
+@pytest.fixture(params=[1, 2], ids=["one_cta", "cta_pair"])
+def gemm_variant(request, lib):
+    """Run a GEMM test on the one-CTA kernel and on the cta_group::2 pair kernel; restore automatic choice after."""
+    lib.gemm_set_variant(request.param)
+    yield request.param
+    lib.gemm_set_variant(0)
+
+
 @pytest.mark.parametrize("layout", [0, 1, 2])
-@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
-def test_gemm(lib, layout, M, N, K):
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES + [(640, 1280, 192), (8192, 1536, 512)])
+def test_gemm(lib, gemm_variant, layout, M, N, K):
     torch.manual_seed(M * 7 + N * 3 + K + layout)
     if layout == 0:
         a, b = _rand(M, K), _rand(N, K)
@@ -50,7 +58,7 @@ def test_gemm(lib, layout, M, N, K):
     assert rel < 5e-3, f"layout {layout} {M}x{N}x{K}: rel err {rel}"
 
 
-def test_gemm_accumulate_and_strided_out(lib):
+def test_gemm_accumulate_and_strided_out(lib, gemm_variant):
     M, N, K = 512, 384, 256
     a, b = _rand(K, M), _rand(K, N)
     base = _rand(M, N)
