@@ -148,12 +148,13 @@ def main():
     ap.add_argument("--no-lib", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--gemm-variant", type=int, default=0, help="0 automatic, 1 one-CTA kernel, 2 CTA-pair kernel")
-    ap.add_argument("--fwd-poly", type=int, default=0, help="attention forward: exponential pairs per four on the FMA pipe (0..2)")
+    ap.add_argument("--fwd-kslice", type=int, default=-1, help="attention forward: 1 = Q / K tiles as 32-byte-swizzled slices, 0 = 128-byte halves")
     a = ap.parse_args()
     from odysseus_transformer_b200.ops import native
     native.set_backend("fused")
     lib = native.lib()
-    lib.attn_fwd_set_poly(a.fwd_poly)
+    if a.fwd_kslice >= 0:
+        lib.attn_fwd_set_kslice(bool(a.fwd_kslice))
     lib.gemm_set_variant(a.gemm_variant)
     wl = not a.no_lib
     if a.what == "gemm":

@@ -151,7 +151,7 @@ void ody_register_attention(pybind11::module& m) {
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_fwd_split", &attn_fwd_split);
   m.def("attn_bwd_split", &attn_bwd_split);
-  m.def("attn_fwd_set_poly", [](int64_t n) { req(ody_flash_fwd_set_poly((int)n) == 0, "attn_fwd_set_poly: 0..2"); });
+  m.def("attn_fwd_set_kslice", [](bool on) { req(ody_flash_fwd_set_kslice(on ? 1 : 0) == 0, "attn_fwd_set_kslice"); });
   m.def("attn_fwd_ctas", [](int64_t Tq, int64_t H) { return (int64_t)ody_flash_fwd_ctas((int)Tq, (int)H); });
   m.def("attn_bwd_set_trace", [](const c10::optional<at::Tensor>& t) {
     if (t.has_value()) { req(t.value().is_cuda() && t.value().scalar_type() == at::kLong && t.value().numel() >= 96 * 8, "trace: int64 [96*8] (dK/dV kernel stamps, then dQ kernel stamps; only a build with -DODY_ATTN_TRACE records them)"); ody_flash_bwd_set_trace((long long*)t.value().data_ptr()); }

@@ -25,8 +25,10 @@
 #include "sm100.cuh"
 #include "peer_comm.cuh"
 
-// POLY: of every 4 column pairs, the first POLY take their exponentials on the FMA pipe (exp2_poly2) instead of the
-// special-function unit, which otherwise has to deliver 16384 exponentials per 128 x 128 tile at 16 per clock.
+// KS32: Q and K sit in shared memory as eight [128 rows x 32 B] slices (32-byte swizzle) instead of two
+// [128 rows x 128 B] halves (128-byte swizzle), so that each Q K^T instruction reads two contiguous 4 KB blocks.
+// (Moving part of the exponentials from the special-function unit to an FMA-pipe polynomial, or announcing P in four
+// pieces so that P V starts early, both measured slower than this form.)
 
 namespace ody {
 namespace fwd {
@@ -74,7 +76,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 // PUSH: four extra comm warps in CTAs 0..push_ctas-1 store this rank's K/V shard into the gathered
 // buffers of the ring peers named by `pp` while the attention tiles run (ring attention: the kernel of
 // ring step s delivers the shard that the peer s+1 places downstream needs for its step s+1).
-template <bool PUSH, int POLY>
+template <bool PUSH, bool KS32>
 __global__ void __launch_bounds__(PUSH ? NUM_THREADS_PUSH : NUM_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -145,22 +147,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (warp == 0) {
       // ------------------------------------------------------------------ TMA producer
       if (lane == 0) {
-        mbar_expect_tx(&bars->q_full[0], TILE_BYTES);
-        tma_load_3d(sQ, &tmQ, 0, head, q0, &bars->q_full[0]);
-        tma_load_3d(sQ + HALF_BYTES, &tmQ, 64, head, q0, &bars->q_full[0]);
-        if (has_b) {
-          mbar_expect_tx(&bars->q_full[1], TILE_BYTES);
-          tma_load_3d(sQ + TILE_BYTES, &tmQ, 0, head, q0 + BM, &bars->q_full[1]);
-          tma_load_3d(sQ + TILE_BYTES + HALF_BYTES, &tmQ, 64, head, q0 + BM, &bars->q_full[1]);
-        }
+        // a [128 x 128] K-major tile: two 64-column halves, or eight 16-column slices with KS32
+        auto load_kmajor = [&](uint8_t* dst, const CUtensorMap* tm, int h, int row, uint64_t* bar) {
+          mbar_expect_tx(bar, TILE_BYTES);
+          if constexpr (KS32) {
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) tma_load_3d(dst + kk * 4096, tm, kk * 16, h, row, bar);
+          } else {
+            tma_load_3d(dst, tm, 0, h, row, bar);
+            tma_load_3d(dst + HALF_BYTES, tm, 64, h, row, bar);
+          }
+        };
+        load_kmajor(sQ, &tmQ, head, q0, &bars->q_full[0]);
+        if (has_b) load_kmajor(sQ + TILE_BYTES, &tmQ, head, q0 + BM, &bars->q_full[1]);
         int issued_k = 0, issued_v = 0;
         for (int j = 0; j < nblk; ++j) {
           const int s = j & 1;
           const uint32_t ph = (j >> 1) & 1;
           if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
-          mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
-          tma_load_3d(sK + s * TILE_BYTES, &tmK, 0, kv_head, j * BN, &bars->k_full[s]);
-          tma_load_3d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, 64, kv_head, j * BN, &bars->k_full[s]);
+          load_kmajor(sK + s * TILE_BYTES, &tmK, kv_head, j * BN, &bars->k_full[s]);
           ++issued_k;
           if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
           mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
@@ -184,8 +189,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0) {
         constexpr uint32_t IDESC_QK = make_idesc_bf16(BM, BN, 0, 0);
         constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
-        const uint64_t qdesc0 = make_smem_desc(smem_u32(sQ), 16, 1024);
-        const uint64_t kdesc0 = make_smem_desc(smem_u32(sK), 16, 1024);
+        const uint64_t qdesc0 = KS32 ? make_smem_desc_sw32(smem_u32(sQ)) : make_smem_desc(smem_u32(sQ), 16, 1024);
+        const uint64_t kdesc0 = KS32 ? make_smem_desc_sw32(smem_u32(sK)) : make_smem_desc(smem_u32(sK), 16, 1024);
         const uint64_t vdesc0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
         bool ok = true;
         // S_t = Q_t K(j)^T
@@ -196,7 +201,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_ss(d, q, k, IDESC_QK, 0u);
 #pragma unroll
           for (int kk = 1; kk < HD / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+            const uint32_t off = KS32 ? kk * 4096 : (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
             umma_ss(d, desc_advance(q, off), desc_advance(k, off), IDESC_QK, 1u);
           }
           umma_commit(&bars->s_full[t]);
@@ -334,13 +339,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 0; c < 16; ++c) {
           float p0, p1;
           const uint64_t x2 = fma2(pk2u(sv[32 * g + 2 * c], sv[32 * g + 2 * c + 1]), sl2_2, nm_2);
-          if ((c % 4) < POLY) {
-            exp2_poly2(x2, p0, p1);
-          } else {
-            upk2(x2, p0, p1);
-            p0 = exp2_mufu(p0);
-            p1 = exp2_mufu(p1);
-          }
+          upk2(x2, p0, p1);
+          p0 = exp2_mufu(p0);
+          p1 = exp2_mufu(p1);
           rs2 = add2(rs2, pk2(p0, p1));
           pk[c] = pack_bf16(p0, p1);
         }
@@ -419,11 +420,10 @@ extern "C" int ody_flash_fwd_ctas(int Tq, int H) {
   return ((Tq + ody::fwd::CTA_ROWS - 1) / ody::fwd::CTA_ROWS) * H;
 }
 
-static int g_fwd_poly = 0;
-// 0..2: how many of every four exponential pairs the forward evaluates on the FMA pipe (see POLY above)
-extern "C" int ody_flash_fwd_set_poly(int n) {
-  if (n < 0 || n > 2) return (int)cudaErrorInvalidValue;
-  g_fwd_poly = n;
+static int g_fwd_ks32 = 0;
+// 1: Q and K tiles as eight 32-byte-swizzled slices (KS32 above), 0: as two 128-byte-swizzled halves
+extern "C" int ody_flash_fwd_set_kslice(int on) {
+  g_fwd_ks32 = on ? 1 : 0;
   return 0;
 }
 
@@ -457,17 +457,18 @@ extern "C" int ody_flash_fwd_ex(const void* q, const void* k, const void* v, voi
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)o) & 15) return (int)cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<false, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<true, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_fwd_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   CUtensorMap tQ, tK, tV, tO;
   int r;
-  if ((r = make_tmap_3d_bf16(&tQ, q, HD, H, Tq, HD * 2, q_row * 2, 64, 1, BM))) return 730000 + r;
-  if ((r = make_tmap_3d_bf16(&tK, k, HD, Hkv, Tk, HD * 2, k_row * 2, 64, 1, BN))) return 740000 + r;
+  const bool ks32 = g_fwd_ks32 != 0;
+  if ((r = make_tmap_3d_bf16(&tQ, q, HD, H, Tq, HD * 2, q_row * 2, ks32 ? 16 : 64, 1, BM, ks32))) return 730000 + r;
+  if ((r = make_tmap_3d_bf16(&tK, k, HD, Hkv, Tk, HD * 2, k_row * 2, ks32 ? 16 : 64, 1, BN, ks32))) return 740000 + r;
   if ((r = make_tmap_3d_bf16(&tV, v, HD, Hkv, Tk, HD * 2, v_row * 2, 64, 1, BN))) return 750000 + r;
   if ((r = make_tmap_3d_bf16(&tO, o, HD, H, Tq, HD * 2, o_row * 2, 64, 1, BM))) return 760000 + r;
   SplitMaps sm;
@@ -487,14 +488,14 @@ extern "C" int ody_flash_fwd_ex(const void* q, const void* k, const void* v, voi
     if ((r = gc::fill_gather(pp, push))) return r;
     const int ctas = (int)(grid.x * grid.y);
     if (push->n_cta <= 0 || push->n_cta > ctas) return (int)cudaErrorInvalidValue;
-    flash_fwd_kernel<true, 0><<<grid, NUM_THREADS_PUSH, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err,
-                                                                          pp, push->n_cta, sm);
-  } else if (g_fwd_poly == 1) {
-    flash_fwd_kernel<false, 1><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, 0, sm);
-  } else if (g_fwd_poly == 2) {
-    flash_fwd_kernel<false, 2><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, 0, sm);
+    if (ks32)
+      flash_fwd_kernel<true, true><<<grid, NUM_THREADS_PUSH, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, push->n_cta, sm);
+    else
+      flash_fwd_kernel<true, false><<<grid, NUM_THREADS_PUSH, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, push->n_cta, sm);
+  } else if (ks32) {
+    flash_fwd_kernel<false, true><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, 0, sm);
   } else {
-    flash_fwd_kernel<false, 0><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, 0, sm);
+    flash_fwd_kernel<false, false><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tQ, tK, tV, tO, lse, Tq, Tk, H, Hkv, causal, scale, err, pp, 0, sm);
   }
   return (int)cudaGetLastError();
 }

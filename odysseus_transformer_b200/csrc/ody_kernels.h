@@ -75,8 +75,8 @@ int ody_flash_fwd(const void* q, const void* k, const void* v, void* o, float* l
 int64_t ody_flash_bwd_workspace_bytes(int Tq, int H);
 /* CTAs of the forward grid (one per 256 query rows and head): the upper bound of a push description's n_cta */
 int ody_flash_fwd_ctas(int Tq, int H);
-/* 0..2 of every four exponential pairs of the forward on the FMA pipe instead of the special-function unit */
-int ody_flash_fwd_set_poly(int n);
+/* 1: the forward keeps its Q / K tiles as eight 32-byte-swizzled slices, 0: as two 128-byte-swizzled halves */
+int ody_flash_fwd_set_kslice(int on);
 /* optional 96 x 8 int64 timeline of one CTA of each backward kernel; recorded only by a build with -DODY_ATTN_TRACE */
 void ody_flash_bwd_set_trace(long long* buf);
 int ody_flash_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,

@@ -302,6 +302,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
   d |= (uint64_t)2 << 61;   // SWIZZLE_128B
   return d;
 }
+// K-major operand stored as K / 16 slices of [rows x 32 B] with the 32-byte swizzle (TMA SWIZZLE_32B tiles whose rows are
+// 32 bytes): the 16-deep slice one MMA instruction reads is then one contiguous rows x 32 B block - whole 128-byte
+// lines - instead of a 32-byte piece out of every row of a 128-byte-swizzled tile.  8-row groups are 256 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc_sw32(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+  d |= (uint64_t)(1) << 16;                  // leading-dimension offset: unused for swizzled K-major operands
+  d |= (uint64_t)((256 >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;   // descriptor version for sm_100
+  d |= (uint64_t)6 << 61;   // SWIZZLE_32B
+  return d;
+}
 // Same, without swizzle ("interleaved" core matrices of 8 rows x 16 bytes): K-adjacent core matrices `lbo` bytes
 // apart, 8-row groups `sbo` apart.  Used for the 16-column statistics tiles of the attention backward.
 __device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -393,10 +405,11 @@ inline int make_tmap_2d_bf16_linear(CUtensorMap* m, const void* base, uint64_t i
   return (int)r;
 }
 
-// 3-D bf16 tensor {inner, mid, outer} with byte pitches for mid and outer.
+// 3-D bf16 tensor {inner, mid, outer} with byte pitches for mid and outer.  box_inner * 2 bytes must equal the swizzle
+// span: 128 for the default, 32 with sw32 (box_inner 16).
 inline int make_tmap_3d_bf16(CUtensorMap* m, const void* base, uint64_t inner, uint64_t mid, uint64_t outer,
                              uint64_t pitch_mid_bytes, uint64_t pitch_outer_bytes, uint32_t box_inner,
-                             uint32_t box_mid, uint32_t box_outer) {
+                             uint32_t box_mid, uint32_t box_outer, bool sw32 = false) {
   PFN_encodeTiled enc = get_encode_fn();
   if (enc == nullptr) return -1;
   cuuint64_t dims[3] = {inner, mid, outer};
@@ -404,8 +417,8 @@ inline int make_tmap_3d_bf16(CUtensorMap* m, const void* base, uint64_t inner, u
   cuuint32_t box[3] = {box_inner, box_mid, box_outer};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return (int)r;
 }
 

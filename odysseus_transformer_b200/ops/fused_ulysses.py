@@ -19,9 +19,16 @@ backward dq,dk,dv          attention backward kernels store each gradient tile t
 Receivers wait (bounded, one small kernel) on per-source arrival words before the consumer kernel
 is launched, and tell the senders through ``consumed`` epoch words when a buffer may be overwritten.
 One autograd function covers the whole block, so no gradient ever exists in a layout autograd would
-have to understand.  Requirements: bf16, head_dim 128, local tokens a multiple of 128, ring degree 1,
-symmetric heaps for the weight group and the exchange group; otherwise ``available`` is False and the
-module runs the torch.distributed composition.
+have to understand.  Requirements: bf16, head_dim 128, local tokens a multiple of 128, symmetric heaps
+for the weight group and the exchange group; otherwise ``available`` is False and the module runs the
+torch.distributed composition.
+
+Inner x ring hybrid (ring degree > 1, the layout the reference README only claims, reference
+``README.md:14``): the attention core is the zigzag ring attention of ``ops.fused_comm`` (K/V pushed by
+comm warps inside the attention kernels).  Its output is merged over ring steps by a separate kernel,
+so the two exchanges that follow attention (o forward, dq/dk/dv backward) cannot ride an attention
+epilogue; they run as one NCCL all-to-all each, while the two exchanges that follow a GEMM (q/k/v
+forward, dO backward) stay in the GEMM epilogues.
 """
 from __future__ import annotations
 
@@ -34,9 +41,11 @@ from . import native
 
 def available(mod, x: torch.Tensor) -> bool:
     pc = mod.pctx
-    if pc.inner_size < 2 or pc.ring_size > 1 or mod.head_dim != 128 or x.shape[0] % 128:
+    if pc.inner_size < 2 or mod.head_dim != 128 or x.shape[0] % 128:
         return False
     if not (FC.enabled(x, pc.inner_group) and FC.enabled(x, pc.world_group)):
+        return False
+    if pc.ring_size > 1 and not FC.enabled(x, pc.ring_group):
         return False
     return native.has_native_attention() and native.has_native_attention_bwd()
 
@@ -84,16 +93,23 @@ class _FusedUlyssesAttention(Function):
         _rope_inplace_(qkv3, hq + hkv, cos, sin, False)
         q, k, v = qkv3[:, :hq], qkv3[:, hq:hq + hkv], qkv3[:, hq + hkv:]
 
-        # 2. attention; each output tile also goes to the rank that owns its rows (columns of head group r there)
-        s_o = _need(heap_a.a2a_slot(t, U * hq * 128, "o"), "the attention-output receive buffer")
-        e_o = s_o.begin_epoch()
-        lib.wait_flags(flag_dev, s_o.consumed_local(), everyone, e_o - 1)
-        dests = [s_o.on_peer(p).view(t, U, hq, 128)[:, r] for p in range(U)]
-        o, lse = lib.attn_fwd_split(q, k, v, True, mod.head_dim ** -0.5, dests)
-        lib.signal_flags(flag_dev, s_o.arrived_ptrs(), everyone, r, e_o)
-        lib.wait_flags(flag_dev, s_o.arrived_local(), everyone, e_o)
-        o_seq = s_o.local().clone()                     # [t, H * 128], kept for the o_proj wgrad
-        lib.signal_flags(flag_dev, s_o.consumed_ptrs(), everyone, r, e_o)
+        scale = mod.head_dim ** -0.5
+        if pc.ring_size > 1:
+            # 2'. hybrid: zigzag ring attention over the ring group, then the head -> sequence exchange as one all-to-all
+            from ..parallel.attention import _head_to_seq
+            o, lse = FC.ring_attn_fwd(q, k, v, pc.ring_group, scale)
+            o_seq = _head_to_seq(o, pc.inner_group).reshape(t, U * hq * 128)
+        else:
+            # 2. attention; each output tile also goes to the rank that owns its rows (columns of head group r there)
+            s_o = _need(heap_a.a2a_slot(t, U * hq * 128, "o"), "the attention-output receive buffer")
+            e_o = s_o.begin_epoch()
+            lib.wait_flags(flag_dev, s_o.consumed_local(), everyone, e_o - 1)
+            dests = [s_o.on_peer(p).view(t, U, hq, 128)[:, r] for p in range(U)]
+            o, lse = lib.attn_fwd_split(q, k, v, True, scale, dests)
+            lib.signal_flags(flag_dev, s_o.arrived_ptrs(), everyone, r, e_o)
+            lib.wait_flags(flag_dev, s_o.arrived_local(), everyone, e_o)
+            o_seq = s_o.local().clone()                     # [t, H * 128], kept for the o_proj wgrad
+            lib.signal_flags(flag_dev, s_o.consumed_ptrs(), everyone, r, e_o)
 
         # 3. output projection (ZeRO-3 weight gather fused)
         y = _gather_w(heap_w, sched, io, +1, wo.detach(), o_seq, 0)
@@ -127,29 +143,42 @@ class _FusedUlyssesAttention(Function):
         lib.wait_flags(flag_dev, s_do.arrived_local(), everyone, s_do.arrived_total)
         do = s_do.local().view(Tb, hq, 128)
 
-        # 2. attention backward; gradient tiles go to the rank owning the rows, landing packed as [t, U * G]
-        s_dqkv = _need(heap_a.a2a_slot(t, U * G, "dqkv"), "the dq/dk/dv receive buffer")
-        e = s_dqkv.begin_epoch()
-        lib.wait_flags(flag_dev, s_dqkv.consumed_local(), everyone, e - 1)
         qkv3 = qkv.view(Tb, nh, 128)
         q, k, v = qkv3[:, :hq], qkv3[:, hq:hq + hkv], qkv3[:, hq + hkv:]
-        there = [s_dqkv.on_peer(p).view(t, U, nh, 128)[:, r] for p in range(U)]
-        lib.attn_bwd_split(do, q, k, v, o, lse, True, mod.head_dim ** -0.5, [d[:, :hq] for d in there],
-                           [d[:, hq:hq + hkv] for d in there], [d[:, hq + hkv:] for d in there])
-        lib.signal_flags(flag_dev, s_do.consumed_ptrs(), everyone, r, s_do.uses)
-        lib.signal_flags(flag_dev, s_dqkv.arrived_ptrs(), everyone, r, e)
-        lib.wait_flags(flag_dev, s_dqkv.arrived_local(), everyone, e)
-        dqkv = s_dqkv.local()
-        # inverse rotation of the dq / dk heads of every head group, at this rank's own token positions
-        cos_l, sin_l = cos[r * t:(r + 1) * t], sin[r * t:(r + 1) * t]
-        by_group = dqkv.view(t, U, nh, 128)
-        for u in range(U):
-            _rope_inplace_(by_group[:, u], hq + hkv, cos_l, sin_l, True)
+        scale = mod.head_dim ** -0.5
+        hybrid = pc.ring_size > 1
+        if hybrid:
+            # 2'. hybrid: ring attention backward into a local packed gradient, inverse rotation at the block's positions,
+            # then the head -> sequence exchange of the packed gradient as one all-to-all
+            from ..parallel.attention import _head_to_seq
+            dq3 = torch.empty_like(qkv3)
+            FC.ring_attn_bwd(do, q, k, v, o, lse, pc.ring_group, scale, dqkv=dq3)
+            lib.signal_flags(flag_dev, s_do.consumed_ptrs(), everyone, r, s_do.uses)
+            _rope_inplace_(dq3, hq + hkv, cos, sin, True)
+            dqkv = _head_to_seq(dq3, pc.inner_group).reshape(t, U * G)
+        else:
+            # 2. attention backward; gradient tiles go to the rank owning the rows, landing packed as [t, U * G]
+            s_dqkv = _need(heap_a.a2a_slot(t, U * G, "dqkv"), "the dq/dk/dv receive buffer")
+            e = s_dqkv.begin_epoch()
+            lib.wait_flags(flag_dev, s_dqkv.consumed_local(), everyone, e - 1)
+            there = [s_dqkv.on_peer(p).view(t, U, nh, 128)[:, r] for p in range(U)]
+            lib.attn_bwd_split(do, q, k, v, o, lse, True, scale, [d[:, :hq] for d in there],
+                               [d[:, hq:hq + hkv] for d in there], [d[:, hq + hkv:] for d in there])
+            lib.signal_flags(flag_dev, s_do.consumed_ptrs(), everyone, r, s_do.uses)
+            lib.signal_flags(flag_dev, s_dqkv.arrived_ptrs(), everyone, r, e)
+            lib.wait_flags(flag_dev, s_dqkv.arrived_local(), everyone, e)
+            dqkv = s_dqkv.local()
+            # inverse rotation of the dq / dk heads of every head group, at this rank's own token positions
+            cos_l, sin_l = cos[r * t:(r + 1) * t], sin[r * t:(r + 1) * t]
+            by_group = dqkv.view(t, U, nh, 128)
+            for u in range(U):
+                _rope_inplace_(by_group[:, u], hq + hkv, cos_l, sin_l, True)
 
         # 3. QKV projection backward, reading the receive buffer in place
         dx = _gather_w(heap_w, sched, iq, -1, wqkv.detach(), dqkv, 1)
         g_wqkv = FC.zero3_wgrad(heap_w, pc.world_group, wqkv, dqkv, x)
-        lib.signal_flags(flag_dev, s_dqkv.consumed_ptrs(), everyone, r, e)
+        if not hybrid:
+            lib.signal_flags(flag_dev, s_dqkv.consumed_ptrs(), everyone, r, e)
         return dx, g_wqkv, g_wo, None, None, None
 
 

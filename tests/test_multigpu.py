@@ -35,6 +35,23 @@ def test_modes_2gpu(mode, backend):
     _launch(2, mode, "small", 1024, 0, 1, backend)
 
 
+def test_shard_rows_with_tile_edges_2gpu():
+    """L / N = 192: shard boundaries fall inside 128-row tiles of the fused GEMMs (64-row units on the wire)."""
+    _launch(2, "odysseus", "small", 384, 0, 1, "fused", 2)
+    _launch(2, "tpsp", "small", 384, 0, 1, "fused", 2)
+
+
+@pytest.mark.parametrize("mode", ["odysseus", "ulysses", "ring"])
+def test_five_iterations_reuse_every_slot_2gpu(mode):
+    """Both buffers of every slot pair are reused several times; the cumulative arrival targets keep growing."""
+    _launch(2, mode, "small", 1024, 0, 1, "fused", 5)
+
+
+@pytest.mark.parametrize("variant", ["zero2", "gradckpt", "chunked"])
+def test_optional_modes_fused_2gpu(variant):
+    _launch(2, "odysseus", "small", 1024, 0, 1, "fused", 3, variant)
+
+
 def test_ulysses_4gpu():
     if torch.cuda.device_count() < 4:
         pytest.skip("needs 4 GPUs")
