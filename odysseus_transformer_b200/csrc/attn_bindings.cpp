@@ -151,6 +151,11 @@ void ody_register_attention(pybind11::module& m) {
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_fwd_split", &attn_fwd_split);
   m.def("attn_bwd_split", &attn_bwd_split);
+  m.def("attn_fwd_set_trace", [](const c10::optional<at::Tensor>& t) {
+    if (t.has_value()) req(t.value().is_cuda() && t.value().scalar_type() == at::kLong && t.value().numel() >= 64 * 16, "trace: int64 [64*16]");
+    req(ody_flash_fwd_set_trace(t.has_value() ? (long long*)t.value().data_ptr() : nullptr) == 0,
+        "attn_fwd_set_trace needs a build with -DODY_ATTN_TRACE");
+  });
   m.def("attn_fwd_set_kslice", [](bool on) { req(ody_flash_fwd_set_kslice(on ? 1 : 0) == 0, "attn_fwd_set_kslice"); });
   m.def("attn_fwd_ctas", [](int64_t Tq, int64_t H) { return (int64_t)ody_flash_fwd_ctas((int)Tq, (int)H); });
   m.def("attn_bwd_set_trace", [](const c10::optional<at::Tensor>& t) {

@@ -30,6 +30,15 @@
 // (Moving part of the exponentials from the special-function unit to an FMA-pipe polynomial, or announcing P in four
 // pieces so that P V starts early, both measured slower than this form.)
 
+// Development aid, compiled only with -DODY_ATTN_TRACE: SM-clock stamps of one CTA's first blocks, written to a buffer
+// given with ody_flash_fwd_set_trace ([64 blocks][16] int64: 0-4 softmax of tile A, 5-9 softmax of tile B, 10-13 MMA thread).
+#ifdef ODY_ATTN_TRACE
+__device__ long long* g_fwd_trace_buf = nullptr;
+#define ODY_FWD_STAMP(cond, j, slot) do { if ((cond) && (j) < 64 && g_fwd_trace_buf) g_fwd_trace_buf[(j) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define ODY_FWD_STAMP(cond, j, slot) do { } while (0)
+#endif
+
 namespace ody {
 namespace fwd {
 
@@ -235,6 +244,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const int nt = t == 0 ? nA : nB;
             if (j >= nt) continue;
             if (!mbar_wait(&bars->p_full[t], j & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+            ODY_FWD_STAMP(blockIdx.x == 0 && blockIdx.y == 0, j, 10 + t * 2);
             if (!have_v) {
               if (!mbar_wait(&bars->v_full[s], ph, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
               have_v = true;
@@ -247,6 +257,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 have_k1 = true;
               }
               issue_qk(t, j + 1);      // its commit on s_full[t] also covers the P V just issued
+              ODY_FWD_STAMP(blockIdx.x == 0 && blockIdx.y == 0, j, 11 + t * 2);
             } else {
               umma_commit(&bars->o_done[t]);
             }
@@ -278,8 +289,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nt; ++j) {
+      const bool tr = blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x == 128 || threadIdx.x == 256);
+      ODY_FWD_STAMP(tr, j, t * 5 + 0);
       ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full[t], j & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
       if (!ok) break;
+      ODY_FWD_STAMP(tr, j, t * 5 + 1);
       tc_fence_after();
       uint32_t sv[128];
       tmem_ld_32x32(col_s, sv);
@@ -287,6 +301,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld_32x32(col_s + 64, sv + 64);
       tmem_ld_32x32(col_s + 96, sv + 96);
       tmem_ld_wait();
+      ODY_FWD_STAMP(tr, j, t * 5 + 2);
       const int kv0 = j * BN;
       if (j == diag) {
 #pragma unroll
@@ -328,6 +343,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           tmem_st_32x16(col_o + c * 16, o);
         }
       }
+      ODY_FWD_STAMP(tr, j, t * 5 + 3);
       // packed pairs: x = s * scale * log2(e) - m for two columns per instruction; P goes back over S in four
       // 32-column pieces (16 packed registers each)
       const uint64_t sl2_2 = pk2(sl2, sl2), nm_2 = pk2(-m_used, -m_used);
@@ -355,6 +371,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full[t]);
+      ODY_FWD_STAMP(tr, j, t * 5 + 4);
     }
     // epilogue: O / l -> bf16 -> swizzled smem (this tile's Q is dead by now) -> TMA store; lse
     if (ok && nt > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_done[t], 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
@@ -419,6 +436,12 @@ extern "C" int ody_flash_fwd(const void* q, const void* k, const void* v, void* 
 extern "C" int ody_flash_fwd_ctas(int Tq, int H) {
   return ((Tq + ody::fwd::CTA_ROWS - 1) / ody::fwd::CTA_ROWS) * H;
 }
+
+#ifdef ODY_ATTN_TRACE
+extern "C" int ody_flash_fwd_set_trace(long long* buf) { return (int)cudaMemcpyToSymbol(g_fwd_trace_buf, &buf, sizeof(buf)); }
+#else
+extern "C" int ody_flash_fwd_set_trace(long long*) { return (int)cudaErrorNotSupported; }
+#endif
 
 static int g_fwd_ks32 = 0;
 // 1: Q and K tiles as eight 32-byte-swizzled slices (KS32 above), 0: as two 128-byte-swizzled halves

@@ -77,6 +77,8 @@ int64_t ody_flash_bwd_workspace_bytes(int Tq, int H);
 int ody_flash_fwd_ctas(int Tq, int H);
 /* 1: the forward keeps its Q / K tiles as eight 32-byte-swizzled slices, 0: as two 128-byte-swizzled halves */
 int ody_flash_fwd_set_kslice(int on);
+/* development builds (-DODY_ATTN_TRACE) only: [64][16] int64 SM-clock stamps of one forward CTA; otherwise cudaErrorNotSupported */
+int ody_flash_fwd_set_trace(long long* buf);
 /* optional 96 x 8 int64 timeline of one CTA of each backward kernel; recorded only by a build with -DODY_ATTN_TRACE */
 void ody_flash_bwd_set_trace(long long* buf);
 int ody_flash_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse, void* dq,

@@ -243,7 +243,7 @@ def main(args) -> Dict[str, float]:
     writer = JsonlWriter(args.jsonl, rank)
     warmup = args.warmup_iterations
     timer = DeviceTimer(dev)
-    elapse, timed_steps = 0.0, 0
+    elapse, timed_steps, exposed_sum = 0.0, 0, 0.0
     loss_val = float("nan")
     with init_prof(args.use_profiler) as prof:
         for step in range(start_step, args.max_train_steps):
@@ -271,6 +271,8 @@ def main(args) -> Dict[str, float]:
             if args.jsonl:      # every rank takes part in the max-over-ranks reductions
                 rec["exposed_comm_ms"] = exposed_comm_ms(ctx, reset=True)
                 rec["phase_ms"] = trainer.phase_summary(reset=True)
+                if timed:
+                    exposed_sum += rec["exposed_comm_ms"]
             writer.write(**rec, **memory_gb(dev))
     trainer.check_status(block=True)
     dev_ms = max_over_ranks(timer.elapsed_ms(), dev)
@@ -281,8 +283,13 @@ def main(args) -> Dict[str, float]:
         m = memory_gb(dev)
         print(f"device time (max over ranks) {dev_ms / 1e3:.3f} s over {timed_steps} steps; {tok_s:.0f} tokens/s; "
               f"peak allocated {m['peak_allocated']:.2f} GB, peak reserved {m['peak_reserved']:.2f} GB")
-    writer.write(final=True, mode=args.parallel_mode, seq_length=args.seq_length, world=world, elapsed_s=elapse,
-                 device_s=dev_ms / 1e3, tokens_per_s=tok_s, model_tflops_per_gpu=flops / 1e12, **memory_gb(dev))
+    peak = max_over_ranks(memory_gb(dev)["peak_allocated"], dev)
+    writer.write(final=True, mode=args.parallel_mode, model=cfg.name, seq_length=args.seq_length, world=world,
+                 inner_degree=ctx.inner_size, ring_degree=ctx.ring_size, backend=native.get_backend(),
+                 grad_checkpoint=bool(args.grad_checkpoint), timed_steps=timed_steps, elapsed_s=elapse,
+                 device_s=dev_ms / 1e3, tokens_per_s=tok_s, model_tflops_per_gpu=flops / 1e12,
+                 exposed_comm_ms_per_step=(exposed_sum / timed_steps) if timed_steps else None,
+                 peak_allocated_gb_max_over_ranks=peak, **memory_gb(dev))
     writer.close()
     if args.save:
         ckpt.save_hf_checkpoint(trainer.model, args.save)

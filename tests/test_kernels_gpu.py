@@ -299,8 +299,16 @@ ATTN_CASES = [  # Tq, Tk, H, Hkv, causal
 ]
 
 
+@pytest.fixture(params=[False, True], ids=["halves128", "slices32"])
+def fwd_kslice(request, lib):
+    """Both shared-memory layouts of the forward's Q / K tiles."""
+    lib.attn_fwd_set_kslice(request.param)
+    yield request.param
+    lib.attn_fwd_set_kslice(False)
+
+
 @pytest.mark.parametrize("Tq,Tk,H,Hkv,causal", ATTN_CASES)
-def test_attention_fwd(lib, Tq, Tk, H, Hkv, causal):
+def test_attention_fwd(lib, fwd_kslice, Tq, Tk, H, Hkv, causal):
     from odysseus_transformer_b200.ops import torch_ref as R
     torch.manual_seed(Tq + Tk + H)
     q, k, v = _rand(Tq, H, 128), _rand(Tk, Hkv, 128), _rand(Tk, Hkv, 128)
