@@ -148,11 +148,13 @@ def main():
     ap.add_argument("--no-lib", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--gemm-variant", type=int, default=0, help="0 automatic, 1 one-CTA kernel, 2 CTA-pair kernel")
+    ap.add_argument("--bwd-variant", type=int, default=1, help="attention backward: 0 fused dK/dV/dQ kernel, 1 split kernels")
     ap.add_argument("--fwd-kslice", type=int, default=-1, help="attention forward: 1 = Q / K tiles as 32-byte-swizzled slices, 0 = 128-byte halves")
     a = ap.parse_args()
     from odysseus_transformer_b200.ops import native
     native.set_backend("fused")
     lib = native.lib()
+    lib.attn_bwd_set_variant(a.bwd_variant)
     if a.fwd_kslice >= 0:
         lib.attn_fwd_set_kslice(bool(a.fwd_kslice))
     lib.gemm_set_variant(a.gemm_variant)

@@ -15,7 +15,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 BUILD = os.path.join(HERE, "build")
 
-NVCC_FLAGS = (["-DODY_ATTN_TRACE"] if __import__("os").environ.get("ODY_ATTN_TRACE") else []) + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+# ODY_EXTRA_NVCC_FLAGS: extra flags for development builds, e.g. -DODY_ATTN_TRACE (clock-stamp timelines of the attention kernels)
+NVCC_FLAGS = os.environ.get("ODY_EXTRA_NVCC_FLAGS", "").split() + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"]
 
 

@@ -156,6 +156,7 @@ void ody_register_attention(pybind11::module& m) {
     req(ody_flash_fwd_set_trace(t.has_value() ? (long long*)t.value().data_ptr() : nullptr) == 0,
         "attn_fwd_set_trace needs a build with -DODY_ATTN_TRACE");
   });
+  m.def("attn_bwd_set_variant", [](int64_t v) { req(ody_flash_bwd_set_variant((int)v) == 0, "attn_bwd_set_variant: 0 fused, 1 split"); });
   m.def("attn_fwd_set_kslice", [](bool on) { req(ody_flash_fwd_set_kslice(on ? 1 : 0) == 0, "attn_fwd_set_kslice"); });
   m.def("attn_fwd_ctas", [](int64_t Tq, int64_t H) { return (int64_t)ody_flash_fwd_ctas((int)Tq, (int)H); });
   m.def("attn_bwd_set_trace", [](const c10::optional<at::Tensor>& t) {

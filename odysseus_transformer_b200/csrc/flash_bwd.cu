@@ -439,6 +439,444 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
+// ------------------------------------------------------------------------------------------- dK / dV / dQ in one kernel
+// The split pair above computes S and dP twice (seven 128 x 128 x 128 products per (query block, KV tile) pair) to stay
+// free of atomics.  This kernel computes them once (five products) and is the default: same grid and streaming as the
+// dK/dV kernel, plus
+//   * dS^T leaves the softmax warps through SHARED memory instead of TMEM ([128 kv rows][128 query columns] bf16, the
+//     layout of a K tile): read K-major it is the A operand of dK += dS^T Q, read MN-major it is the A operand of
+//     dQ_blk = dS K (K itself, resident, is the MN-major B operand);
+//   * dQ_blk (this KV tile's contribution to one query block) accumulates in the TMEM columns of dP^T, which are free once
+//     the softmax warps hold dP^T in registers; the same warps drain it (query rows on lanes) and add it to an fp32
+//     [H, Tq_pad, 128] accumulator with vector reductions (red.global.add.v4.f32) - contributions of different KV tiles
+//     arrive in no fixed order, so dQ is reproducible only up to fp32 summation order; a small kernel scales and rounds
+//     it to bf16 afterwards (and performs the Ulysses row split);
+//   * the dO ring has ONE stage (dO(i+1) is fetched while S^T(i+1), dQ(i) and dK(i) run) to make room for the dS^T tile.
+// Issue order per block: dV(i), S^T(i+1), dQ(i), dK(i), dP^T(i+1); dK(i) runs while dQ(i) is drained.
+struct BarsF {
+  uint64_t kv_full;
+  uint64_t q_full[STAGES], q_empty[STAGES];      // Q block + its statistics tiles
+  uint64_t d_full, d_empty;                      // the single dO block
+  uint64_t s_full, dp_full, p_full, ds_full;     // one completion per block each: parity = block & 1
+  uint64_t dq_full, dq_free, ds_free;
+  uint64_t acc_done, drain;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int F_SMEM_TILES = 2 * BIG_BYTES + STAGES * (BLK_BYTES + STAT_BYTES) + BLK_BYTES + BLK_BYTES + STAT_TILE;
+constexpr int F_SMEM_TOTAL = F_SMEM_TILES + 256 + 1024;
+static_assert(F_SMEM_TOTAL <= 232448, "fused backward exceeds the shared memory of an SM");
+// the issuing thread of this kernel juggles more descriptors than those of the split kernels
+constexpr int F_REGS_ISSUE = 72, F_REGS_MATH = 216;
+static_assert(128 * F_REGS_ISSUE + 256 * F_REGS_MATH <= NUM_THREADS * REGS_LAUNCH, "setmaxnreg split exceeds the CTA's registers");
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                       const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                       const __grid_constant__ CUtensorMap tmDK, const __grid_constant__ CUtensorMap tmDV,
+                       const uint8_t* __restrict__ stat_tiles, float* __restrict__ dq_acc, int Tq, int Tk, int Tq_pad,
+                       int H, int Hkv, int causal, float scale, int* __restrict__ err,
+                       const __grid_constant__ SplitMaps dk_split, const __grid_constant__ SplitMaps dv_split) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + BIG_BYTES;
+  uint8_t* sQs = smem + 2 * BIG_BYTES;                    // STAGES Q blocks
+  uint8_t* sD = sQs + STAGES * BLK_BYTES;                 // the dO block
+  uint8_t* sDS = sD + BLK_BYTES;                          // dS^T of the current block
+  uint8_t* sStat = sDS + BLK_BYTES;                       // per Q stage: -lse/scale tile | -delta tile
+  uint8_t* sOnes = sStat + STAGES * STAT_BYTES;           // 128 x 16 bf16 ones: the A operand of the statistics step
+  BarsF* bars = (BarsF*)(smem + F_SMEM_TILES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, kvh = blockIdx.y;
+  const int kv0 = kt * BIG;
+  const int G = H / Hkv;
+  const int nq = (Tq + BLK - 1) / BLK;
+  const int i0 = causal ? min(nq, kv0 / BLK) : 0;          // first query block that sees this KV tile
+  const int per_head = nq - i0;
+  const int total = per_head * G;
+  // CTAs that run at the same time work on neighbouring KV tiles of one head.  Were they all to walk the query blocks
+  // in the same order, their dQ reductions would hit the same lines of the accumulator at the same moment and be
+  // serialised by the L2; each CTA therefore starts its walk at a different block (the order is free: dK and dV sum
+  // over all of them).
+  const int rot = per_head > 0 ? (int)(((unsigned)kt * 5u + (unsigned)kvh * 3u) % (unsigned)per_head) : 0;
+  auto q_block = [&](int it) { return i0 + (it % per_head + rot) % per_head; };
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&bars->q_full[s], 1); mbar_init(&bars->q_empty[s], 1); }
+    mbar_init(&bars->d_full, 1); mbar_init(&bars->d_empty, 1);
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->p_full, 256);
+    mbar_init(&bars->ds_full, 256);
+    mbar_init(&bars->dq_full, 1);
+    mbar_init(&bars->dq_free, 256);
+    mbar_init(&bars->ds_free, 1);
+    mbar_init(&bars->acc_done, 1);
+    mbar_init(&bars->drain, 1);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&bars->tmem_base, 512); tmem_relinquish(); }
+  for (int i = threadIdx.x; i < STAT_TILE / 16; i += NUM_THREADS)
+    reinterpret_cast<uint4*>(sOnes)[i] = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+  fence_proxy_async_smem();       // the tensor core reads sOnes through the async proxy
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp < 4) {
+   reg_dec<F_REGS_ISSUE>();
+   if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(&bars->kv_full, 2 * BIG_BYTES);
+      tma_load_3d(sK, &tmK, 0, kvh, kv0, &bars->kv_full);
+      tma_load_3d(sK + BIG_HALF, &tmK, 64, kvh, kv0, &bars->kv_full);
+      tma_load_3d(sV, &tmV, 0, kvh, kv0, &bars->kv_full);
+      tma_load_3d(sV + BIG_HALF, &tmV, 64, kvh, kv0, &bars->kv_full);
+      int issued_q = 0, issued_d = 0;
+      for (int it = 0; it < total; ++it) {
+        const int stage = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        const int head = kvh * G + it / per_head;
+        const int qrow = q_block(it) * BLK;
+        if (!mbar_wait(&bars->q_empty[stage], phase ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        uint8_t* sQ = sQs + stage * BLK_BYTES;
+        mbar_expect_tx(&bars->q_full[stage], BLK_BYTES + STAT_BYTES);
+        tma_load_3d(sQ, &tmQ, 0, head, qrow, &bars->q_full[stage]);
+        tma_load_3d(sQ + BLK_HALF, &tmQ, 64, head, qrow, &bars->q_full[stage]);
+        bulk_load_1d(sStat + stage * STAT_BYTES, stat_tiles + ((int64_t)head * (Tq_pad / BLK) + qrow / BLK) * STAT_BYTES, STAT_BYTES,
+                     &bars->q_full[stage]);
+        ++issued_q;
+        // the single dO slot is released by dV of the block before
+        if (!mbar_wait(&bars->d_empty, (it & 1) ^ 1, abort_flag, err, ODY_ERR_TIMEOUT_EMPTY)) break;
+        mbar_expect_tx(&bars->d_full, BLK_BYTES);
+        tma_load_3d(sD, &tmDO, 0, head, qrow, &bars->d_full);
+        tma_load_3d(sD + BLK_HALF, &tmDO, 64, head, qrow, &bars->d_full);
+        ++issued_d;
+      }
+      if (*abort_flag) {
+        // somebody gave up: let the copies still in flight land before the CTA's shared memory goes away (bounded)
+        const long long t0 = clock64();
+        for (int b = 0; b < 2; ++b) {
+          const int jq = issued_q - 1 - b;
+          while (jq >= 0 && !mbar_try_wait(&bars->q_full[jq % STAGES], (jq / STAGES) & 1) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+        }
+        const int jd = issued_d - 1;
+        while (jd >= 0 && !mbar_try_wait(&bars->d_full, jd & 1) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = make_idesc_bf16(BIG, BLK, 0, 0);      // S^T, dP^T: both operands K-major
+      constexpr uint32_t IDESC_ACC = make_idesc_bf16(BIG, HD, 0, 1);     // dV (A in TMEM), dK (A K-major): B MN-major
+      constexpr uint32_t IDESC_DQ = make_idesc_bf16(BLK, HD, 1, 1);      // dQ_blk: A = dS MN-major, B = K MN-major
+      bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
+      uint64_t kdesc0 = make_smem_desc(smem_u32(sK), 16, 1024), vdesc0 = make_smem_desc(smem_u32(sV), 16, 1024);
+      uint64_t k_mn = make_smem_desc(smem_u32(sK), BIG_HALF, 1024);
+      uint64_t q_k0 = make_smem_desc(smem_u32(sQs), 16, 1024), d_k = make_smem_desc(smem_u32(sD), 16, 1024);
+      uint64_t q_mn0 = make_smem_desc(smem_u32(sQs), BLK_HALF, 1024), d_mn = make_smem_desc(smem_u32(sD), BLK_HALF, 1024);
+      uint64_t ds_k = make_smem_desc(smem_u32(sDS), 16, 1024), ds_mn = make_smem_desc(smem_u32(sDS), BLK_HALF, 1024);
+      const uint64_t ones_d = make_smem_desc_noswizzle(smem_u32(sOnes), 128, 256);
+      const uint64_t stat_d0 = make_smem_desc_noswizzle(smem_u32(sStat), 128, 256);
+      // Nine descriptor bases times eight slice offsets each are loop invariants the compiler would rather keep in
+      // ~110 registers than recompute with one add per MMA; this thread has no such room.  Passing the bases through
+      // an empty asm each iteration makes them opaque, so the sums are formed where they are used.
+      auto opaque = [&]() {
+        asm volatile("" : "+l"(kdesc0), "+l"(vdesc0), "+l"(k_mn), "+l"(q_k0), "+l"(d_k), "+l"(q_mn0), "+l"(d_mn), "+l"(ds_k), "+l"(ds_mn));
+      };
+      // S^T(it) = K Q^T - lse / scale (per query column): waits for the Q block
+      auto issue_s = [&](int it) -> bool {
+        const int stage = it % STAGES;
+        if (!mbar_wait(&bars->q_full[stage], (it / STAGES) & 1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+        const uint64_t qd = desc_advance(q_k0, stage * BLK_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+          umma_ss(tmem + COL_ST, desc_advance(kdesc0, off), desc_advance(qd, off), IDESC_S, kk > 0 ? 1u : 0u);
+        }
+        umma_ss(tmem + COL_ST, ones_d, desc_advance(stat_d0, stage * STAT_BYTES), IDESC_S, 1u);
+        umma_commit(&bars->s_full);
+        return true;
+      };
+      // dP^T(it) = V dO^T - delta: waits for the dO block (its statistics tile came with the Q block)
+      auto issue_dp = [&](int it) -> bool {
+        const int stage = it % STAGES;
+        if (!mbar_wait(&bars->d_full, it & 1, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
+          umma_ss(tmem + COL_DPT, desc_advance(vdesc0, off), desc_advance(d_k, off), IDESC_S, kk > 0 ? 1u : 0u);
+        }
+        umma_ss(tmem + COL_DPT, ones_d, desc_advance(stat_d0, stage * STAT_BYTES + STAT_TILE), IDESC_S, 1u);
+        umma_commit(&bars->dp_full);
+        return true;
+      };
+      if (ok && total > 0) ok = issue_s(0) && issue_dp(0);
+      for (int it = 0; it < total && ok; ++it) {
+        const int stage = it % STAGES;
+        const uint32_t par = it & 1;
+        const uint32_t acc0 = it > 0 ? 1u : 0u;
+        opaque();
+        if (!mbar_wait(&bars->p_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk)      // dV += P^T dO
+          umma_ts(tmem + COL_DV, tmem + COL_ST + kk * 8, desc_advance(d_mn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        umma_commit(&bars->d_empty);               // dO(it) is free: the producer fetches dO(it+1)
+        if (it + 1 < total && !issue_s(it + 1)) { ok = false; break; }
+        if (!mbar_wait(&bars->ds_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BIG / 16; ++kk)      // dQ_blk = dS K   (k runs over the 128 kv rows)
+          umma_ss(tmem + COL_DPT, desc_advance(ds_mn, kk * 2048), desc_advance(k_mn, kk * 2048), IDESC_DQ, kk > 0 ? 1u : 0u);
+        umma_commit(&bars->dq_full);
+        const uint64_t qmn = desc_advance(q_mn0, stage * BLK_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk) {    // dK += dS^T Q   (k runs over the 128 query rows)
+          const uint32_t off = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
+          umma_ss(tmem + COL_DK, desc_advance(ds_k, off), desc_advance(qmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        }
+        umma_commit(&bars->q_empty[stage]);
+        umma_commit(&bars->ds_free);               // the dS^T tile may be overwritten
+        if (it + 1 < total) {
+          // dP^T(it+1) lands where dQ_blk(it) sits: the softmax warps must have drained it
+          if (!mbar_wait(&bars->dq_free, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          if (!issue_dp(it + 1)) { ok = false; break; }
+        }
+      }
+      if (ok) umma_commit(&bars->acc_done);
+      else {
+        umma_commit(&bars->drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
+      }
+    }
+   }
+  } else {
+    reg_inc<F_REGS_MATH>();
+    const int q = warp & 3;                               // TMEM lane quarter
+    const int hf = (warp - 4) >> 2;                       // which 64 of 128 columns this warp handles
+    const int r = q * 32 + lane;                          // TMEM lane: kv row for S^T / dP^T, query row for dQ_blk
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const float sl2 = scale * LOG2E;
+    const uint64_t sl2_2 = pk2(sl2, sl2);
+    bool ok = true;
+    // dQ_blk(it) -> fp32 accumulator; this thread: query row r of the block, head-dim columns [hf * 64, hf * 64 + 64)
+    auto drain_dq = [&](int it) -> bool {
+      if (!ok) return false;
+      bool good = __all_sync(0xffffffffu, mbar_wait(&bars->dq_full, it & 1, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      if (!good) return false;
+      tc_fence_after();
+      const int head = kvh * G + it / per_head;
+      const int qrow = q_block(it) * BLK + r;     // < Tq_pad: the accumulator has padded rows
+      float* dst = dq_acc + ((int64_t)head * Tq_pad + qrow) * HD + hf * 64;
+      // two passes of 32 columns: the P values of part 1 stay in registers across this call
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t a[32];
+        tmem_ld_32x32(tmem + COL_DPT + hf * 64 + half * 32 + lane_off, a);
+        tmem_ld_wait();
+        if (half == 1) {
+          tc_fence_before();
+          mbar_arrive(&bars->dq_free);                     // dQ_blk is out of TMEM: dP^T of the next block may land there
+        }
+#ifndef ODY_BWD_NO_RED
+        // Each thread holds 32 consecutive floats (one 128-byte line) of its own row.  Written as they are, one
+        // instruction would touch 32 different lines with 16 bytes each; an 8 x 8 transpose of the 16-byte chunks
+        // inside every group of 8 lanes (three butterfly steps of shuffles) makes instruction c write the whole
+        // line of row 8 * group + c from 8 neighbouring lanes instead: 4 full lines per instruction.
+        {
+          const int li = lane & 7;
+#pragma unroll
+          for (int sft = 1; sft < 8; sft <<= 1) {
+            const bool upper = (li & sft) != 0;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              if (c & sft) continue;
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const uint32_t send = upper ? a[4 * c + w] : a[4 * (c ^ sft) + w];
+                const uint32_t got = __shfl_xor_sync(0xffffffffu, send, sft);
+                if (upper) a[4 * c + w] = got; else a[4 * (c ^ sft) + w] = got;
+              }
+            }
+          }
+          float* line0 = dst - (int64_t)li * HD + half * 32 + 4 * li;     // row 8 * group, this lane's 16-byte chunk of it
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            red_add_v4(line0 + (int64_t)c * HD, __uint_as_float(a[4 * c]), __uint_as_float(a[4 * c + 1]),
+                       __uint_as_float(a[4 * c + 2]), __uint_as_float(a[4 * c + 3]));
+        }
+#else
+        if (a[0] == 0x7fc12345u) dst[0] = 1.f;     // timing experiment: keep the loads alive, skip the reductions
+#endif
+      }
+      return true;
+    };
+    // `ok` is warp-uniform.  The loop is left only at the pair barrier of part 1, where the two warps of a lane quarter
+    // agree on it: a warp that has seen a wait give up skips the rest of its iteration and says so there.
+    for (int it = 0; it < total; ++it) {
+      const uint32_t par = it & 1;
+      const int qrow0 = q_block(it) * BLK + hf * 64;
+      // ---- part 1: S^T -> P^T (TMEM)
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->s_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      uint32_t sv[64];
+      if (ok) {
+        tc_fence_after();
+        tmem_ld_32x32(tmem + COL_ST + hf * 64 + lane_off, sv);
+        tmem_ld_32x32(tmem + COL_ST + hf * 64 + 32 + lane_off, sv + 32);
+        tmem_ld_wait();
+      }
+      // P^T is written over the first 64 columns of S^T: the other warp of this lane quarter must have read
+      // its inputs before either of us stores
+      if (!named_barrier_and(4 + q, 64, ok)) { ok = false; break; }
+      const bool diag = causal && (qrow0 < kv0 + BIG);     // some (q, kv) pairs of this half block are masked
+      {
+        uint32_t pp[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const uint64_t x2 = mul2(pk2u(sv[2 * c], sv[2 * c + 1]), sl2_2);
+          float p0, p1;
+          upk2(x2, p0, p1);
+          p0 = exp2_mufu(p0);
+          p1 = exp2_mufu(p1);
+          if (diag) {
+            if (qrow0 + 2 * c < kv0 + r) p0 = 0.f;
+            if (qrow0 + 2 * c + 1 < kv0 + r) p1 = 0.f;
+          }
+          sv[2 * c] = __float_as_uint(p0);
+          sv[2 * c + 1] = __float_as_uint(p1);
+          pp[c] = pack_bf16(p0, p1);
+        }
+        tmem_st_32x16(tmem + COL_ST + hf * 32 + lane_off, pp);
+        tmem_st_32x16(tmem + COL_ST + hf * 32 + 16 + lane_off, pp + 16);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full);
+      }
+      // ---- dQ_blk of the block before: its MMAs ran while part 1 was computed
+      if (it > 0) ok = drain_dq(it - 1);
+      // ---- part 2: dP^T -> dS^T = P^T * (dP^T - delta) -> shared memory
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->dp_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL));
+      uint32_t dp[64];
+      if (ok) {
+        tc_fence_after();
+        tmem_ld_32x32(tmem + COL_DPT + hf * 64 + lane_off, dp);
+        tmem_ld_32x32(tmem + COL_DPT + hf * 64 + 32 + lane_off, dp + 32);
+        tmem_ld_wait();
+      }
+      // the tile still holds dS^T of the block before until dQ and dK of that block have read it
+      if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars->ds_free, (it - 1) & 1, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
+      if (ok) {
+        uint8_t* row = sDS + hf * BLK_HALF + r * 128;      // kv row r, query columns [hf * 64, hf * 64 + 64): one swizzled 128-byte row
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          uint32_t w[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const int c = g * 4 + t;
+            float d0, d1;
+            upk2(mul2(pk2u(sv[2 * c], sv[2 * c + 1]), pk2u(dp[2 * c], dp[2 * c + 1])), d0, d1);
+            w[t] = pack_bf16(d0, d1);
+          }
+          *reinterpret_cast<uint4*>(row + ((g ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        fence_proxy_async_smem();                           // the tensor core reads the tile through the async proxy
+        tc_fence_before();                                  // and dP^T is in registers: its columns may take dQ_blk
+        mbar_arrive(&bars->ds_full);
+      }
+    }
+    if (ok && total > 0) ok = drain_dq(total - 1);
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->acc_done, 0, abort_flag, err, ODY_ERR_TIMEOUT_MISC));
+    if (ok) {
+      tc_fence_after();
+      // dV -> sV region, dK -> sK region (both dead now), bf16, swizzled for the TMA store
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        uint8_t* dst = (which == 0 ? sV : sK) + hf * BIG_HALF;
+        const uint32_t col = (which == 0 ? COL_DV : COL_DK) + hf * 64;
+        const float mult = which == 0 ? 1.f : scale;       // dK = scale * dS^T Q
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[16];
+          tmem_ld_32x16(tmem + col + lane_off + c * 16, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int t = 0; t < 16; ++t) o[t] = __float_as_uint(__uint_as_float(o[t]) * mult);
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            uint4 v4;
+            v4.x = pack_bf16(__uint_as_float(o[8 * t + 0]), __uint_as_float(o[8 * t + 1]));
+            v4.y = pack_bf16(__uint_as_float(o[8 * t + 2]), __uint_as_float(o[8 * t + 3]));
+            v4.z = pack_bf16(__uint_as_float(o[8 * t + 4]), __uint_as_float(o[8 * t + 5]));
+            v4.w = pack_bf16(__uint_as_float(o[8 * t + 6]), __uint_as_float(o[8 * t + 7]));
+            const int chunk = c * 2 + t;
+            *reinterpret_cast<uint4*>(dst + r * 128 + ((chunk ^ (r & 7)) << 4)) = v4;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+    }
+    tc_fence_before();
+    named_barrier(1, 256);
+    if (ok && warp == 4 && lane == 0 && !*abort_flag) {
+      const int d = dk_split.rows > 0 ? kv0 / dk_split.rows : 0;
+      const int row = dk_split.rows > 0 ? kv0 - d * dk_split.rows : kv0;
+      const CUtensorMap* mV = dk_split.rows > 0 ? &dv_split.m[d] : &tmDV;
+      const CUtensorMap* mK = dk_split.rows > 0 ? &dk_split.m[d] : &tmDK;
+      tma_store_3d(mV, sV, 0, kvh, row);
+      tma_store_3d(mV, sV + BIG_HALF, 64, kvh, row);
+      tma_store_3d(mK, sK, 0, kvh, row);
+      tma_store_3d(mK, sK + BIG_HALF, 64, kvh, row);
+      tma_store_commit();
+      tma_store_wait<0>();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// dq [Tq, H, 128] bf16 (row pitch dq_row) = scale * acc [H, Tq_pad, 128]; with split_rows > 0 the rows go, in groups of
+// split_rows, to dq_split.p[d] instead (possibly peer memory: plain 16-byte stores).
+struct DqDests { __nv_bfloat16* p[8]; };
+__global__ void dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, const __grid_constant__ DqDests split,
+                                  int split_rows, int64_t dq_row, int Tq, int Tq_pad, int H, float scale) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;      // one thread per 8 elements
+  const int64_t total = (int64_t)Tq * H * (HD / 8);
+  if (idx >= total) return;
+  const int c8 = (int)(idx % (HD / 8));
+  const int h = (int)((idx / (HD / 8)) % H);
+  const int t = (int)(idx / ((int64_t)(HD / 8) * H));
+  const float* src = acc + ((int64_t)h * Tq_pad + t) * HD + c8 * 8;
+  const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+  uint4 o;
+  o.x = pack_bf16(a.x * scale, a.y * scale);
+  o.y = pack_bf16(a.z * scale, a.w * scale);
+  o.z = pack_bf16(b.x * scale, b.y * scale);
+  o.w = pack_bf16(b.z * scale, b.w * scale);
+  __nv_bfloat16* base = dq;
+  int row = t;
+  if (split_rows > 0) {
+    const int d = t / split_rows;
+    base = split.p[d];
+    row = t - d * split_rows;
+  }
+  *reinterpret_cast<uint4*>(base + (int64_t)row * dq_row + h * HD + c8 * 8) = o;
+}
+
 // ------------------------------------------------------------------------------------------- dQ
 // Q and dO of the tile are the A operands of every S = Q K^T and dP = dO V^T of the kernel, so they live in TMEM (bf16,
 // 64 columns each, written once by the softmax warps straight from global memory) and all 24 MMAs of a block are of the
@@ -726,9 +1164,20 @@ static long long* g_bwd_trace = nullptr;
 // Optional per-block timeline of CTA (0,0) of the dK/dV kernel: 48 x 8 SM-clock stamps (see the kernel).
 extern "C" void ody_flash_bwd_set_trace(long long* buf) { g_bwd_trace = buf; }
 
+static int g_bwd_variant = 1;
+// 1 (default): the split pair (dK/dV kernel + dQ kernel: seven products per block pair, no atomics, bitwise
+// reproducible); 0: the fused dK/dV/dQ kernel (five products; dQ summed over KV tiles with fp32 reductions in no fixed
+// order - at present the reduction traffic, not the tensor core, bounds it, and the split pair is the faster one)
+extern "C" int ody_flash_bwd_set_variant(int v) {
+  if (v < 0 || v > 1) return (int)cudaErrorInvalidValue;
+  g_bwd_variant = v;
+  return 0;
+}
+
 extern "C" int64_t ody_flash_bwd_workspace_bytes(int Tq, int H) {
   const int64_t Tpad = ((int64_t)Tq + 127) / 128 * 128;
-  return 2 * (int64_t)H * Tpad * 4 + (int64_t)H * (Tpad / 128) * ody::bwd::STAT_BYTES;
+  // -delta and exp2-domain -lse (padded), the statistics tiles, and the fp32 dQ accumulator of the fused kernel
+  return 2 * (int64_t)H * Tpad * 4 + (int64_t)H * (Tpad / 128) * ody::bwd::STAT_BYTES + (int64_t)H * Tpad * ody::bwd::HD * 4;
 }
 
 // workspace: ody_flash_bwd_workspace_bytes(Tq, H) bytes, 16-byte aligned (delta and exp2-domain LSE, padded).
@@ -781,6 +1230,8 @@ extern "C" int ody_flash_bwd_ex(const void* dO, const void* q, const void* k, co
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_TOTAL);
     if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(flash_bwd_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM_TOTAL);
+    if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int Tpad = (Tq + 127) / 128 * 128;
@@ -804,6 +1255,20 @@ extern "C" int ody_flash_bwd_ex(const void* dO, const void* q, const void* k, co
   if ((r = make_tmap_3d_bf16(&tDK, dk, HD, Hkv, Tk, HD * 2, dk_row * 2, 64, 1, BIG))) return 790000 + r;
   if ((r = make_tmap_3d_bf16(&tDV, dv, HD, Hkv, Tk, HD * 2, dv_row * 2, 64, 1, BIG))) return 790000 + r;
   dim3 gkv((Tk + BIG - 1) / BIG, Hkv);
+  if (g_bwd_variant == 0) {
+    float* dq_acc = (float*)(stat_tiles + (int64_t)H * (Tpad / BLK) * STAT_BYTES);
+    cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)H * Tpad * HD * sizeof(float), st);
+    if (e != cudaSuccess) return (int)e;
+    flash_bwd_fused_kernel<<<gkv, NUM_THREADS, F_SMEM_TOTAL, st>>>(tQ, tDO, tK, tV, tDK, tDV, stat_tiles, dq_acc, Tq, Tk, Tpad, H, Hkv,
+                                                                   causal, scale, err, sk, sv);
+    DqDests dd;
+    memset(&dd, 0, sizeof(dd));
+    for (int d = 0; d < n_split; ++d) dd.p[d] = (__nv_bfloat16*)dq_split[d];
+    const int64_t items = (int64_t)Tq * H * (HD / 8);
+    dq_convert_kernel<<<(unsigned)((items + 255) / 256), 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dq, dd, n_split > 0 ? split_rows : 0,
+                                                                        dq_row, Tq, Tpad, H, scale);
+    return (int)cudaGetLastError();
+  }
   flash_bwd_dkdv_kernel<<<gkv, NUM_THREADS, KV_SMEM_TOTAL, st>>>(tQ, tDO, tK, tV, tDK, tDV, stat_tiles, Tq, Tk,
                                                                  Tpad, H, Hkv, causal, scale, err, g_bwd_trace, sk, sv);
   dim3 gq((Tq + BIG - 1) / BIG, H);

@@ -73,6 +73,8 @@ int ody_flash_fwd(const void* q, const void* k, const void* v, void* o, float* l
 // ---- attention backward.  workspace: ody_flash_bwd_workspace_bytes(Tq, H) bytes of scratch, 16-byte aligned.
 // dq/dk/dv may be row-pitched views (e.g. slices of one packed gradient tensor).
 int64_t ody_flash_bwd_workspace_bytes(int Tq, int H);
+/* 1 (default): dK/dV kernel + dQ kernel, no atomics; 0: one fused dK/dV/dQ kernel, dQ summed with fp32 reductions */
+int ody_flash_bwd_set_variant(int variant);
 /* CTAs of the forward grid (one per 256 query rows and head): the upper bound of a push description's n_cta */
 int ody_flash_fwd_ctas(int Tq, int H);
 /* 1: the forward keeps its Q / K tiles as eight 32-byte-swizzled slices, 0: as two 128-byte-swizzled halves */

@@ -353,8 +353,16 @@ def test_attention_fwd_packed_views(lib):
     torch.testing.assert_close(o.float(), orf.float(), rtol=3e-2, atol=3e-2)
 
 
+@pytest.fixture(params=[0, 1], ids=["fused_dq", "split_dq"])
+def bwd_variant(request, lib):
+    """The fused dK/dV/dQ backward kernel and the split pair (dK/dV kernel + dQ kernel)."""
+    lib.attn_bwd_set_variant(request.param)
+    yield request.param
+    lib.attn_bwd_set_variant(1)
+
+
 @pytest.mark.parametrize("Tq,Tk,H,Hkv,causal", ATTN_CASES)
-def test_attention_bwd(lib, Tq, Tk, H, Hkv, causal):
+def test_attention_bwd(lib, bwd_variant, Tq, Tk, H, Hkv, causal):
     from odysseus_transformer_b200.ops import torch_ref as R
     torch.manual_seed(Tq * 3 + Tk + H)
     q, k, v = _rand(Tq, H, 128), _rand(Tk, Hkv, 128), _rand(Tk, Hkv, 128)
@@ -370,7 +378,7 @@ def test_attention_bwd(lib, Tq, Tk, H, Hkv, causal):
         torch.testing.assert_close(a.float(), b, rtol=5e-2, atol=5e-2 * b.abs().max().item(), msg=lambda m: f"{name}: {m}")
 
 
-def test_attention_bwd_packed_outputs(lib):
+def test_attention_bwd_packed_outputs(lib, bwd_variant):
     """Gradients written straight into slices of one packed [T, hq+2hkv, 128] tensor."""
     from odysseus_transformer_b200.ops import torch_ref as R
     T, hq, hkv = 512, 4, 2
