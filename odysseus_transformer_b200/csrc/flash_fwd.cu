@@ -16,7 +16,8 @@
 //     P in 32-key pieces so that P V could start early measured slower: four store waits instead of one);
 //   * two softmax warpgroups, one thread per query row: 128 scores straight from TMEM, no exchange between
 //     threads, exp2 domain, lazy rescaling of O (the running maximum used for exponentiation only moves when
-//     it would grow by more than 2^8, so the O read-modify-write is rare).  A tcgen05.commit after Q K^T of
+//     it would grow by more than 2^8, so the O read-modify-write is rare) - and because that maximum is known
+//     before the block arrives, the exponentials start at once and the block's own maximum is found on the side.  A tcgen05.commit after Q K^T of
 //     block j also covers P V of block j-1, so a thread that sees S(j) may touch O without another barrier.
 //
 // q [Tq, H, 128], k/v [Tk, Hkv, 128] with arbitrary row pitch; out [Tq, H, 128] bf16; lse [H, Tq] fp32
@@ -198,9 +199,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0) {
         constexpr uint32_t IDESC_QK = make_idesc_bf16(BM, BN, 0, 0);
         constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
-        const uint64_t qdesc0 = KS32 ? make_smem_desc_sw32(smem_u32(sQ)) : make_smem_desc(smem_u32(sQ), 16, 1024);
-        const uint64_t kdesc0 = KS32 ? make_smem_desc_sw32(smem_u32(sK)) : make_smem_desc(smem_u32(sK), 16, 1024);
-        const uint64_t vdesc0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
+        uint64_t qdesc0 = KS32 ? make_smem_desc_sw32(smem_u32(sQ)) : make_smem_desc(smem_u32(sQ), 16, 1024);
+        uint64_t kdesc0 = KS32 ? make_smem_desc_sw32(smem_u32(sK)) : make_smem_desc(smem_u32(sK), 16, 1024);
+        uint64_t vdesc0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
         bool ok = true;
         // S_t = Q_t K(j)^T
         auto issue_qk = [&](int t, int j) {
@@ -236,6 +237,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_commit(&bars->k_empty[0]);
         }
         for (int j = 0; j < nblk && ok; ++j) {
+          // keep the descriptor bases opaque: the compiler would otherwise hold every base + slice offset of the loop
+          // in registers this thread does not have, instead of one add per MMA
+          asm volatile("" : "+l"(qdesc0), "+l"(kdesc0), "+l"(vdesc0));
           const int s = j & 1, s1 = (j + 1) & 1;
           const uint32_t ph = (j >> 1) & 1, ph1 = ((j + 1) >> 1) & 1;
           bool have_v = false, have_k1 = false;
@@ -313,61 +317,76 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 0; c < 128; ++c)
           if (kv0 + c >= Tk) sv[c] = 0xff800000u;
       }
-      // row maximum, four independent chains
-      float mx[4];
+      // One pass over the 128 scores: exponentials against the maximum in use (packed pairs, x = s * scale * log2(e) - m),
+      // P back over S in four 32-column pieces, the row sum, and - on the side, off the dependent chain - the row maximum
+      // of THIS block.  The maximum in use only has to be within 2^8 of the true one, so the common case needs no
+      // separate maximum pass in front of the exponentials; a block that moves it further is redone (rare).
+      const uint64_t sl2_2 = pk2(sl2, sl2);
+      float rsum, rmax;
+      auto exp_pass = [&]() {
+        const uint64_t nm_2 = pk2(-m_used, -m_used);
+        uint64_t rs2 = pk2(0.f, 0.f);
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) mx[i] = __uint_as_float(sv[i]);
+        for (int g = 0; g < 4; ++g) {
+          uint32_t pk[16];
 #pragma unroll
-      for (int c = 4; c < 128; c += 4) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) mx[i] = fmaxf(mx[i], __uint_as_float(sv[c + i]));
-      }
-      const float rmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      const float m_new = fmaxf(m_used, rmax * sl2);
-      const bool need = (m_new - m_used) > 8.f;        // true on the first block (m_used = -inf)
-      if (j == 0) {
-        m_used = m_new;
-      } else if (__any_sync(0xffffffffu, need)) {
-        // the running maximum moved by more than 2^8 for some row of this warp: rescale O and l.  P V of block j-1
-        // completed before S(j) was announced and P V of block j waits for this thread, so O is ours now.
-        const float alpha = need ? exp2_mufu(m_used - m_new) : 1.f;
-        if (need) m_used = m_new;
-        l *= alpha;
-#pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
-          uint32_t o[16];
-          tmem_ld_32x16(col_o + c * 16, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x16(col_o + c * 16, o);
+          for (int c = 0; c < 16; ++c) {
+            float p0, p1;
+            const uint32_t s0 = sv[32 * g + 2 * c], s1 = sv[32 * g + 2 * c + 1];
+            mx[c & 1] = fmaxf(mx[c & 1], __uint_as_float(s0));
+            mx[2 + (c & 1)] = fmaxf(mx[2 + (c & 1)], __uint_as_float(s1));
+            const uint64_t x2 = fma2(pk2u(s0, s1), sl2_2, nm_2);
+            upk2(x2, p0, p1);
+            p0 = exp2_mufu(p0);
+            p1 = exp2_mufu(p1);
+            rs2 = add2(rs2, pk2(p0, p1));
+            pk[c] = pack_bf16(p0, p1);
+          }
+          tmem_st_32x16(col_s + g * 16, pk);
         }
-      }
-      ODY_FWD_STAMP(tr, j, t * 5 + 3);
-      // packed pairs: x = s * scale * log2(e) - m for two columns per instruction; P goes back over S in four
-      // 32-column pieces (16 packed registers each)
-      const uint64_t sl2_2 = pk2(sl2, sl2), nm_2 = pk2(-m_used, -m_used);
-      uint64_t rs2 = pk2(0.f, 0.f);
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          float p0, p1;
-          const uint64_t x2 = fma2(pk2u(sv[32 * g + 2 * c], sv[32 * g + 2 * c + 1]), sl2_2, nm_2);
-          upk2(x2, p0, p1);
-          p0 = exp2_mufu(p0);
-          p1 = exp2_mufu(p1);
-          rs2 = add2(rs2, pk2(p0, p1));
-          pk[c] = pack_bf16(p0, p1);
-        }
-        tmem_st_32x16(col_s + g * 16, pk);
-      }
-      {
         float r0, r1;
         upk2(rs2, r0, r1);
-        l += r0 + r1;
+        rsum = r0 + r1;
+        rmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      };
+      if (j == 0) {
+        // first block: there is no maximum in use yet
+        float mx[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx[i] = __uint_as_float(sv[i]);
+#pragma unroll
+        for (int c = 4; c < 128; c += 4) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) mx[i] = fmaxf(mx[i], __uint_as_float(sv[c + i]));
+        }
+        m_used = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sl2;
+        ODY_FWD_STAMP(tr, j, t * 5 + 3);
+        exp_pass();
+      } else {
+        ODY_FWD_STAMP(tr, j, t * 5 + 3);
+        exp_pass();
+        const float m_new = fmaxf(m_used, rmax * sl2);
+        const bool need = (m_new - m_used) > 8.f;
+        if (__any_sync(0xffffffffu, need)) {
+          // the running maximum moved by more than 2^8 for some row of this warp: rescale O and l, redo the block.
+          // P V of block j-1 completed before S(j) was announced and P V of block j waits for this thread, so O is ours.
+          const float alpha = need ? exp2_mufu(m_used - m_new) : 1.f;
+          if (need) m_used = m_new;
+          l *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t o[16];
+            tmem_ld_32x16(col_o + c * 16, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(col_o + c * 16, o);
+          }
+          exp_pass();
+        }
       }
+      l += rsum;
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars->p_full[t]);
