@@ -49,7 +49,8 @@ def build(verbose: bool = False, force: bool = False) -> str:
         name="_C", sources=sources(), extra_cflags=["-O3", "-std=c++17"], extra_cuda_cflags=NVCC_FLAGS,
         extra_ldflags=["-lcuda"] if False else [], build_directory=BUILD, verbose=verbose, is_python_module=False)
     built = os.path.join(BUILD, "_C.so")
-    shutil.copyfile(built, target)
+    shutil.copyfile(built, target + ".tmp")
+    os.replace(target + ".tmp", target)      # readers of the tree never see a half-written library
     with open(stamp_file, "w") as f:
         f.write(stamp)
     return target

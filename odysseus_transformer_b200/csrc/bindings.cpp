@@ -12,6 +12,7 @@
 #include <mutex>
 
 #include "ody_kernels.h"
+#include "epilogue_arg.h"
 
 namespace {
 
@@ -62,7 +63,7 @@ void check_bf16(const at::Tensor& t, const char* name) {
 
 // ------------------------------------------------------------------------------------------- GEMM
 at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& out, int64_t layout,
-                bool accumulate) {
+                bool accumulate, const py::object& rope, const c10::optional<at::Tensor>& residual) {
   check_bf16(a, "a");
   check_bf16(b, "b");
   ody_req(a.dim() == 2 && b.dim() == 2, "gemm expects 2-D operands");
@@ -77,9 +78,15 @@ at::Tensor gemm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at
   ody_req(c.dim() == 2 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1, "bad out shape");
   ody_req(!accumulate || out.has_value(), "accumulate needs out");
   if (M == 0 || N == 0) return c;
+  OdyEpilogue epi;
+  const bool has_epi = ody_epi::fill(rope, residual, M, M, N, a.device(), epi);
+  ody_req(!has_epi || K > 0, "gemm: an epilogue needs K > 0");
+  ody_req(!(accumulate && residual.has_value()), "gemm: accumulate and residual exclude each other");
+  ody_req(rope.is_none() || layout == 0, "gemm: the rotary epilogue belongs to layout 0 (a forward projection)");
   if (K == 0) { if (!accumulate) c.zero_(); return c; }
-  ODY_CHECK(ody_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
-                          c.stride(0), (int)layout, accumulate ? 1 : 0, status_ptr(a), cur_stream()),
+  ODY_CHECK(ody_gemm_bf16_ex(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                             c.stride(0), (int)layout, accumulate ? 1 : 0, has_epi ? &epi : nullptr, status_ptr(a),
+                             cur_stream()),
             "gemm");
   ++g_launches;
   return c;
@@ -166,6 +173,29 @@ void rope_inplace_(at::Tensor x, int64_t n_rot, const at::Tensor& cos, const at:
   c10::cuda::CUDAGuard guard(x.device());
   ODY_CHECK(ody_rope_inplace(x.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), x.size(0), (int)n_rot,
                              (int)x.size(2), x.stride(0), inverse ? 1 : 0, cur_stream()), "rope_inplace");
+  ++g_launches;
+}
+
+// src [T, heads, hd] -> dst [T, heads, hd] (src may be dst): heads in groups of `period` (0 = one group of all heads), the
+// first n_rot of each group rotated, the rest copied when dst is another tensor.  Rows may be strided, heads packed.
+void rope_grouped_(const at::Tensor& src, at::Tensor dst, int64_t n_rot, int64_t period, const at::Tensor& cos,
+                   const at::Tensor& sin, bool inverse) {
+  check_bf16(src, "src");
+  check_bf16(dst, "dst");
+  ody_req(src.dim() == 3 && src.stride(2) == 1 && src.stride(1) == src.size(2), "rope: src must be [T, heads, hd] with packed heads");
+  ody_req(dst.dim() == 3 && dst.stride(2) == 1 && dst.stride(1) == dst.size(2), "rope: dst must be [T, heads, hd] with packed heads");
+  ody_req(src.sizes() == dst.sizes() && src.device() == dst.device(), "rope: src and dst differ in shape or device");
+  ody_req(cos.is_contiguous() && sin.is_contiguous() && cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat,
+          "rope tables: fp32 contiguous");
+  ody_req(cos.size(0) == src.size(0) && cos.size(1) * 2 == src.size(2) && sin.sizes() == cos.sizes(), "rope tables shape");
+  ody_req(cos.device() == src.device() && sin.device() == src.device(), "rope tables on another device");
+  const int64_t per = period > 0 ? period : src.size(1);
+  ody_req(per > 0 && src.size(1) % per == 0 && n_rot >= 0 && n_rot <= per, "rope: heads, period and n_rot disagree");
+  ody_req((((uintptr_t)src.data_ptr()) & 15) == 0 && (((uintptr_t)dst.data_ptr()) & 15) == 0, "rope: 16-byte aligned tensors");
+  c10::cuda::CUDAGuard dev_guard(src.device());
+  ODY_CHECK(ody_rope(src.data_ptr(), dst.data_ptr(), cos.data_ptr<float>(), sin.data_ptr<float>(), src.size(0),
+                     (int)src.size(1), (int)per, (int)n_rot, (int)src.size(2), src.stride(0), dst.stride(0),
+                     inverse ? 1 : 0, cur_stream()), "rope");
   ++g_launches;
 }
 
@@ -340,13 +370,14 @@ void ody_register_comm(pybind11::module& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("out") = py::none(), py::arg("layout") = 0,
-        py::arg("accumulate") = false);
+        py::arg("accumulate") = false, py::arg("rope") = py::none(), py::arg("residual") = py::none());
   m.def("gemm_set_variant", [](int64_t v) { ODY_CHECK(ody_gemm_set_variant((int)v), "gemm_set_variant (0 auto, 1 one CTA, 2 CTA pairs)"); });
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope_tables", &rope_tables);
   m.def("rope_inplace_", &rope_inplace_);
+  m.def("rope_grouped_", &rope_grouped_);
   m.def("rope_apply", &rope_apply);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);

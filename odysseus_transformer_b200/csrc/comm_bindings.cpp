@@ -7,6 +7,7 @@
 #include <string>
 
 #include "ody_kernels.h"
+#include "epilogue_arg.h"
 namespace py = pybind11;
 
 int* ody_status_ptr(const at::Tensor& like);
@@ -136,7 +137,8 @@ void signal_flags(const at::Tensor& like, const std::vector<int64_t>& ptrs, int6
 }
 
 at::Tensor gemm_comm(const at::Tensor& a, const at::Tensor& b, const c10::optional<at::Tensor>& out, int64_t layout,
-                     const py::object& gather, const py::object& push, const py::object& scatter) {
+                     const py::object& gather, const py::object& push, const py::object& scatter, const py::object& rope,
+                     const c10::optional<at::Tensor>& residual) {
   req(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "bf16 CUDA operands");
   req(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "row-major 2-D operands");
   c10::cuda::CUDAGuard guard(a.device());
@@ -188,8 +190,14 @@ at::Tensor gemm_comm(const at::Tensor& a, const at::Tensor& b, const c10::option
     req(c.dim() == 2 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1 && c.scalar_type() == at::kBFloat16, "bad out");
   }
   req(gdp != nullptr || sdp != nullptr, "gemm_comm needs a gather or a scatter description");
-  int rc = ody_gemm_comm(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
-                         c.stride(0), (int)layout, gdp, pdp, sdp, ody_status_ptr(a), at::cuda::getCurrentCUDAStream().stream());
+  OdyEpilogue epi;
+  const bool reduces = sdp != nullptr && sd.mode != 2;
+  req(rope.is_none() || (!reduces && layout == 0), "gemm_comm: the rotary epilogue belongs to a layout-0 product that is not reduced");
+  req(!residual.has_value() || sdp == nullptr || reduces, "gemm_comm: no residual in the all-to-all epilogue");
+  const bool has_epi = ody_epi::fill(rope, residual, M, reduces ? sd.chunk_rows : M, N, a.device(), epi);
+  int rc = ody_gemm_comm_ex(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                            c.stride(0), (int)layout, gdp, pdp, sdp, has_epi ? &epi : nullptr, ody_status_ptr(a),
+                            at::cuda::getCurrentCUDAStream().stream());
   req(rc == 0, "gemm_comm failed with code " + std::to_string(rc));
   ody_count_launches(1);
   return c;
@@ -226,5 +234,5 @@ void ody_register_comm(pybind11::module& m) {
   });
   m.def("set_peer_wait_limit", [](int64_t cycles) { req(ody_set_peer_wait_limit(cycles) == 0, "set_peer_wait_limit failed"); });
   m.def("gemm_comm", &gemm_comm, py::arg("a"), py::arg("b"), py::arg("out"), py::arg("layout"), py::arg("gather"),
-        py::arg("push"), py::arg("scatter"));
+        py::arg("push"), py::arg("scatter"), py::arg("rope") = py::none(), py::arg("residual") = py::none());
 }

@@ -195,35 +195,48 @@ __global__ void rope_tables_k(const int64_t* __restrict__ pos, float* __restrict
   sin_o[i] = s;
 }
 
-__global__ void rope_inplace_k(bf16* __restrict__ x, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                               int64_t T, int n_rot, int head_dim, int64_t row_stride, int inverse) {
+// Rotary embedding over a [T, heads, head_dim] tensor whose heads come in groups of `period`: the first `n_rot` heads of
+// every group are rotated, the rest are not.  In place (COPY false: only the rotated heads are touched) or from `src`
+// to `dst` (COPY true: the other heads are copied as they are, so a rotation that follows a copy costs one pass, not two).
+template <bool COPY>
+__global__ void rope_k(const bf16* __restrict__ src, bf16* __restrict__ dst, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t, int64_t T, int groups, int period, int n_rot, int head_dim,
+                       int64_t src_stride, int64_t dst_stride, int inverse) {
   const int half = head_dim >> 1;
   const int vec_per_head = half >> 3;
+  const int per_group = COPY ? period : n_rot;
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int64_t total = T * n_rot * vec_per_head;
+  const int64_t total = T * groups * per_group * vec_per_head;
   if (i >= total) return;
   const int kv = (int)(i % vec_per_head);
-  const int h = (int)((i / vec_per_head) % n_rot);
-  const int64_t t = i / ((int64_t)vec_per_head * n_rot);
-  bf16* p1 = x + t * row_stride + (int64_t)h * head_dim + kv * 8;
-  bf16* p2 = p1 + half;
+  const int hh = (int)((i / vec_per_head) % ((int64_t)groups * per_group));
+  const int64_t t = i / ((int64_t)vec_per_head * groups * per_group);
+  const int g = hh / per_group, hg = hh - g * per_group;
+  const int64_t col = ((int64_t)g * period + hg) * head_dim + kv * 8;
+  const bf16* s1 = src + t * src_stride + col;
+  bf16* d1 = dst + t * dst_stride + col;
+  if (COPY && hg >= n_rot) {
+    st8(d1, ld8(s1));
+    st8(d1 + half, ld8(s1 + half));
+    return;
+  }
   float a[8], b[8], o1[8], o2[8];
-  unpack8(ld8(p1), a);
-  unpack8(ld8(p2), b);
+  unpack8(ld8(s1), a);
+  unpack8(ld8(s1 + half), b);
   const float* cp = cos_t + t * half + kv * 8;
   const float* sp = sin_t + t * half + kv * 8;
   const float4 c0 = *reinterpret_cast<const float4*>(cp), c1 = *reinterpret_cast<const float4*>(cp + 4);
-  const float4 s0 = *reinterpret_cast<const float4*>(sp), s1 = *reinterpret_cast<const float4*>(sp + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(sp), s1v = *reinterpret_cast<const float4*>(sp + 4);
   const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-  float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1v.x, s1v.y, s1v.z, s1v.w};
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const float sj = inverse ? -s[j] : s[j];
     o1[j] = a[j] * c[j] - b[j] * sj;
     o2[j] = b[j] * c[j] + a[j] * sj;
   }
-  st8(p1, pack8(o1));
-  st8(p2, pack8(o2));
+  st8(d1, pack8(o1));
+  st8(d1 + half, pack8(o2));
 }
 
 // ------------------------------------------------------------------------------------------- SwiGLU
@@ -514,14 +527,29 @@ extern "C" int ody_rope_tables(const int64_t* positions, float* cos_out, float* 
   return last_err();
 }
 
+extern "C" int ody_rope(const void* src, void* dst, const float* cos_t, const float* sin_t, int64_t T, int heads,
+                        int period, int n_rot, int head_dim, int64_t src_stride, int64_t dst_stride, int inverse,
+                        cudaStream_t st) {
+  if (head_dim % 16 != 0 || src_stride % 8 != 0 || dst_stride % 8 != 0 || period <= 0 || heads % period != 0 ||
+      n_rot < 0 || n_rot > period)
+    return (int)cudaErrorInvalidValue;
+  const int groups = heads / period;
+  const bool copy = src != (const void*)dst;
+  const int64_t total = T * groups * (copy ? period : n_rot) * (head_dim / 16);
+  if (total == 0) return 0;
+  if (copy)
+    rope_k<true><<<blocks_for(total, 256), 256, 0, st>>>((const bf16*)src, (bf16*)dst, cos_t, sin_t, T, groups, period,
+                                                         n_rot, head_dim, src_stride, dst_stride, inverse);
+  else
+    rope_k<false><<<blocks_for(total, 256), 256, 0, st>>>((const bf16*)src, (bf16*)dst, cos_t, sin_t, T, groups, period,
+                                                          n_rot, head_dim, src_stride, dst_stride, inverse);
+  return last_err();
+}
+
 extern "C" int ody_rope_inplace(void* x, const float* cos_t, const float* sin_t, int64_t T, int n_rot, int head_dim,
                                 int64_t row_stride, int inverse, cudaStream_t st) {
-  if (head_dim % 16 != 0 || row_stride % 8 != 0) return (int)cudaErrorInvalidValue;
-  const int64_t total = T * n_rot * (head_dim / 16);
-  if (total == 0) return 0;
-  rope_inplace_k<<<blocks_for(total, 256), 256, 0, st>>>((bf16*)x, cos_t, sin_t, T, n_rot, head_dim, row_stride,
-                                                         inverse);
-  return last_err();
+  if (n_rot == 0 || T == 0) return 0;
+  return ody_rope(x, x, cos_t, sin_t, T, n_rot, n_rot, n_rot, head_dim, row_stride, row_stride, inverse, st);
 }
 
 extern "C" int ody_swiglu_fwd(const void* gu, void* h, int64_t T, int64_t I, cudaStream_t st) {

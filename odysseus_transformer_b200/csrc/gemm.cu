@@ -60,11 +60,13 @@ __device__ __forceinline__ bool epi_all_ok(bool ok) {
   return r != 0;
 }
 
-template <int LAYOUT>
+// ROPE: the epilogue rotates the q / k heads of a packed projection (RopeEpi, sm100.cuh); a separate instance, so that
+// the plain one keeps its register allocation
+template <int LAYOUT, bool ROPE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __nv_bfloat16* __restrict__ c_in, int M, int N, int K,
-                 int64_t ldc, int accumulate, int mn3d, int* __restrict__ err) {
+                 int64_t ldc, int accumulate, int mn3d, const RopeEpi rp, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   GemmBars* bars = (GemmBars*)(smem + SMEM_TILES);
@@ -210,11 +212,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32(taddr, v);
         tmem_ld_32x32(taddr + 32, v + 32);
         tmem_ld_wait();
+        const int row = m0 + r, col0 = n0 + c * EPI_COLS;
+        if (ROPE && rope_epi_wants(rp, col0)) {
+          // the other half of this head, still in the accumulator (read before the buffer is handed back below)
+          uint32_t w[64];
+          const uint32_t paddr = (c & 1) ? taddr - EPI_COLS : taddr + EPI_COLS;
+          tmem_ld_32x32(paddr, w);
+          tmem_ld_32x32(paddr + 32, w + 32);
+          tmem_ld_wait();
+          if (row < M) rope_epi_apply(rp, row, c & 1, v, w);
+        }
         if (c == BN / EPI_COLS - 1) {
           tc_fence_before();
           mbar_arrive(&bars->tmem_empty[buf]);
         }
-        const int row = m0 + r, col0 = n0 + c * EPI_COLS;
         if (accumulate && row < M) {
           const __nv_bfloat16* cp = c_in + (int64_t)row * ldc + col0;
 #pragma unroll
@@ -261,12 +272,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 static int g_num_sms = 0;
 
-template <int LAYOUT>
+template <int LAYOUT, bool ROPE>
 static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
-                       int64_t ldc, int accumulate, int* err, cudaStream_t st) {
+                       int64_t ldc, int accumulate, const void* c_in, int64_t ld_in, const RopeEpi& rp, int* err,
+                       cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<LAYOUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<LAYOUT, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -290,8 +302,8 @@ static int launch_gemm(const void* A, const void* B, void* C, int M, int N, int 
   if (r) return 720000 + r;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int grid = tiles < g_num_sms ? tiles : g_num_sms;
-  gemm_bf16_kernel<LAYOUT><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tA, tB, tC, (const __nv_bfloat16*)C, M, N, K, ldc,
-                                                                  accumulate, mn3d, err);
+  gemm_bf16_kernel<LAYOUT, ROPE><<<grid, NUM_THREADS, SMEM_TOTAL, st>>>(tA, tB, tC, (const __nv_bfloat16*)c_in, M, N, K, ld_in,
+                                                                  accumulate, mn3d, rp, err);
   return (int)cudaGetLastError();
 }
 
@@ -306,8 +318,38 @@ extern "C" int ody_gemm_set_variant(int v) {
   return 0;
 }
 
-extern "C" int ody_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
-                             int64_t ldc, int layout, int accumulate, int* err, cudaStream_t st) {
+// Checks an epilogue description against the problem and turns it into what the kernels take: where the values added
+// to the product come from (C itself when accumulating, the residual otherwise) and the rotary description.
+extern "C" int ody_gemm_resolve_epilogue(const OdyEpilogue* epi, const void* C, int M, int N, int64_t ldc, int* accumulate,
+                                         const void** c_in, int64_t* ld_in, ody::RopeEpi* rp) {
+  *c_in = C;
+  *ld_in = ldc;
+  rp->cos = nullptr;
+  rp->sin = nullptr;
+  rp->period_cols = rp->rot_cols = 0;
+  if (epi == nullptr) return 0;
+  if (epi->residual != nullptr) {
+    if (*accumulate || (epi->residual_ld % 8) || ((uintptr_t)epi->residual & 15)) return (int)cudaErrorInvalidValue;
+    *c_in = epi->residual;
+    *ld_in = epi->residual_ld;
+    *accumulate = 1;
+  }
+  if (epi->rope_cos != nullptr) {
+    if (epi->rope_sin == nullptr || epi->rope_period_cols <= 0 || (epi->rope_period_cols % 128) || (epi->rope_rot_cols % 128) ||
+        epi->rope_rot_cols < 0 || epi->rope_rot_cols > epi->rope_period_cols || (N % 128) ||
+        ((uintptr_t)epi->rope_cos & 15) || ((uintptr_t)epi->rope_sin & 15))
+      return (int)cudaErrorInvalidValue;
+    rp->cos = epi->rope_cos;
+    rp->sin = epi->rope_sin;
+    rp->period_cols = epi->rope_period_cols;
+    rp->rot_cols = epi->rope_rot_cols;
+  }
+  (void)M;
+  return 0;
+}
+
+extern "C" int ody_gemm_bf16_ex(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                                int64_t ldc, int layout, int accumulate, const OdyEpilogue* epi, int* err, cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0) return (int)cudaErrorInvalidValue;
   bool pairs = g_gemm_variant == 2;
   if (g_gemm_variant == 0 && M > 128) {
@@ -319,13 +361,25 @@ extern "C" int ody_gemm_bf16(const void* A, const void* B, void* C, int M, int N
     const double e1 = (double)t1 / (double)(((t1 + s1 - 1) / s1) * s1), e2 = (double)t2 / (double)(((t2 + s2 - 1) / s2) * s2);
     pairs = e2 * 1.06 >= e1;
   }
-  if (pairs) return ody_gemm_bf16_2cta(A, B, C, M, N, K, lda, ldb, ldc, layout, accumulate, err, st);
+  if (pairs) return ody_gemm_bf16_2cta_ex(A, B, C, M, N, K, lda, ldb, ldc, layout, accumulate, epi, err, st);
   if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15))
     return (int)cudaErrorInvalidValue;
+  const void* c_in;
+  int64_t ld_in;
+  ody::RopeEpi rp;
+  if (int r = ody_gemm_resolve_epilogue(epi, C, M, N, ldc, &accumulate, &c_in, &ld_in, &rp)) return r;
+  if (rp.cos != nullptr)   // a forward projection: layout 0 only
+    return layout == 0 ? ody::launch_gemm<0, true>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, c_in, ld_in, rp, err, st)
+                       : (int)cudaErrorInvalidValue;
   switch (layout) {
-    case 0: return ody::launch_gemm<0>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, err, st);
-    case 1: return ody::launch_gemm<1>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, err, st);
-    case 2: return ody::launch_gemm<2>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, err, st);
+    case 0: return ody::launch_gemm<0, false>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, c_in, ld_in, rp, err, st);
+    case 1: return ody::launch_gemm<1, false>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, c_in, ld_in, rp, err, st);
+    case 2: return ody::launch_gemm<2, false>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, c_in, ld_in, rp, err, st);
   }
   return (int)cudaErrorInvalidValue;
+}
+
+extern "C" int ody_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                             int64_t ldc, int layout, int accumulate, int* err, cudaStream_t st) {
+  return ody_gemm_bf16_ex(A, B, C, M, N, K, lda, ldb, ldc, layout, accumulate, nullptr, err, st);
 }

@@ -22,6 +22,10 @@
 #include "ody_kernels.h"
 #include "sm100.cuh"
 
+// defined in gemm.cu: validates an epilogue description and resolves it into kernel arguments
+extern "C" int ody_gemm_resolve_epilogue(const OdyEpilogue* epi, const void* C, int M, int N, int64_t ldc, int* accumulate,
+                                         const void** c_in, int64_t* ld_in, ody::RopeEpi* rp);
+
 namespace ody {
 namespace g2 {
 
@@ -125,11 +129,13 @@ __device__ __forceinline__ bool epi_all_ok(bool ok) {
   return r != 0;
 }
 
-template <int LAYOUT>
+// ROPE: the epilogue rotates the q / k heads of a packed projection (RopeEpi, sm100.cuh); a separate instance, so that
+// the plain one keeps its register allocation
+template <int LAYOUT, bool ROPE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, const __nv_bfloat16* __restrict__ c_in, int M, int N, int K,
-                  int64_t ldc, int accumulate, int mn3d, int* __restrict__ err) {
+                  int64_t ldc, int accumulate, int mn3d, const RopeEpi rp, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Bars* bars = (Bars*)(smem + SMEM_TILES);
@@ -281,11 +287,20 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         tmem_ld_32x32(taddr, v);
         tmem_ld_32x32(taddr + 32, v + 32);
         tmem_ld_wait();
+        const int row = m0 + r, col0 = n0 + c * EPI_COLS;
+        if (ROPE && rope_epi_wants(rp, col0)) {
+          // the other half of this head, still in the accumulator (read before the buffer is handed back below)
+          uint32_t w[64];
+          const uint32_t paddr = (c & 1) ? taddr - EPI_COLS : taddr + EPI_COLS;
+          tmem_ld_32x32(paddr, w);
+          tmem_ld_32x32(paddr + 32, w + 32);
+          tmem_ld_wait();
+          if (row < M) rope_epi_apply(rp, row, c & 1, v, w);
+        }
         if (c == BN / EPI_COLS - 1) {
           tc_fence_before();
           mbar_arrive_cluster(empty0);            // this thread's rows of the accumulator are in registers
         }
-        const int row = m0 + r, col0 = n0 + c * EPI_COLS;
         if (accumulate && row < M) {
           const __nv_bfloat16* cp = c_in + (int64_t)row * ldc + col0;
 #pragma unroll
@@ -334,12 +349,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 static int g_max_pairs = 0;
 
-template <int LAYOUT>
+template <int LAYOUT, bool ROPE>
 static int launch(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                  int accumulate, int* err, cudaStream_t st) {
+                  int accumulate, const void* c_src, int64_t ld_in, const RopeEpi& rp, int* err, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_kernel<LAYOUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(gemm2_bf16_kernel<LAYOUT, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -360,7 +375,7 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cfg.gridDim = dim3(sms - (sms & 1));
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm2_bf16_kernel<LAYOUT>, &cfg);
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm2_bf16_kernel<LAYOUT, ROPE>, &cfg);
     if (e != cudaSuccess || n <= 0) { cudaGetLastError(); n = sms / 2; }     // fall back to the nominal count
     g_max_pairs = n < sms / 2 ? n : sms / 2;
   }
@@ -380,24 +395,37 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
   const int pairs = tiles < g_max_pairs ? tiles : g_max_pairs;
   cfg.gridDim = dim3(2 * pairs);
-  const __nv_bfloat16* c_in = (const __nv_bfloat16*)C;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel<LAYOUT>, tA, tB, tC, c_in, M, N, K, ldc, accumulate, mn3d, err);
+  const __nv_bfloat16* c_in = (const __nv_bfloat16*)c_src;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2_bf16_kernel<LAYOUT, ROPE>, tA, tB, tC, c_in, M, N, K, ld_in, accumulate, mn3d, rp, err);
   return (int)e;
 }
 
 }  // namespace g2
 }  // namespace ody
 
-// Same arguments as ody_gemm_bf16; the pair kernel.  ody_gemm_bf16 chooses between the two (gemm.cu).
-extern "C" int ody_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
-                                  int64_t ldc, int layout, int accumulate, int* err, cudaStream_t st) {
+// Same arguments as ody_gemm_bf16_ex; the pair kernel.  ody_gemm_bf16_ex chooses between the two (gemm.cu).
+extern "C" int ody_gemm_bf16_2cta_ex(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                                     int64_t ldc, int layout, int accumulate, const OdyEpilogue* epi, int* err,
+                                     cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0) return (int)cudaErrorInvalidValue;
   if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15))
     return (int)cudaErrorInvalidValue;
+  const void* c_in;
+  int64_t ld_in;
+  ody::RopeEpi rp;
+  if (int r = ody_gemm_resolve_epilogue(epi, C, M, N, ldc, &accumulate, &c_in, &ld_in, &rp)) return r;
+  if (rp.cos != nullptr)   // a forward projection: layout 0 only
+    return layout == 0 ? ody::g2::launch<0, true>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, c_in, ld_in, rp, err, st)
+                       : (int)cudaErrorInvalidValue;
   switch (layout) {
-    case 0: return ody::g2::launch<0>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, err, st);
-    case 1: return ody::g2::launch<1>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, err, st);
-    case 2: return ody::g2::launch<2>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, err, st);
+    case 0: return ody::g2::launch<0, false>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, c_in, ld_in, rp, err, st);
+    case 1: return ody::g2::launch<1, false>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, c_in, ld_in, rp, err, st);
+    case 2: return ody::g2::launch<2, false>(A, B, C, M, N, K, lda, ldb, ldc, accumulate, c_in, ld_in, rp, err, st);
   }
   return (int)cudaErrorInvalidValue;
+}
+
+extern "C" int ody_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                                  int64_t ldc, int layout, int accumulate, int* err, cudaStream_t st) {
+  return ody_gemm_bf16_2cta_ex(A, B, C, M, N, K, lda, ldb, ldc, layout, accumulate, nullptr, err, st);
 }

@@ -58,6 +58,9 @@ struct ScatterParams {
   int a2a_cols;
   int64_t a2a_ld, a2a_row0, a2a_col0;
   unsigned long long* wait_acc;           // optional running totals (ns): [1] += the time owners waited for the sources' tiles
+  const __nv_bfloat16* residual;          // optional, added to the result: SCATTER == 1 [chunk_rows, N], this rank's reduced
+                                          // rows; SCATTER == 0 [M, N]
+  int64_t residual_ld;
 };
 
 struct Bars {
@@ -146,12 +149,14 @@ __global__ void __launch_bounds__(COMM_THREADS) push_shard_kernel(const __grid_c
 // 1 push rows to their owner and reduce own rows, 2 all-to-all: push column groups to their owner (the
 // Ulysses sequence<->head exchange, yunchang SeqAllToAll4D called at reference decoder/ulysses.py:40-47;
 // the receivers wait on the per-source counters with ody_wait_flags).
-template <int LAYOUT, int GATHER, int SCATTER>
+// ROPE: the epilogue rotates the q / k heads of a packed projection (RopeEpi, sm100.cuh); compiled only where a
+// q|k|v projection can be the product, so that the other instances keep their register allocation.
+template <int LAYOUT, int GATHER, int SCATTER, bool ROPE>
 __global__ void __launch_bounds__(NUM_THREADS + COMM_THREADS, 1)
 gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ GatherParams gp,
                  const __grid_constant__ GatherParams pp, const __grid_constant__ ScatterParams sp, int M, int N, int K, int64_t ldc, int n_gemm,
-                 int mn3d, int* __restrict__ err) {
+                 int mn3d, const RopeEpi rp, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Bars* bars = (Bars*)(smem + SMEM_TILES);
@@ -358,8 +363,17 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_32x32(taddr, v);
         tmem_ld_32x32(taddr + 32, v + 32);
         tmem_ld_wait();
-        if (c == BN / EPI_COLS - 1) { tc_fence_before(); mbar_arrive(&bars->tmem_empty[buf]); }
         const int col0 = n0 + c * EPI_COLS;
+        if (ROPE && SCATTER != 1 && rope_epi_wants(rp, col0)) {
+          // rotary embedding of a q / k head: the other half of the head is still in the accumulator
+          uint32_t w[64];
+          const uint32_t paddr = (c & 1) ? taddr - EPI_COLS : taddr + EPI_COLS;
+          tmem_ld_32x32(paddr, w);
+          tmem_ld_32x32(paddr + 32, w + 32);
+          tmem_ld_wait();
+          if (m0 + r < M) rope_epi_apply(rp, m0 + r, c & 1, v, w);
+        }
+        if (c == BN / EPI_COLS - 1) { tc_fence_before(); mbar_arrive(&bars->tmem_empty[buf]); }
         if (SCATTER) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -395,6 +409,23 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         } else {
+          if (sp.residual != nullptr && m0 + r < M) {
+            // the residual stream's row joins the product before it is rounded
+            const __nv_bfloat16* cp = sp.residual + (int64_t)(m0 + r) * sp.residual_ld + col0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (col0 + j * 8 < N) {   // N is a multiple of 8
+                const uint4 old = *reinterpret_cast<const uint4*>(cp + j * 8);
+                const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  const float2 f = __bfloat1622float2(o2[t]);
+                  v[j * 8 + 2 * t] = __float_as_uint(__uint_as_float(v[j * 8 + 2 * t]) + f.x);
+                  v[j * 8 + 2 * t + 1] = __float_as_uint(__uint_as_float(v[j * 8 + 2 * t + 1]) + f.y);
+                }
+              }
+            }
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             uint4 pk;
@@ -464,6 +495,17 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             off[u] = rr * ldc + cc;
 #pragma unroll
             for (int t = 0; t < 8; ++t) acc[u][t] = 0.f;
+            if (sp.residual != nullptr && live[u]) {
+              // the residual stream's rows of this rank start the sum
+              const uint4 pk = *reinterpret_cast<const uint4*>(sp.residual + rr * sp.residual_ld + cc);
+              const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const float2 f = __bfloat1622float2(p2[t]);
+                acc[u][2 * t] = f.x;
+                acc[u][2 * t + 1] = f.y;
+              }
+            }
           }
           for (int s = 0; s < sp.n_ranks; ++s) {
             uint4 pk[RU];
@@ -535,12 +577,13 @@ static unsigned long long* wait_acc_here() {
   return g_wait_acc[dev];
 }
 
-template <int LAYOUT, int GATHER, int SCATTER>
+template <int LAYOUT, int GATHER, int SCATTER, bool ROPE>
 static int launch(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                  const OdyGatherDesc* gd, const OdyGatherDesc* pd, const OdyScatterDesc* sd, int* err, cudaStream_t st) {
+                  const OdyGatherDesc* gd, const OdyGatherDesc* pd, const OdyScatterDesc* sd, const OdyEpilogue* epi, int* err,
+                  cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_comm_kernel<LAYOUT, GATHER, SCATTER>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_comm_kernel<LAYOUT, GATHER, SCATTER, ROPE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -601,14 +644,35 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
     ldc = N;
     C = sd->stage_peer[sd->rank];
   }
+  RopeEpi rp;
+  rp.cos = rp.sin = nullptr;
+  rp.period_cols = rp.rot_cols = 0;
+  if (epi != nullptr) {
+    // the residual joins the reduction of a reduce-scatter or the plain epilogue, the rotation the epilogues that keep whole rows
+    if (epi->residual != nullptr) {
+      if (SCATTER == 2 || (epi->residual_ld % 8) || ((uintptr_t)epi->residual & 15)) return (int)cudaErrorInvalidValue;
+      sp.residual = (const __nv_bfloat16*)epi->residual;
+      sp.residual_ld = epi->residual_ld;
+    }
+    if (epi->rope_cos != nullptr) {
+      if (!ROPE || SCATTER == 1 || epi->rope_sin == nullptr || epi->rope_period_cols <= 0 || (epi->rope_period_cols % 128) ||
+          (epi->rope_rot_cols % 128) || epi->rope_rot_cols < 0 || epi->rope_rot_cols > epi->rope_period_cols || (N % 128) ||
+          ((uintptr_t)epi->rope_cos & 15) || ((uintptr_t)epi->rope_sin & 15))
+        return (int)cudaErrorInvalidValue;
+      rp.cos = epi->rope_cos;
+      rp.sin = epi->rope_sin;
+      rp.period_cols = epi->rope_period_cols;
+      rp.rot_cols = epi->rope_rot_cols;
+    }
+  }
   if ((r = make_tmap_2d_bf16(&tC, C, (uint64_t)N, (uint64_t)(SCATTER == 1 ? sd->chunk_rows : M), (uint64_t)ldc * 2, EPI_COLS, BM))) return 720000 + r;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int n_gemm = g_sms;
   if (tiles < n_gemm) n_gemm = tiles;
   if (GATHER && (gd->n_cta != n_gemm || (pd != nullptr && pd->n_cta != n_gemm))) return (int)cudaErrorInvalidConfiguration;   // the host's running totals assume this grid
   if (SCATTER) { sp.reduce_target = (uint32_t)n_gemm * sd->uses; sp.arrived_target = (uint32_t)n_gemm * sd->uses; }
-  gemm_comm_kernel<LAYOUT, GATHER, SCATTER><<<n_gemm, (GATHER && has_push) ? NUM_THREADS + COMM_THREADS : NUM_THREADS, SMEM_TOTAL, st>>>(tA, tB, tC, gp, pp, sp, M, N, K, ldc,
-                                                                                           n_gemm, mn3d, err);
+  gemm_comm_kernel<LAYOUT, GATHER, SCATTER, ROPE><<<n_gemm, (GATHER && has_push) ? NUM_THREADS + COMM_THREADS : NUM_THREADS, SMEM_TOTAL, st>>>(tA, tB, tC, gp, pp, sp, M, N, K, ldc,
+                                                                                           n_gemm, mn3d, rp, err);
   return (int)cudaGetLastError();
 }
 
@@ -617,20 +681,32 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
 
 // gather / scatter may be null when that half is not used.  gather->which selects the gathered operand; push is
 // the shard this launch's comm warps deliver (null: none - the operand was pushed by an earlier launch).
-extern "C" int ody_gemm_comm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
-                             int64_t ldc, int layout, const OdyGatherDesc* gd, const OdyGatherDesc* pd,
-                             const OdyScatterDesc* sd, int* err, cudaStream_t st) {
+extern "C" int ody_gemm_comm_ex(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                                int64_t ldc, int layout, const OdyGatherDesc* gd, const OdyGatherDesc* pd,
+                                const OdyScatterDesc* sd, const OdyEpilogue* epi, int* err, cudaStream_t st) {
   using namespace ody::gc;
   if (M <= 0 || N <= 0 || K <= 0 || (lda % 8) || (ldb % 8) || (N % 8)) return (int)cudaErrorInvalidValue;
   const int g = gd ? gd->which : 0;
   const int s = sd ? (sd->mode == 2 ? 2 : 1) : 0;
+  const bool rope = epi != nullptr && epi->rope_cos != nullptr;
 #define ODY_CASE(L, G, S) \
-  if (layout == L && g == G && s == S) return launch<L, G, S>(A, B, C, M, N, K, lda, ldb, ldc, gd, pd, sd, err, st);
+  if (layout == L && g == G && s == S && !rope) return launch<L, G, S, false>(A, B, C, M, N, K, lda, ldb, ldc, gd, pd, sd, epi, err, st);
+#define ODY_CASE_ROPE(L, G, S) \
+  if (layout == L && g == G && s == S && rope) return launch<L, G, S, true>(A, B, C, M, N, K, lda, ldb, ldc, gd, pd, sd, epi, err, st);
   ODY_CASE(0, 1, 0) ODY_CASE(0, 2, 0) ODY_CASE(1, 1, 0) ODY_CASE(1, 2, 0) ODY_CASE(2, 2, 0) ODY_CASE(2, 1, 0)
   ODY_CASE(0, 0, 1) ODY_CASE(1, 0, 1) ODY_CASE(2, 0, 1)
   ODY_CASE(0, 2, 2) ODY_CASE(1, 2, 2)
+  // forward projections only: sequence gather -> q|k|v, weight gather -> q|k|v, weight gather -> q|k|v -> all-to-all
+  ODY_CASE_ROPE(0, 1, 0) ODY_CASE_ROPE(0, 2, 0) ODY_CASE_ROPE(0, 2, 2)
+#undef ODY_CASE_ROPE
 #undef ODY_CASE
   return (int)cudaErrorInvalidValue;
+}
+
+extern "C" int ody_gemm_comm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb,
+                             int64_t ldc, int layout, const OdyGatherDesc* gd, const OdyGatherDesc* pd,
+                             const OdyScatterDesc* sd, int* err, cudaStream_t st) {
+  return ody_gemm_comm_ex(A, B, C, M, N, K, lda, ldb, ldc, layout, gd, pd, sd, nullptr, err, st);
 }
 
 // Deliver a shard into every rank's gathered buffer without a GEMM (n_cta CTAs of 128 threads).

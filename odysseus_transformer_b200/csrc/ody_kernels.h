@@ -24,6 +24,10 @@ int ody_rope_tables(const int64_t* positions, float* cos_out, float* sin_out, in
 // rotates heads [0, n_rot) of x [T, heads, hd] (row stride in elements) in place; inverse = transpose rotation
 int ody_rope_inplace(void* x, const float* cos_t, const float* sin_t, int64_t T, int n_rot, int head_dim,
                      int64_t row_stride, int inverse, cudaStream_t stream);
+// general form: heads come in groups of `period`, the first n_rot of each group are rotated; src == dst rotates in place,
+// otherwise every head is written to dst (the others copied), so that a copy followed by a rotation is one pass
+int ody_rope(const void* src, void* dst, const float* cos_t, const float* sin_t, int64_t T, int heads, int period,
+             int n_rot, int head_dim, int64_t src_stride, int64_t dst_stride, int inverse, cudaStream_t stream);
 
 // ---- SwiGLU: gu [T, 2I] = [gate | up]  ->  h [T, I] ; bwd writes dgu [T, 2I]
 int ody_swiglu_fwd(const void* gu, void* h, int64_t T, int64_t I, cudaStream_t stream);
@@ -63,6 +67,19 @@ int ody_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, in
 int ody_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                        int layout, int accumulate, int* err, cudaStream_t stream);
 int ody_gemm_set_variant(int variant);
+// Work folded into the GEMM epilogue (all optional).
+//  rope_*: rotary embedding of a packed q|k|v projection with head_dim 128 - output columns in groups of
+//    rope_period_cols, the first rope_rot_cols of each group rotated with cos / sin [M, 64] fp32 indexed by output row.
+//  residual: bf16 [M, N] (row pitch residual_ld) added to the product; C need not hold it (not together with accumulate).
+typedef struct OdyEpilogue {
+  const float* rope_cos; const float* rope_sin;
+  int rope_period_cols, rope_rot_cols;
+  const void* residual; int64_t residual_ld;
+} OdyEpilogue;
+int ody_gemm_bf16_ex(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                     int layout, int accumulate, const OdyEpilogue* epilogue, int* err, cudaStream_t stream);
+int ody_gemm_bf16_2cta_ex(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                          int layout, int accumulate, const OdyEpilogue* epilogue, int* err, cudaStream_t stream);
 
 // ---- attention forward (head_dim 128): q [Tq,H,128], k/v [Tk,Hkv,128], row pitches in elements; out bf16, lse [H,Tq]
 // fp32 natural log.  causal needs Tq == Tk.
@@ -122,6 +139,11 @@ typedef struct OdyScatterDesc {
 int ody_gemm_comm(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                   int layout, const OdyGatherDesc* gather, const OdyGatherDesc* push, const OdyScatterDesc* scatter, int* err,
                   cudaStream_t stream);
+// epilogue: rotary embedding in the epilogues that write whole rows (no scatter, or the all-to-all); the residual in
+// the plain epilogue ([M, N]) or in the reduction of the reduce-scatter (this rank's [chunk_rows, N] rows)
+int ody_gemm_comm_ex(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                     int layout, const OdyGatherDesc* gather, const OdyGatherDesc* push, const OdyScatterDesc* scatter,
+                     const OdyEpilogue* epilogue, int* err, cudaStream_t stream);
 int ody_push_shard(const OdyGatherDesc* push, int* err, cudaStream_t stream);
 // one-thread kernel: bounded wait until source `src`'s whole shard of the slot's current epoch has arrived here
 int ody_wait_shard(const OdyGatherDesc* slot, int src, int* err, cudaStream_t stream);

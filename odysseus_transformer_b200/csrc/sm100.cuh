@@ -338,6 +338,36 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, int a_mn_ma
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// ------------------------------------------------------------------------------------------- rotary embedding in a GEMM epilogue
+// The output columns are heads of 128 in groups of `period_cols`; the first `rot_cols` columns of every group belong
+// to heads that are rotated (q and k of a packed q|k|v projection), with the two halves of a head 64 columns apart.
+// An epilogue thread owns one output row and takes the accumulator in chunks of 64 columns, so a chunk is one half of
+// a head: it reads the other half (64 TMEM columns up or down) next to its own and writes
+//   low half:  x_lo * cos - x_hi * sin        high half:  x_hi * cos + x_lo * sin
+// with cos / sin [rows, 64] fp32 indexed by the output row.  cos == nullptr switches it off.
+struct RopeEpi {
+  const float* cos;
+  const float* sin;
+  int period_cols, rot_cols;
+};
+__device__ __forceinline__ bool rope_epi_wants(const RopeEpi& rp, int col0) {
+  return rp.cos != nullptr && (col0 % rp.period_cols) < rp.rot_cols;
+}
+// v: this chunk's 64 accumulators (fp32 bits), w: the partner half's; hi: this chunk is the high half of its head
+__device__ __forceinline__ void rope_epi_apply(const RopeEpi& rp, int64_t row, bool hi, uint32_t* v, const uint32_t* w) {
+  const float4* c4 = reinterpret_cast<const float4*>(rp.cos + row * 64);
+  const float4* s4 = reinterpret_cast<const float4*>(rp.sin + row * 64);
+  const float sg = hi ? 1.f : -1.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float4 c = __ldg(c4 + i), s = __ldg(s4 + i);
+    v[4 * i + 0] = __float_as_uint(__uint_as_float(v[4 * i + 0]) * c.x + sg * __uint_as_float(w[4 * i + 0]) * s.x);
+    v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) * c.y + sg * __uint_as_float(w[4 * i + 1]) * s.y);
+    v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) * c.z + sg * __uint_as_float(w[4 * i + 2]) * s.z);
+    v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) * c.w + sg * __uint_as_float(w[4 * i + 3]) * s.w);
+  }
+}
+
 #endif  // __CUDACC__
 
 // ------------------------------------------------------------------------------------------- host: tensor maps

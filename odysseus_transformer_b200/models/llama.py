@@ -22,7 +22,8 @@ up and every parameter receives exactly the gradient of that one scalar (the ref
 per-rank means with summed and averaged reductions, reference ``train.py:214-222``,
 ``utils/linear_zero3.py:82-84``).
 
-Inter-layer activations are ``[T/N, d]``; the residual add is fused into the following RMSNorm.
+Inter-layer activations are ``[T/N, d]``; the residual add happens in the epilogue of each block's output projection
+(``ops.functional.fuse_epilogues``; otherwise it is fused into the following RMSNorm).
 """
 from __future__ import annotations
 
@@ -67,7 +68,17 @@ class DecoderLayer(nn.Module):
             p.grad_sync_group = ctx.world_group
 
     def forward(self, x, delta, cos, sin):
-        """(x, delta): residual stream and the not-yet-added output of the previous block."""
+        """(x, delta): residual stream and the not-yet-added output of the previous block (None when that block
+        added it itself)."""
+        if F.epilogue_fusion("residual"):
+            # each block's output projection adds the residual stream in its own epilogue; the norms only normalise
+            if delta is None:
+                x, h = F.rmsnorm_keep(x, self.input_layernorm, self.eps)
+            else:
+                x, h = F.add_rmsnorm(x, delta, self.input_layernorm, self.eps)
+            x = self.self_attn(h, cos, sin, residual=x)
+            x, h = F.rmsnorm_keep(x, self.post_attention_layernorm, self.eps)
+            return self.mlp(h, residual=x), None
         if delta is None:
             h = F.rmsnorm(x, self.input_layernorm, self.eps)
         else:
@@ -132,6 +143,8 @@ class LlamaForCausalLM(nn.Module):
                 x, delta = checkpoint(layer, x, delta, cos, sin, use_reentrant=False)
             else:
                 x, delta = layer(x, delta, cos, sin)
+        if delta is None:
+            return F.rmsnorm(x, self.norm, self.cfg.rms_norm_eps)
         _, h = F.add_rmsnorm(x, delta, self.norm, self.cfg.rms_norm_eps)
         return h
 

@@ -12,7 +12,8 @@ Tensor conventions: batch size is 1 and folded away, as in the reference
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
+import os
+from typing import NamedTuple, Optional, Tuple
 
 import torch
 from torch.autograd import Function
@@ -22,13 +23,63 @@ from . import native, torch_ref as R
 # ----------------------------------------------------------------------------- GEMM primitives
 
 
-def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """C[M,N] = A[M,K] @ B[N,K]^T  (the forward of a linear layer: x @ W^T)."""
+class RopeEpilogue(NamedTuple):
+    """Rotary embedding folded into the epilogue of a packed q|k|v projection: the output columns are heads in groups
+    of ``period_cols`` columns, the first ``rot_cols`` columns of each group (the q and k heads) are rotated with
+    ``cos`` / ``sin`` [rows, head_dim / 2] fp32, indexed by output row.  The reference rotates q and k in separate
+    passes after the projection (reference ``decoder/odysseus.py:200-226``)."""
+    cos: torch.Tensor
+    sin: torch.Tensor
+    rot_cols: int
+    period_cols: int
+
+    def in_kernel(self, n_cols: int) -> bool:
+        """The GEMM kernels' epilogue handles head_dim 128 with whole heads per group."""
+        return (self.cos.shape[1] == 64 and self.period_cols % 128 == 0 and self.rot_cols % 128 == 0
+                and n_cols % self.period_cols == 0)
+
+
+def rope_grouped_(src: torch.Tensor, dst: torch.Tensor, n_rot: int, period: int, cos, sin, inverse: bool) -> torch.Tensor:
+    """src [T, heads, hd] -> dst (may be src): heads in groups of ``period``, the first ``n_rot`` of each rotated and the
+    others copied.  One kernel where the reference's block does a copy and a rotation per tensor
+    (reference ``decoder/odysseus.py:200-226``)."""
+    if native.use_native(src):
+        native.lib().rope_grouped_(src, dst, n_rot, period, cos, sin, inverse)
+        return dst
+    T, heads, hd = src.shape
+    g = heads // period
+    s4 = src.reshape(T, g, period, hd)
+    rot = R.rope_apply(s4[:, :, :n_rot].reshape(T, g * n_rot, hd), cos, sin, inverse).reshape(T, g, n_rot, hd)
+    dst.copy_(torch.cat([rot.to(src.dtype), s4[:, :, n_rot:]], dim=2).reshape(T, heads, hd))
+    return dst
+
+
+def apply_rope_epilogue_(y: torch.Tensor, rope: RopeEpilogue) -> torch.Tensor:
+    """What the kernels' rotary epilogue computes, as a pass over the finished product y [rows, N] (in place)."""
+    hd = 2 * rope.cos.shape[1]
+    y3 = y.view(y.shape[0], y.shape[1] // hd, hd)
+    rope_grouped_(y3, y3, rope.rot_cols // hd, rope.period_cols // hd, rope.cos, rope.sin, False)
+    return y
+
+
+def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, rope: Optional[RopeEpilogue] = None,
+            residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C[M,N] = A[M,K] @ B[N,K]^T  (the forward of a linear layer: x @ W^T), optionally with the rotary embedding of a
+    packed q|k|v projection applied to the product and / or a residual [M, N] added to it, both in the GEMM epilogue."""
     if native.use_native(a):
-        return native.lib().gemm(a, b, out, 0, False)
-    if out is None:
-        return a @ b.t()
-    return torch.matmul(a, b.t(), out=out)
+        lib = native.lib()
+        if rope is None or rope.in_kernel(b.shape[0]):
+            if rope is None and residual is None:
+                return lib.gemm(a, b, out, 0, False)
+            return lib.gemm(a, b, out, 0, False, tuple(rope) if rope is not None else None, residual)
+        y = apply_rope_epilogue_(lib.gemm(a, b, out, 0, False), rope)       # head_dim other than 128: a pass of its own
+        return y if residual is None else y.add_(residual)
+    y = a @ b.t() if out is None else torch.matmul(a, b.t(), out=out)
+    if rope is not None:
+        apply_rope_epilogue_(y, rope)
+    if residual is not None:
+        y += residual
+    return y
 
 
 def gemm_nn(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -162,6 +213,55 @@ class _AddRMSNorm(Function):
 
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float):
     return _AddRMSNorm.apply(x, delta, w, eps)
+
+
+class _RMSNormKeep(Function):
+    """y = rmsnorm(s), returning (s, y) with s passed through: the residual stream arrives already summed (the block
+    before it added the residual in its GEMM epilogue) and goes on to the next block's epilogue, so its gradient comes
+    back as a second input of this op's backward and joins the normalisation's gradient in the same kernel."""
+
+    @staticmethod
+    def forward(ctx, s, w, eps):
+        if native.use_native(s):
+            y, rstd = native.lib().rmsnorm_fwd(s, w, eps)
+        else:
+            y, rstd = R.rmsnorm_fwd(s, w, eps)
+        ctx.save_for_backward(s, w, rstd)
+        return s.view_as(s), y
+
+    @staticmethod
+    def backward(ctx, ds, dy):
+        s, w, rstd = ctx.saved_tensors
+        dy = dy.contiguous()
+        if native.use_native(s):
+            dx, dw = native.lib().rmsnorm_bwd(dy, s, w, rstd, ds.contiguous())
+        else:
+            dx, dw = R.rmsnorm_bwd(dy, s, w, rstd)
+            dx = (dx.float() + ds.float()).to(dx.dtype)
+        return dx, deliver_grad(w, dw), None
+
+
+def rmsnorm_keep(s: torch.Tensor, w: torch.Tensor, eps: float):
+    """(s, rmsnorm(s)); see ``_RMSNormKeep``."""
+    return _RMSNormKeep.apply(s, w, eps)
+
+
+# Work folded into GEMM epilogues by the model blocks: "rope" - the q|k|v projection rotates q and k; "residual" - the
+# output projections of the attention and MLP blocks add the residual stream.  Switchable for A/B measurements.
+_EPILOGUE_FUSION = {"rope": os.environ.get("ODY_FUSE_ROPE", "1") != "0", "residual": os.environ.get("ODY_FUSE_RESIDUAL", "1") != "0"}
+
+
+def fuse_epilogues(rope: Optional[bool] = None, residual: Optional[bool] = None) -> dict:
+    """Set (where not None) and return which epilogue fusions the model blocks use."""
+    if rope is not None:
+        _EPILOGUE_FUSION["rope"] = bool(rope)
+    if residual is not None:
+        _EPILOGUE_FUSION["residual"] = bool(residual)
+    return dict(_EPILOGUE_FUSION)
+
+
+def epilogue_fusion(what: str) -> bool:
+    return _EPILOGUE_FUSION[what]
 
 
 # ----------------------------------------------------------------------------- RoPE

@@ -78,7 +78,8 @@ def _push_only(heap, shard: torch.Tensor):
 
 
 def _gather_gemm(heap, shard: torch.Tensor, which: int, other: torch.Tensor, layout: int,
-                 out: Optional[torch.Tensor] = None, slot=None, prefetch: Optional[torch.Tensor] = None, scatter=None):
+                 out: Optional[torch.Tensor] = None, slot=None, prefetch: Optional[torch.Tensor] = None, scatter=None,
+                 rope=None, residual: Optional[torch.Tensor] = None):
     """GEMM whose operand ``which`` (1 = A, 2 = B) is the all-gather of ``shard``.
 
     ``slot``: the gathered buffer when an earlier launch already delivered ``shard`` (prefetch), else the
@@ -86,9 +87,16 @@ def _gather_gemm(heap, shard: torch.Tensor, which: int, other: torch.Tensor, lay
     deliver when they have nothing else to do (only possible when ``slot`` was given).
     ``scatter``: an all-to-all description (``comm.symm.A2ASlot.gemm_desc``) for the epilogue; the result
     is then the local receive buffer, complete only after a wait on the slot's arrival words.
+    ``rope`` (``ops.functional.RopeEpilogue``; layout 0) / ``residual`` ([M, N]; not with ``scatter``): applied to
+    the product in the epilogue.  A ``rope`` the kernel cannot take (head_dim other than 128) makes the call unsupported.
     Returns (result, gathered view, slot holding the prefetched shard or None); result None = unsupported."""
     shard = shard if shard.stride(-1) == 1 else shard.contiguous()
     pushed = slot is not None
+    if rope is not None and not rope.in_kernel((shard.shape[0] * heap.n) if which == 2 else other.shape[0]):
+        if slot is None:
+            stats["fallback"] += 1
+            return None, None, None
+        raise RuntimeError("fused GEMM: the rotary epilogue needs head_dim 128")
     if slot is None:
         slot = heap.gather_slot(shard.shape[0], shard.shape[1])
         if slot is None:
@@ -109,13 +117,18 @@ def _gather_gemm(heap, shard: torch.Tensor, which: int, other: torch.Tensor, lay
         if next_slot is not None:
             push = next_slot.push_desc(prefetch, n_cta)
             stats["prefetch"] = stats.get("prefetch", 0) + 1
-    y = _lib().gemm_comm(a, b, out, layout, slot.consume_desc(which, n_cta), push, scatter)
+    if rope is None and residual is None:
+        y = _lib().gemm_comm(a, b, out, layout, slot.consume_desc(which, n_cta), push, scatter)
+    else:
+        y = _lib().gemm_comm(a, b, out, layout, slot.consume_desc(which, n_cta), push, scatter,
+                             tuple(rope) if rope is not None else None, residual)
     return y, g, next_slot
 
 
 def _scatter_gemm(heap, a: torch.Tensor, b: torch.Tensor, layout: int, M: int, N: int,
-                  out: Optional[torch.Tensor] = None):
-    """GEMM whose [M, N] result is reduce-scattered on rows; returns this rank's [M/n, N] or None."""
+                  out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None):
+    """GEMM whose [M, N] result is reduce-scattered on rows; returns this rank's [M/n, N] or None.
+    ``residual`` [M/n, N] starts the sum of this rank's rows."""
     if M % heap.n:
         stats["fallback"] += 1
         return None
@@ -127,7 +140,11 @@ def _scatter_gemm(heap, a: torch.Tensor, b: torch.Tensor, layout: int, M: int, N
     stats["scatter"] += 1
     if out is None:
         out = torch.empty(chunk, N, dtype=a.dtype, device=a.device)
-    _lib().gemm_comm(a, b, None, layout, None, None, slot.describe(out))
+    if residual is None:
+        _lib().gemm_comm(a, b, None, layout, None, None, slot.describe(out))
+    else:
+        residual = residual if residual.stride(-1) == 1 else residual.contiguous()
+        _lib().gemm_comm(a, b, None, layout, None, None, slot.describe(out), None, residual)
     return out
 
 
@@ -136,15 +153,15 @@ def _scatter_gemm(heap, a: torch.Tensor, b: torch.Tensor, layout: int, M: int, N
 
 class _FusedAGLinear(Function):
     @staticmethod
-    def forward(ctx, x, w, group):
+    def forward(ctx, x, w, group, rope=None):
         from ..ops import functional as F
         heap = heap_for(group)
         ctx.group = group
         ctx.save_for_backward(x, w)
-        y, _, _ = _gather_gemm(heap, x, 1, w, 0)
+        y, _, _ = _gather_gemm(heap, x, 1, w, 0, rope=rope)
         if y is None:
             from ..comm import torch_backend as C
-            y = F.gemm_nt(C.all_gather_rows(x, group), w)
+            y = F.gemm_nt(C.all_gather_rows(x, group), w, rope=rope)
         return y
 
     @staticmethod
@@ -163,15 +180,15 @@ class _FusedAGLinear(Function):
         fresh = mg is not None and not getattr(w, "_grad_written", False)
         dw, _, _ = _gather_gemm(heap, x, 2, dy, 2, out=mg if fresh else None)
         if dw is None:
-            return dx, F.store_weight_grad(w, dy, C.all_gather_rows(x, ctx.group)), None
+            return dx, F.store_weight_grad(w, dy, C.all_gather_rows(x, ctx.group)), None, None
         if fresh:
             w._grad_written = True
-            return dx, None, None
-        return dx, F.deliver_grad(w, dw), None
+            return dx, None, None, None
+        return dx, F.deliver_grad(w, dw), None, None
 
 
-def ag_linear(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
-    return _FusedAGLinear.apply(x, w, group)
+def ag_linear(x: torch.Tensor, w: torch.Tensor, group, rope=None) -> torch.Tensor:
+    return _FusedAGLinear.apply(x, w, group, rope)
 
 
 # ----------------------------------------------------------------------------- row parallel
@@ -179,16 +196,18 @@ def ag_linear(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
 
 class _FusedLinearRS(Function):
     @staticmethod
-    def forward(ctx, x, w, group):
+    def forward(ctx, x, w, group, residual=None):
         from ..comm import torch_backend as C
         from ..ops import functional as F
         heap = heap_for(group)
         ctx.group = group
         ctx.save_for_backward(x, w)
         x = x if x.stride(-1) == 1 else x.contiguous()
-        y = _scatter_gemm(heap, x, w, 0, x.shape[0], w.shape[0])
+        y = _scatter_gemm(heap, x, w, 0, x.shape[0], w.shape[0], residual=residual)
         if y is None:
             y = C.reduce_scatter_rows(F.gemm_nt(x, w), group)
+            if residual is not None:
+                y.add_(residual)
         return y
 
     @staticmethod
@@ -204,11 +223,11 @@ class _FusedLinearRS(Function):
             dy_full = C.all_gather_rows(dy, ctx.group)
             dx = F.gemm_nn(dy_full, w)
         dw = F.store_weight_grad(w, dy_full, x)
-        return dx, dw, None
+        return dx, dw, None, (dy if ctx.needs_input_grad[3] else None)
 
 
-def linear_rs(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
-    return _FusedLinearRS.apply(x, w, group)
+def linear_rs(x: torch.Tensor, w: torch.Tensor, group, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return _FusedLinearRS.apply(x, w, group, residual)
 
 
 # ----------------------------------------------------------------------------- ZeRO-3
@@ -235,20 +254,28 @@ def _chain(sched, heap, idx: int, step: int, w: torch.Tensor):
 
 class _FusedZero3Linear(Function):
     @staticmethod
-    def forward(ctx, x, w, group, sched, idx):
+    def forward(ctx, x, w, group, sched, idx, rope=None, residual=None):
         from ..comm import torch_backend as C
         from ..ops import functional as F
         heap = heap_for(group)
         ctx.group, ctx.sched, ctx.idx = group, sched, idx
         ctx.save_for_backward(x, w)
         x = x if x.stride(-1) == 1 else x.contiguous()
+        if residual is not None and residual.stride(-1) != 1:
+            residual = residual.contiguous()
         slot, nxt_w, nxt = _chain(sched, heap, idx, +1, w.detach())
-        y, full, nslot = _gather_gemm(heap, w.detach(), 2, x, 0, slot=slot, prefetch=nxt_w)
+        if rope is not None and not rope.in_kernel(w.shape[0] * heap.n):
+            # head_dim other than 128: the rotation is a pass of its own after the fused GEMM
+            y, full, nslot = _gather_gemm(heap, w.detach(), 2, x, 0, slot=slot, prefetch=nxt_w, residual=residual)
+            if y is not None:
+                F.apply_rope_epilogue_(y, rope)
+        else:
+            y, full, nslot = _gather_gemm(heap, w.detach(), 2, x, 0, slot=slot, prefetch=nxt_w, rope=rope, residual=residual)
         if nslot is not None:
             sched._fused_prefetched[nxt] = nslot
         if y is None:
             full = C.all_gather_rows(w.detach(), group)
-            y = F.gemm_nt(x, full)
+            y = F.gemm_nt(x, full, rope=rope, residual=residual)
         if sched is not None and sched.keep_gathered and any(ctx.needs_input_grad):
             # ZeRO-2 style (the reference's --use_zero2, train.py:137-141): the whole weight stays resident until
             # this layer's backward, which then needs no second gather.  The slot itself is recycled, so copy.
@@ -264,9 +291,10 @@ class _FusedZero3Linear(Function):
         heap = heap_for(group)
         dy = dy.contiguous()
         kept = sched._kept.pop(idx, None) if (sched is not None and sched.keep_gathered) else None
+        d_res = dy if ctx.needs_input_grad[6] else None
         if kept is not None:
             dx = F.gemm_nn(dy, kept) if ctx.needs_input_grad[0] else None
-            return dx, zero3_wgrad(heap, group, w, dy, x), None, None, None
+            return dx, zero3_wgrad(heap, group, w, dy, x), None, None, None, None, d_res
         slot, nxt_w, nxt = _chain(sched, heap, idx, -1, w.detach())
         dx = None
         if ctx.needs_input_grad[0] or slot is not None:
@@ -275,7 +303,7 @@ class _FusedZero3Linear(Function):
                 sched._fused_prefetched[nxt] = nslot
             if dx is None:
                 dx = F.gemm_nn(dy, C.all_gather_rows(w.detach(), group))
-        return dx, zero3_wgrad(heap, group, w, dy, x), None, None, None
+        return dx, zero3_wgrad(heap, group, w, dy, x), None, None, None, None, d_res
 
 
 def zero3_wgrad(heap, group, w, dy, x):
@@ -295,8 +323,9 @@ def zero3_wgrad(heap, group, w, dy, x):
     return F.deliver_grad(w, dw)
 
 
-def zero3_linear(x: torch.Tensor, w_shard: torch.Tensor, group, sched=None, idx: int = 0) -> torch.Tensor:
-    return _FusedZero3Linear.apply(x, w_shard, group, sched, idx)
+def zero3_linear(x: torch.Tensor, w_shard: torch.Tensor, group, sched=None, idx: int = 0, rope=None,
+                 residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return _FusedZero3Linear.apply(x, w_shard, group, sched, idx, rope, residual)
 
 
 # ----------------------------------------------------------------------------- zigzag ring attention

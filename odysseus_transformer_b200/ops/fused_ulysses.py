@@ -10,7 +10,8 @@ buffer over NVLink:
 exchange                   producer kernel
 =========================  ==========================================================================
 forward  q,k,v seq->head   QKV projection GEMM (ZeRO-3 weight gather fused as well): ``gemm_comm``
-                           with the all-to-all epilogue - column group ``u`` of a tile goes to rank ``u``
+                           with the all-to-all epilogue - column group ``u`` of a tile goes to rank ``u``,
+                           q and k rotated (RoPE) on the way out of the accumulator
 forward  o head->seq       attention forward: each CTA's output tile is stored to the rank owning those rows
 backward do seq->head      output-projection dgrad GEMM with the all-to-all epilogue
 backward dq,dk,dv          attention backward kernels store each gradient tile to the rank owning the rows
@@ -57,10 +58,11 @@ def _need(v, what: str):
     return v
 
 
-def _gather_w(heap, sched, idx, step, w, other, layout, scatter=None):
+def _gather_w(heap, sched, idx, step, w, other, layout, scatter=None, rope=None, residual=None):
     """ZeRO-3 weight gather fused with its GEMM (operand B), riding the prefetch chain of ``sched``."""
     slot, nxt_w, nxt = FC._chain(sched, heap, idx, step, w)
-    y, _, nslot = FC._gather_gemm(heap, w, 2, other, layout, slot=slot, prefetch=nxt_w, scatter=scatter)
+    y, _, nslot = FC._gather_gemm(heap, w, 2, other, layout, slot=slot, prefetch=nxt_w, scatter=scatter, rope=rope,
+                                  residual=residual)
     if nslot is not None:
         sched._fused_prefetched[nxt] = nslot
     return _need(y, "a weight gather buffer")
@@ -68,8 +70,8 @@ def _gather_w(heap, sched, idx, step, w, other, layout, scatter=None):
 
 class _FusedUlyssesAttention(Function):
     @staticmethod
-    def forward(ctx, x, wqkv, wo, cos, sin, mod):
-        from ..parallel.attention import _rope_inplace_
+    def forward(ctx, x, wqkv, wo, cos, sin, mod, residual=None):
+        from . import functional as F
         lib = native.lib()
         pc = mod.pctx
         heap_w, heap_a = FC.heap_for(pc.world_group), FC.heap_for(pc.inner_group)
@@ -85,12 +87,20 @@ class _FusedUlyssesAttention(Function):
         # 1. QKV projection; the epilogue scatters head group u to rank u (rows r*t.. of its [Tb, G] buffer)
         s_qkv = _need(heap_a.a2a_slot(Tb, G, "qkv"), "the q/k/v receive buffer")
         desc = s_qkv.gemm_desc(G, r * t, 0, FC._n_cta(heap_w, t, U * G))
-        _gather_w(heap_w, sched, iq, +1, wqkv.detach(), x, 0, scatter=desc)
+        in_gemm = F.epilogue_fusion("rope")
+        # q and k are rotated in the GEMM epilogue, at this rank's own token positions, before they cross the link
+        rope = F.RopeEpilogue(cos[r * t:(r + 1) * t], sin[r * t:(r + 1) * t], (hq + hkv) * 128, G) if in_gemm else None
+        _gather_w(heap_w, sched, iq, +1, wqkv.detach(), x, 0, scatter=desc, rope=rope)
         lib.wait_flags(flag_dev, s_qkv.arrived_local(), everyone, s_qkv.arrived_total)
-        qkv = s_qkv.local().clone()                     # kept for backward; the buffer is free again at once
+        # out of the receive buffer in one pass (rotating on the way when the epilogue did not); the copy is kept for
+        # backward and the buffer is free again at once
+        qkv3 = torch.empty(Tb, nh, 128, dtype=x.dtype, device=x.device)
+        if in_gemm:
+            qkv3.copy_(s_qkv.local().view(Tb, nh, 128))
+        else:
+            F.rope_grouped_(s_qkv.local().view(Tb, nh, 128), qkv3, hq + hkv, nh, cos, sin, False)
+        qkv = qkv3.view(Tb, G)
         lib.signal_flags(flag_dev, s_qkv.consumed_ptrs(), everyone, r, s_qkv.uses)
-        qkv3 = qkv.view(Tb, nh, 128)
-        _rope_inplace_(qkv3, hq + hkv, cos, sin, False)
         q, k, v = qkv3[:, :hq], qkv3[:, hq:hq + hkv], qkv3[:, hq + hkv:]
 
         scale = mod.head_dim ** -0.5
@@ -112,7 +122,9 @@ class _FusedUlyssesAttention(Function):
             lib.signal_flags(flag_dev, s_o.consumed_ptrs(), everyone, r, e_o)
 
         # 3. output projection (ZeRO-3 weight gather fused)
-        y = _gather_w(heap_w, sched, io, +1, wo.detach(), o_seq, 0)
+        if residual is not None and residual.stride(-1) != 1:
+            residual = residual.contiguous()
+        y = _gather_w(heap_w, sched, io, +1, wo.detach(), o_seq, 0, residual=residual)
         ctx.save_for_backward(x, wqkv, wo, cos, sin, qkv, o, lse, o_seq)
         ctx.mod = mod
         FC.stats["ulysses"] = FC.stats.get("ulysses", 0) + 1
@@ -120,7 +132,7 @@ class _FusedUlyssesAttention(Function):
 
     @staticmethod
     def backward(ctx, dy):
-        from ..parallel.attention import _rope_inplace_
+        from ..parallel.attention import _rope_grouped, _rope_inplace_
         x, wqkv, wo, cos, sin, qkv, o, lse, o_seq = ctx.saved_tensors
         mod = ctx.mod
         lib = native.lib()
@@ -170,18 +182,18 @@ class _FusedUlyssesAttention(Function):
             dqkv = s_dqkv.local()
             # inverse rotation of the dq / dk heads of every head group, at this rank's own token positions
             cos_l, sin_l = cos[r * t:(r + 1) * t], sin[r * t:(r + 1) * t]
-            by_group = dqkv.view(t, U, nh, 128)
-            for u in range(U):
-                _rope_inplace_(by_group[:, u], hq + hkv, cos_l, sin_l, True)
+            by_group = dqkv.view(t, U * nh, 128)
+            _rope_grouped(by_group, by_group, hq + hkv, nh, cos_l, sin_l, True)
 
         # 3. QKV projection backward, reading the receive buffer in place
         dx = _gather_w(heap_w, sched, iq, -1, wqkv.detach(), dqkv, 1)
         g_wqkv = FC.zero3_wgrad(heap_w, pc.world_group, wqkv, dqkv, x)
         if not hybrid:
             lib.signal_flags(flag_dev, s_dqkv.consumed_ptrs(), everyone, r, e)
-        return dx, g_wqkv, g_wo, None, None, None
+        return dx, g_wqkv, g_wo, None, None, None, (dy if ctx.needs_input_grad[6] else None)
 
 
-def attention_block(mod, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """``SequenceParallelAttention.forward`` on the fused path: x [t, d] local tokens -> [t, d]."""
-    return _FusedUlyssesAttention.apply(x, mod.qkv_proj.weight, mod.o_proj.weight, cos, sin, mod)
+def attention_block(mod, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, residual=None) -> torch.Tensor:
+    """``SequenceParallelAttention.forward`` on the fused path: x [t, d] local tokens -> [t, d] (+ residual, added in
+    the output projection's epilogue)."""
+    return _FusedUlyssesAttention.apply(x, mod.qkv_proj.weight, mod.o_proj.weight, cos, sin, mod, residual)

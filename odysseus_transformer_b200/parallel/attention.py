@@ -203,15 +203,19 @@ def _rope_inplace_(x3: torch.Tensor, n_rot: int, cos, sin, inverse: bool) -> Non
         x3[:, :n_rot] = torch_ref.rope_apply(x3[:, :n_rot], cos, sin, inverse)
 
 
+_rope_grouped = F.rope_grouped_
+
+
 class _PackedRopeAttention(Function):
     @staticmethod
-    def forward(ctx, qkv2d, cos, sin, hq, hkv, ring_group, scale):
+    def forward(ctx, qkv2d, cos, sin, hq, hkv, ring_group, scale, pre_rotated=False):
         Tb = qkv2d.shape[0]
         hd = qkv2d.shape[1] // (hq + 2 * hkv)
         # The producer of qkv2d (a GEMM) does not keep its output for backward, so rotating it in
         # place is invisible to autograd; the rotated tensor is what this op saves.
         qkv = qkv2d.detach().view(Tb, hq + 2 * hkv, hd)
-        _rope_inplace_(qkv, hq + hkv, cos, sin, False)
+        if not pre_rotated:
+            _rope_inplace_(qkv, hq + hkv, cos, sin, False)
         q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
         if C.group_size(ring_group) > 1:
             from ..ops import fused_comm
@@ -252,16 +256,19 @@ class _PackedRopeAttention(Function):
             dqkv[:, :hq] = dq
             dqkv[:, hq:hq + hkv] = dk
             dqkv[:, hq + hkv:] = dv
+        # also when the projection rotated q and k itself (pre_rotated): what goes back to it is the gradient of
+        # its product before the rotation
         _rope_inplace_(dqkv, hq + hkv, cos, sin, True)
-        return dqkv.view(Tb, -1), None, None, None, None, None, None
+        return dqkv.view(Tb, -1), None, None, None, None, None, None, None
 
 
 def packed_rope_attention(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, hq: int, hkv: int,
-                          ring_group=None, scale: Optional[float] = None) -> torch.Tensor:
+                          ring_group=None, scale: Optional[float] = None, pre_rotated: bool = False) -> torch.Tensor:
     """qkv [Tb, (hq + 2 hkv) * hd] laid out [q heads | k heads | v heads] per token, *consumed*
     (rotated in place).  cos/sin [Tb, hd/2] for the tokens' global positions.  Returns the
     attention output [Tb, hq * hd] of causal attention over the whole sequence (across
-    ``ring_group`` when given)."""
+    ``ring_group`` when given).  ``pre_rotated``: the projection that produced ``qkv`` already rotated q and k in its
+    epilogue (``parallel.linear.ag_linear(..., rope=...)``); the forward rotation is skipped, the backward one is not."""
     hd = qkv.shape[1] // (hq + 2 * hkv)
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
-    return _PackedRopeAttention.apply(qkv, cos, sin, hq, hkv, ring_group, scale)
+    return _PackedRopeAttention.apply(qkv, cos, sin, hq, hkv, ring_group, scale, pre_rotated)

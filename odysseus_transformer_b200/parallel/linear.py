@@ -158,15 +158,15 @@ def scatter_last_dim(x: torch.Tensor, group) -> torch.Tensor:
 
 class _AGLinear(Function):
     @staticmethod
-    def forward(ctx, x, w, group):
+    def forward(ctx, x, w, group, rope=None):
         ctx.group = group
         ctx.save_for_backward(x, w)           # only the LOCAL shard of the input is kept
         n = C.group_size(group)
         if n == 1:
-            return F.gemm_nt(x, w)
+            return F.gemm_nt(x, w, rope=rope)
         buf = get_global_memory_buffer().get_tensor((n * x.shape[0], x.shape[1]), x.dtype, "mpu", x.device)
         total = C.all_gather_rows(x, group, out=buf)
-        return F.gemm_nt(total, w)
+        return F.gemm_nt(total, w, rope=rope)
 
     @staticmethod
     def backward(ctx, dy):
@@ -176,7 +176,7 @@ class _AGLinear(Function):
         dy = dy.contiguous()
         if n == 1:
             dx = F.gemm_nn(dy, w)
-            return dx, F.store_weight_grad(w, dy, x), None
+            return dx, F.store_weight_grad(w, dy, x), None, None
         # re-gather the input while the dgrad GEMM runs
         buf = get_global_memory_buffer().get_tensor((n * x.shape[0], x.shape[1]), x.dtype, "mpu", x.device)
         total, work = C.all_gather_rows(x, group, out=buf, async_op=True)
@@ -188,15 +188,20 @@ class _AGLinear(Function):
         dw = F.store_weight_grad(w, dy, total)
         if work is not None:
             work.wait()
-        return dx, dw, None
+        return dx, dw, None, None
 
 
-def ag_linear(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
-    """x [T/n, in] (sequence shard), w [out_local, in] -> [T, out_local]."""
+def ag_linear(x: torch.Tensor, w: torch.Tensor, group, rope=None) -> torch.Tensor:
+    """x [T/n, in] (sequence shard), w [out_local, in] -> [T, out_local].
+
+    ``rope`` (``ops.functional.RopeEpilogue``, tables for the T gathered rows): the product is a packed q|k|v
+    projection and leaves the GEMM with its q / k heads rotated.  The op's backward still takes the gradient of the
+    product BEFORE the rotation: whoever consumes the rotated product undoes the rotation on the gradient it returns
+    (``parallel.attention.packed_rope_attention(..., pre_rotated=True)`` does)."""
     from ..ops import fused_comm
     if fused_comm.enabled(x, group):
-        return fused_comm.ag_linear(x, w, group)
-    return _AGLinear.apply(x, w, group)
+        return fused_comm.ag_linear(x, w, group, rope)
+    return _AGLinear.apply(x, w, group, rope)
 
 
 # ----------------------------------------------------------------------------- GEMM -> RS (row parallel)
@@ -204,31 +209,37 @@ def ag_linear(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
 
 class _LinearRS(Function):
     @staticmethod
-    def forward(ctx, x, w, group):
+    def forward(ctx, x, w, group, residual=None):
         ctx.group = group
         ctx.save_for_backward(x, w)
-        y = F.gemm_nt(x, w)
-        return C.reduce_scatter_rows(y, group)
+        if C.group_size(group) == 1:
+            return F.gemm_nt(x, w, residual=residual)
+        y = C.reduce_scatter_rows(F.gemm_nt(x, w), group)
+        return y if residual is None else y.add_(residual)
 
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         n = C.group_size(ctx.group)
         dy = dy.contiguous()
+        d_res = dy if ctx.needs_input_grad[3] else None      # the residual's gradient is the local rows' gradient itself
         if n > 1:
             buf = get_global_memory_buffer().get_tensor((n * dy.shape[0], dy.shape[1]), dy.dtype, "mpu", dy.device)
             dy = C.all_gather_rows(dy, ctx.group, out=buf)
         dx = F.gemm_nn(dy, w)
         dw = F.store_weight_grad(w, dy, x)
-        return dx, dw, None
+        return dx, dw, None, d_res
 
 
-def linear_rs(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
-    """x [T, in_local], w [out, in_local] -> [T/n, out] (sum over ranks, scattered on rows)."""
+def linear_rs(x: torch.Tensor, w: torch.Tensor, group, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, in_local], w [out, in_local] -> [T/n, out] (sum over ranks, scattered on rows).
+
+    ``residual`` [T/n, out]: added to this rank's rows where they are reduced (the residual stream joins the block's
+    output in the producing kernel instead of in the next normalisation)."""
     from ..ops import fused_comm
     if fused_comm.enabled(x, group):
-        return fused_comm.linear_rs(x, w, group)
-    return _LinearRS.apply(x, w, group)
+        return fused_comm.linear_rs(x, w, group, residual)
+    return _LinearRS.apply(x, w, group, residual)
 
 
 # ----------------------------------------------------------------------------- ZeRO-3 linear
@@ -300,18 +311,18 @@ class Zero3Schedule:
 
 class _Zero3Linear(Function):
     @staticmethod
-    def forward(ctx, x, w, group, sched, idx):
+    def forward(ctx, x, w, group, sched, idx, rope=None, residual=None):
         ctx.group, ctx.sched, ctx.idx = group, sched, idx
         ctx.save_for_backward(x, w)           # the SHARD is saved, never the gathered weight
         n = C.group_size(group)
         if n == 1:
-            return F.gemm_nt(x, w)
+            return F.gemm_nt(x, w, rope=rope, residual=residual)
         if sched is not None:
             full = sched.fetch(idx, +1)
         else:
             buf = get_global_memory_buffer().get_tensor((n * w.shape[0], w.shape[1]), w.dtype, "mpu", w.device)
             full = C.all_gather_rows(w, group, out=buf)
-        return F.gemm_nt(x, full)
+        return F.gemm_nt(x, full, rope=rope, residual=residual)
 
     @staticmethod
     def backward(ctx, dy):
@@ -319,9 +330,10 @@ class _Zero3Linear(Function):
         group, sched, idx = ctx.group, ctx.sched, ctx.idx
         n = C.group_size(group)
         dy = dy.contiguous()
+        d_res = dy if ctx.needs_input_grad[6] else None
         if n == 1:
             dx = F.gemm_nn(dy, w) if ctx.needs_input_grad[0] else None
-            return dx, F.store_weight_grad(w, dy, x), None, None, None
+            return dx, F.store_weight_grad(w, dy, x), None, None, None, None, d_res
         if sched is not None:
             full = sched.fetch(idx, -1)
         else:
@@ -352,19 +364,20 @@ class _Zero3Linear(Function):
                 first.wait()
                 w._grad_work = None
             dw = F.deliver_grad(w, C.reduce_scatter_rows(gfull, group))
-        return dx, dw, None, None, None
+        return dx, dw, None, None, None, None, d_res
 
 
 _SLOT_WORK = {}
 
 
 def zero3_linear(x: torch.Tensor, w_shard: torch.Tensor, group, sched: Optional[Zero3Schedule] = None,
-                 idx: int = 0) -> torch.Tensor:
-    """x [T, in] local tokens, w_shard [out/n, in] -> [T, out]."""
+                 idx: int = 0, rope=None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, in] local tokens, w_shard [out/n, in] -> [T, out].  ``rope`` as in ``ag_linear`` (tables for the T local
+    rows), ``residual`` [T, out] as in ``linear_rs``: both are applied in the GEMM epilogue."""
     from ..ops import fused_comm
     if fused_comm.enabled(x, group):
-        return fused_comm.zero3_linear(x, w_shard, group, sched, idx)
-    return _Zero3Linear.apply(x, w_shard, group, sched, idx)
+        return fused_comm.zero3_linear(x, w_shard, group, sched, idx, rope, residual)
+    return _Zero3Linear.apply(x, w_shard, group, sched, idx, rope, residual)
 
 
 class _Zero3Embedding(Function):
@@ -440,9 +453,12 @@ class ColumnParallelLinearAG(nn.Module):
         if self.keep_master_weight_for_test:
             self.master_weight = master.detach().clone()
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, rope=None) -> torch.Tensor:
+        """``rope``: see ``ag_linear``; only the sequence-parallel, bias-free form the model blocks use takes it."""
+        if rope is not None and (not self.sequence_parallel or self.bias is not None or self.gather_output):
+            raise ValueError("the rotary epilogue needs the sequence-parallel projection without bias or output gather")
         if self.sequence_parallel:
-            y = ag_linear(x, self.weight, self.group)
+            y = ag_linear(x, self.weight, self.group, rope)
         else:
             y = F.linear(_CopyToRegion.apply(x, self.group), self.weight)
         if self.bias is not None:
@@ -487,13 +503,18 @@ class RowParallelLinearRS(nn.Module):
         if self.keep_master_weight_for_test:
             self.master_weight = master.detach().clone()
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``residual`` (this rank's output rows): added to the result, inside the kernel on the sequence-parallel path."""
         if not self.input_is_parallel:
             x = scatter_last_dim(x, self.group)
         if self.sequence_parallel:
-            y = linear_rs(x, self.weight, self.group)
+            y = linear_rs(x, self.weight, self.group, residual if self.bias is None else None)
+            if self.bias is not None and residual is not None:
+                y = y + residual
         else:
             y = _ReduceFromRegion.apply(F.linear(x, self.weight), self.group)
+            if residual is not None:
+                y = y + residual
         if self.bias is not None:
             y = y + self.bias
         return y
@@ -517,8 +538,8 @@ class LinearZeRO3(nn.Module):
         self.weight = nn.Parameter(torch.empty(out_features // n, in_features, dtype=dtype, device=device))
         self.idx = sched.register(self.weight, group) if sched is not None else 0
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return zero3_linear(x, self.weight, self.group, self.sched, self.idx)
+    def forward(self, x: torch.Tensor, rope=None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return zero3_linear(x, self.weight, self.group, self.sched, self.idx, rope, residual)
 
     def get_master_weight(self) -> torch.Tensor:
         return C.all_gather_rows(self.weight.detach(), self.group)

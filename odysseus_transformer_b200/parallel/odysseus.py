@@ -29,8 +29,9 @@ class OdysseusMLP(nn.Module):
         self.gate_up_proj = LinearZeRO3(cfg.hidden_size, 2 * cfg.intermediate_size, g, sched, dtype=dtype, device=device)
         self.down_proj = LinearZeRO3(cfg.intermediate_size, cfg.hidden_size, g, sched, dtype=dtype, device=device)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(F.swiglu(self.gate_up_proj(x)))
+    def forward(self, x: torch.Tensor, residual=None) -> torch.Tensor:
+        """``residual`` [T/N, d]: added to the block's output inside the down projection's kernel."""
+        return self.down_proj(F.swiglu(self.gate_up_proj(x)), residual=residual)
 
     def hf_load(self, get, prefix: str) -> None:
         r, n = self.pctx.rank if self.pctx.world_group is not None else 0, max(1, self.pctx.world_size)
@@ -71,8 +72,9 @@ class ReplicatedMLP(nn.Module):
             for p in self.parameters():
                 p.grad_sync_group = ctx.world_group
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return F.linear(F.swiglu(F.linear(x, self.gate_up_proj)), self.down_proj)
+    def forward(self, x: torch.Tensor, residual=None) -> torch.Tensor:
+        y = F.linear(F.swiglu(F.linear(x, self.gate_up_proj)), self.down_proj)
+        return y if residual is None else y + residual
 
     def hf_load(self, get, prefix: str) -> None:
         with torch.no_grad():

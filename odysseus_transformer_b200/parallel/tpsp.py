@@ -52,15 +52,21 @@ class TPSPAttention(nn.Module):
             for p in self.parameters():
                 p.grad_sync_group = ctx.ring_group
 
-    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-        """x [T/N, d] local shard; cos/sin for the positions of this rank's ring block [T/R, hd/2]."""
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, residual=None) -> torch.Tensor:
+        """x [T/N, d] local shard; cos/sin for the positions of this rank's ring block [T/R, hd/2].
+        ``residual`` [T/N, d]: added to the block's output inside the output projection's kernel."""
+        hq, hkv, hd = self.n_local_heads, self.n_local_kv_heads, self.head_dim
+        rope = None
         if self.pack_weight:
-            qkv = self.qkv_proj(x)                               # [Tb, (hq + 2 hkv) * hd]
+            if F.epilogue_fusion("rope"):
+                # q and k leave the projection rotated (GEMM epilogue); the attention op skips its own rotation
+                rope = F.RopeEpilogue(cos, sin, (hq + hkv) * hd, (hq + 2 * hkv) * hd)
+            qkv = self.qkv_proj(x, rope=rope)                    # [Tb, (hq + 2 hkv) * hd]
         else:
             qkv = torch.cat([self.q_proj(x), self.k_proj(x), self.v_proj(x)], dim=-1)
-        o = packed_rope_attention(qkv, cos, sin, self.n_local_heads, self.n_local_kv_heads,
-                                  self.pctx.ring_group)          # [Tb, hq * hd]
-        return self.o_proj(o)                                    # [T/N, d]
+        o = packed_rope_attention(qkv, cos, sin, hq, hkv, self.pctx.ring_group,
+                                  pre_rotated=rope is not None)  # [Tb, hq * hd]
+        return self.o_proj(o, residual=residual)                 # [T/N, d]
 
     # -- HF state-dict <-> shard
     def hf_load(self, get: Callable[[str], torch.Tensor], prefix: str) -> None:
@@ -104,8 +110,8 @@ class TPSPMLP(nn.Module):
                                            dtype=dtype, device=device)
         self.w2 = RowParallelLinearRS(self.i_local, cfg.hidden_size, ctx.inner_group, dtype=dtype, device=device)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.w2(F.swiglu(self.w1w3(x)))
+    def forward(self, x: torch.Tensor, residual=None) -> torch.Tensor:
+        return self.w2(F.swiglu(self.w1w3(x)), residual=residual)
 
     def hf_load(self, get, prefix: str) -> None:
         u, il = self.pctx.inner_rank, self.i_local

@@ -15,6 +15,7 @@ import torch
 import torch.nn as nn
 
 from ..comm import torch_backend as C
+from ..ops import functional as F
 from .attention import head_to_seq, packed_rope_attention, seq_to_head
 from .linear import LinearZeRO3
 
@@ -31,20 +32,28 @@ class SequenceParallelAttention(nn.Module):
         self.qkv_proj = LinearZeRO3(cfg.hidden_size, cfg.q_size + 2 * cfg.kv_size, g, sched, dtype=dtype, device=device)
         self.o_proj = LinearZeRO3(cfg.q_size, cfg.hidden_size, g, sched, dtype=dtype, device=device)
 
-    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-        """x [t, d] local tokens; cos/sin for the positions of this rank's ring block [U*t, hd/2]."""
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, residual=None) -> torch.Tensor:
+        """x [t, d] local tokens; cos/sin for the positions of this rank's ring block [U*t, hd/2].
+        ``residual`` [t, d]: added to the block's output inside the output projection's kernel."""
         U, hd = self.pctx.inner_size, self.head_dim
         t = x.shape[0]
         if U > 1 and x.is_cuda:
             from ..ops import fused_ulysses
             if fused_ulysses.available(self, x):
                 # all four sequence<->head exchanges happen inside the GEMM / attention kernels
-                return fused_ulysses.attention_block(self, x, cos, sin)
-        qkv = self.qkv_proj(x)                                                   # [t, U*(hq+2hkv)*hd]
+                return fused_ulysses.attention_block(self, x, cos, sin, residual)
+        rope = None
+        if F.epilogue_fusion("rope"):
+            # q and k leave the projection rotated, at the positions of this rank's own tokens inside the block
+            r = self.pctx.inner_rank if U > 1 else 0
+            nh = self.hq + 2 * self.hkv
+            rope = F.RopeEpilogue(cos[r * t:(r + 1) * t], sin[r * t:(r + 1) * t], (self.hq + self.hkv) * hd, nh * hd)
+        qkv = self.qkv_proj(x, rope=rope)                                        # [t, U*(hq+2hkv)*hd]
         qkv = seq_to_head(qkv.view(t, U * (self.hq + 2 * self.hkv), hd), self.pctx.inner_group)
-        o = packed_rope_attention(qkv.reshape(U * t, -1), cos, sin, self.hq, self.hkv, self.pctx.ring_group)
+        o = packed_rope_attention(qkv.reshape(U * t, -1), cos, sin, self.hq, self.hkv, self.pctx.ring_group,
+                                  pre_rotated=rope is not None)
         o = head_to_seq(o.view(U * t, self.hq, hd), self.pctx.inner_group)       # [t, H, hd]
-        return self.o_proj(o.reshape(t, -1))
+        return self.o_proj(o.reshape(t, -1), residual=residual)
 
     def _packed_full(self, get, prefix):
         U, hd, hq, hkv = self.pctx.inner_size, self.head_dim, self.hq, self.hkv

@@ -58,6 +58,58 @@ def test_gemm(lib, gemm_variant, layout, M, N, K):
     assert rel < 5e-3, f"layout {layout} {M}x{N}x{K}: rel err {rel}"
 
 
+@pytest.mark.parametrize("M", [300, 1024])
+def test_gemm_rope_epilogue(lib, gemm_variant, M):
+    """q|k|v projection whose epilogue rotates the q and k heads, against the fp32 product rotated in PyTorch."""
+    from odysseus_transformer_b200.ops import torch_ref as R
+    hq, hkv, hd, groups, K = 3, 1, 128, 2, 320
+    nh = hq + 2 * hkv
+    N = groups * nh * hd
+    torch.manual_seed(M)
+    a, b = _rand(M, K), _rand(N, K)
+    pos = torch.randint(0, 100000, (M,), device="cuda")
+    cos, sin = R.rope_tables(pos, hd, 10000.0)
+    got = lib.gemm(a, b, None, 0, False, (cos, sin, (hq + hkv) * hd, nh * hd), None)
+    _check_status(lib)
+    want = (a.float() @ b.float().t()).view(M, groups, nh, hd).clone()
+    for g in range(groups):
+        want[:, g, :hq + hkv] = R.rope_apply(want[:, g, :hq + hkv], cos, sin, False)
+    want = want.view(M, N)
+    rel = (got.float() - want).norm() / want.norm()
+    assert rel < 5e-3, rel
+    # the v heads are the plain product, bit for bit
+    plain = lib.gemm(a, b, None, 0, False)
+    assert torch.equal(got.view(M, groups, nh, hd)[:, :, hq + hkv:], plain.view(M, groups, nh, hd)[:, :, hq + hkv:])
+    assert not torch.equal(got.view(M, groups, nh, hd)[:, :, :hq], plain.view(M, groups, nh, hd)[:, :, :hq])
+    # descriptions the kernel cannot take are refused before a launch
+    with pytest.raises(RuntimeError):
+        lib.gemm(a, b, None, 0, False, (cos[:-1], sin[:-1], (hq + hkv) * hd, nh * hd), None)      # a row short
+    with pytest.raises(RuntimeError):
+        lib.gemm(a, b, None, 0, False, (cos, sin, (hq + hkv) * hd, nh * hd + 64), None)          # period not whole heads
+    with pytest.raises(RuntimeError):
+        lib.gemm(a, b, None, 0, False, (cos.double(), sin.double(), (hq + hkv) * hd, nh * hd), None)
+    with pytest.raises(RuntimeError):
+        lib.gemm(a.t().contiguous(), b.t().contiguous(), None, 2, False, (cos, sin, (hq + hkv) * hd, nh * hd), None)
+
+
+def test_gemm_residual_epilogue(lib, gemm_variant):
+    M, N, K = 520, 640, 256
+    a, b = _rand(M, K), _rand(N, K)
+    wide = _rand(M, 2 * N)
+    res = wide[:, N:]                          # strided residual rows
+    out = lib.gemm(a, b, None, 0, False, None, res)
+    _check_status(lib)
+    ref = a.float() @ b.float().t() + res.float()
+    assert ((out.float() - ref).norm() / ref.norm()) < 5e-3
+    assert torch.equal(wide[:, N:], res)       # the residual itself is only read
+    with pytest.raises(RuntimeError):
+        lib.gemm(a, b, out, 0, True, None, res)                 # accumulate and residual exclude each other
+    with pytest.raises(RuntimeError):
+        lib.gemm(a, b, None, 0, False, None, res[:-1])          # wrong shape
+    with pytest.raises(RuntimeError):
+        lib.gemm(a, b, None, 0, False, None, res.float())       # wrong dtype
+
+
 def test_gemm_accumulate_and_strided_out(lib, gemm_variant):
     M, N, K = 512, 384, 256
     a, b = _rand(K, M), _rand(K, N)
@@ -123,6 +175,41 @@ def test_rope(lib):
     ref[:, :3] = R.rope_apply(view[:, :3], cr, sr, False)
     lib.rope_inplace_(view, 3, cr, sr, False)
     torch.testing.assert_close(view.float(), ref.float(), rtol=1e-2, atol=1e-2)
+
+
+def test_rope_grouped(lib):
+    """Grouped rotation (first n_rot heads of every group of `period`), in place and as a copy, against fp32 PyTorch."""
+    from odysseus_transformer_b200.ops import torch_ref as R
+    T, groups, period, n_rot, hd = 389, 3, 5, 3, 128
+    pos = torch.randint(0, 50000, (T,), device="cuda")
+    cr, sr = R.rope_tables(pos, hd, 10000.0)
+    x = _rand(T, groups * period, hd)
+    want = x.float().view(T, groups, period, hd).clone()
+    rot = R.rope_apply(x.view(T, groups, period, hd)[:, :, :n_rot].reshape(T, groups * n_rot, hd).float(), cr, sr, False)
+    want[:, :, :n_rot] = rot.view(T, groups, n_rot, hd)
+    want = want.view(T, groups * period, hd)
+    out = torch.full_like(x, float("nan"))
+    lib.rope_grouped_(x, out, n_rot, period, cr, sr, False)
+    torch.testing.assert_close(out.float(), want, rtol=1e-2, atol=1e-2)
+    # the heads that are not rotated are copied bit for bit
+    assert torch.equal(out.view(T, groups, period, hd)[:, :, n_rot:], x.view(T, groups, period, hd)[:, :, n_rot:])
+    inplace = x.clone()
+    lib.rope_grouped_(inplace, inplace, n_rot, period, cr, sr, False)
+    assert torch.equal(inplace, out)
+    lib.rope_grouped_(inplace, inplace, n_rot, period, cr, sr, True)
+    torch.testing.assert_close(inplace.float(), x.float(), rtol=2e-2, atol=3e-2)
+    # strided source rows (a slice of a wider buffer) into a packed destination
+    wide = _rand(T, 2 * groups * period * hd)
+    src = wide[:, :groups * period * hd].unflatten(1, (groups * period, hd))
+    out2 = torch.empty(T, groups * period, hd, device="cuda", dtype=torch.bfloat16)
+    lib.rope_grouped_(src, out2, n_rot, period, cr, sr, False)
+    ref2 = torch.empty_like(out2)
+    lib.rope_grouped_(src.contiguous(), ref2, n_rot, period, cr, sr, False)
+    assert torch.equal(out2, ref2)
+    with pytest.raises(RuntimeError):
+        lib.rope_grouped_(x, out, n_rot, 4, cr, sr, False)        # 15 heads are not groups of 4
+    with pytest.raises(RuntimeError):
+        lib.rope_grouped_(x, out[:, :5], n_rot, period, cr, sr, False)
 
 
 def test_swiglu(lib):
