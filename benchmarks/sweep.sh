@@ -7,7 +7,8 @@
 # Every run appends its per-step records and a final record (tokens/s from max-over-ranks device time, peak GB,
 # exposed communication ms) to $OUT; a run that does not fit prints "OOM", as the reference's tables do.
 # HYBRID=1 adds Llama-3-8B at 256K on the Odysseus x ring and Ulysses x ring hybrids (inner degree 4, ring degree 2,
-# activation checkpointing on: 32K tokens per GPU do not fit otherwise).
+# activation checkpointing on: 32K tokens per GPU do not fit otherwise).  EXTRA holds further train.py flags for the
+# sweep runs, e.g. EXTRA="--grad-checkpoint" where the tokens per GPU need it.
 GPU_NUM=${GPU_NUM:-8}
 SEQLENS=${SEQLENS:-"32768 65536 131072"}
 MODES=${MODES:-"odysseus tpsp ulysses ring"}
@@ -41,7 +42,7 @@ run() {   # mode seqlen extra-args...
 
 for L in $SEQLENS; do
   for mode in $MODES; do
-    run $mode $L
+    run $mode $L $EXTRA
   done
 done
 if [ "${HYBRID:-0}" = "1" ]; then
