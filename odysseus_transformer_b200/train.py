@@ -237,6 +237,14 @@ def main(args) -> Dict[str, float]:
               f"backend {native.get_backend()}")
         m = memory_gb(dev)
         print(f"After init model and optimizer, CUDA memory allocated: {m['allocated']:.2f} GB, reserved: {m['reserved']:.2f} GB")
+        if args.parallel_mode in ("odysseus", "tpsp", "ulysses", "ring") and args.seq_length % world == 0:
+            from .utils.memory import estimate_memory
+            est = estimate_memory(cfg, args.parallel_mode, args.seq_length, world, trainer.ctx.inner_size, trainer.ctx.ring_size,
+                                  args.grad_checkpoint, trainer.loss_chunk_rows, args.use_ody_zero3,
+                                  native.get_backend() == "fused")
+            print(f"Estimated peak allocated: {est['peak_allocated']:.1f} GB (states {est['states']:.1f}, saved activations "
+                  f"{est['saved_activations']:.1f}, logits {est['logits']:.1f}, backward transients "
+                  f"{est['backward_transients']:.1f}); communication heap {est['comm_heap']:.1f} GB on top")
     hb = None
     if world > 1 and args.heartbeat_timeout > 0:
         hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world, args.heartbeat_timeout)
