@@ -7,7 +7,8 @@
 # Every run appends its per-step records and a final record (tokens/s from max-over-ranks device time, peak GB,
 # exposed communication ms) to $OUT; a run that does not fit prints "OOM", as the reference's tables do.
 # HYBRID=1 adds Llama-3-8B at 256K on the Odysseus x ring and Ulysses x ring hybrids (inner degree 4, ring degree 2,
-# activation checkpointing on: 32K tokens per GPU do not fit otherwise).  EXTRA holds further train.py flags for the
+# activation checkpointing on: 32K tokens per GPU do not fit otherwise; HYBRID_L / HYBRID_U / HYBRID_R change the sequence
+# length and the two degrees, e.g. 131072 on 2 x 2 GPUs).  EXTRA holds further train.py flags for the
 # sweep runs, e.g. EXTRA="--grad-checkpoint" where the tokens per GPU need it.
 GPU_NUM=${GPU_NUM:-8}
 SEQLENS=${SEQLENS:-"32768 65536 131072"}
@@ -48,6 +49,6 @@ done
 if [ "${HYBRID:-0}" = "1" ]; then
   MODEL=llama3-8b
   for mode in odysseus ulysses; do
-    run $mode 262144 --ulysses-degree 4 --ring-degree 2 --grad-checkpoint
+    run $mode ${HYBRID_L:-262144} --ulysses-degree ${HYBRID_U:-4} --ring-degree ${HYBRID_R:-2} --grad-checkpoint
   done
 fi

@@ -262,6 +262,11 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         return true;
       };
       if (ok && total > 0) ok = issue_s(0) && issue_dp(0);
+      // One thread issues all four products of a block.  Measured and not kept: two issuing warps on two schedulers
+      // (warp 1: dV(it), S^T(it+1); warp 2: dK(it), dP^T(it+1); the same split in the dQ kernel: S by one warp, dQ and dP
+      // by the other).  A lone issuing warp is slowed by the softmax warps of its scheduler (an instruction every 95 - 115
+      // cycles where the pipe takes one every 64), but with two queues the pipe interleaves their instructions and every
+      // product completes later: 688 / 800 / 779 TFLOP/s against 752 / 879 / 855 for the single ordered stream.
       // The tensor pipe executes in issue order, so S^T(it+1) may overwrite P^T(it) once dV(it) has been issued,
       // and dP^T(it+1) may overwrite dS^T(it) once dK(it) has.  While the softmax warps turn dP^T(it) into
       // dS^T(it) the pipe runs dV(it) and S^T(it+1); while they turn S^T(it+1) into P^T(it+1) it runs dK(it)

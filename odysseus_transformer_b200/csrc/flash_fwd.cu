@@ -196,6 +196,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     } else if (warp == 1) {
       // ------------------------------------------------------------------ MMA issuer
+      // One issuing thread for both tiles.  Fed back to back a tcgen05.mma of this shape takes 64 cycles (a probe that issues
+      // nothing else: every operand form, with or without tcgen05.ld traffic), but a warp that shares its scheduler with
+      // busy softmax warps gets an instruction out only every 90 - 97 cycles (the same probe with eight arithmetic warps),
+      // which is what the 16 instructions of a tile's chain cost here.  Measured and not kept: one issuing warp per tile
+      // (the tiles fall into step: both compute exponentials, then both wait for the pipe; 758 against 1007 TFLOP/s), and
+      // issuing a tile's chain from its own softmax warp with a token that makes the tiles take turns (893: that warp
+      // still shares its scheduler with the other tile's softmax warp).  The single issuer also keeps the tiles out of
+      // step, which is what lets one tile's MMAs run under the other tile's exponentials.  Pausing the softmax warps so
+      // that the scheduler turns to the issuing warp (nanosleep 0 every 16 / every 4 exponential pairs) brings the probe's
+      // issue rate to 71 cycles but costs the softmax warps more than it gains here: 915 / 727 TFLOP/s.
       if (lane == 0) {
         constexpr uint32_t IDESC_QK = make_idesc_bf16(BM, BN, 0, 0);
         constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
