@@ -220,7 +220,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // every lane runs the control flow, so the compiler keeps descriptors and loop state in uniform registers;
+      // one elected lane issues the tcgen05 instructions (see the note on the issue rate in flash_fwd.cu)
+      const bool leader = elect_one();
       constexpr uint32_t IDESC_S = make_idesc_bf16(BIG, BLK, 0, 0);
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BIG, HD, 0, 1);
       bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
@@ -239,10 +242,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
-          umma_ss(tmem + COL_ST, desc_advance(kdesc0, off), desc_advance(qd, off), IDESC_S, kk > 0 ? 1u : 0u);
+          if (leader) umma_ss(tmem + COL_ST, desc_advance(kdesc0, off), desc_advance(qd, off), IDESC_S, kk > 0 ? 1u : 0u);
         }
-        umma_ss(tmem + COL_ST, ones_d, desc_advance(stat_d0, stage * STAT_BYTES), IDESC_S, 1u);
-        umma_commit(&bars->s_full);
+        if (leader) umma_ss(tmem + COL_ST, ones_d, desc_advance(stat_d0, stage * STAT_BYTES), IDESC_S, 1u);
+        if (leader) umma_commit(&bars->s_full);
         return true;
       };
       // dP^T(it) = V dO^T: waits for the dO block
@@ -254,19 +257,19 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
-          umma_ss(tmem + COL_DPT, desc_advance(vdesc0, off), desc_advance(dd, off), IDESC_S, kk > 0 ? 1u : 0u);
+          if (leader) umma_ss(tmem + COL_DPT, desc_advance(vdesc0, off), desc_advance(dd, off), IDESC_S, kk > 0 ? 1u : 0u);
         }
         // dP^T - delta: the statistics tile of this block came with its Q block, which S^T(it) already waited for
-        umma_ss(tmem + COL_DPT, ones_d, desc_advance(stat_d0, stage * STAT_BYTES + STAT_TILE), IDESC_S, 1u);
-        umma_commit(&bars->dp_full);
+        if (leader) umma_ss(tmem + COL_DPT, ones_d, desc_advance(stat_d0, stage * STAT_BYTES + STAT_TILE), IDESC_S, 1u);
+        if (leader) umma_commit(&bars->dp_full);
         return true;
       };
       if (ok && total > 0) ok = issue_s(0) && issue_dp(0);
-      // One thread issues all four products of a block.  Measured and not kept: two issuing warps on two schedulers
-      // (warp 1: dV(it), S^T(it+1); warp 2: dK(it), dP^T(it+1); the same split in the dQ kernel: S by one warp, dQ and dP
-      // by the other).  A lone issuing warp is slowed by the softmax warps of its scheduler (an instruction every 95 - 115
-      // cycles where the pipe takes one every 64), but with two queues the pipe interleaves their instructions and every
-      // product completes later: 688 / 800 / 779 TFLOP/s against 752 / 879 / 855 for the single ordered stream.
+      // One warp issues all four products of a block (every lane runs the loop, one elected lane issues: see the note in
+      // flash_fwd.cu; 752 -> 797 and 879 -> 930 TFLOP/s for the two backward kernels together).  Measured before that and
+      // not kept: two issuing warps on two schedulers (warp 1: dV(it), S^T(it+1); warp 2: dK(it), dP^T(it+1); the same
+      // split in the dQ kernel): with two queues the pipe interleaves their instructions and every product completes
+      // later, 688 / 800 TFLOP/s.
       // The tensor pipe executes in issue order, so S^T(it+1) may overwrite P^T(it) once dV(it) has been issued,
       // and dP^T(it+1) may overwrite dS^T(it) once dK(it) has.  While the softmax warps turn dP^T(it) into
       // dS^T(it) the pipe runs dV(it) and S^T(it+1); while they turn S^T(it+1) into P^T(it+1) it runs dK(it)
@@ -282,21 +285,22 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint64_t dmn = desc_advance(d_mn0, stage * BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)      // dV += P^T dO
-          umma_ts(tmem + COL_DV, tmem + COL_ST + kk * 8, desc_advance(dmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
-        umma_commit(&bars->d_empty[stage]);
+          if (leader) umma_ts(tmem + COL_DV, tmem + COL_ST + kk * 8, desc_advance(dmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        if (leader) umma_commit(&bars->d_empty[stage]);
         if (it + 1 < total && !issue_s(it + 1)) { ok = false; break; }
         if (!mbar_wait(&bars->ds_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
         const uint64_t qmn = desc_advance(q_mn0, stage * BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)      // dK += dS^T Q
-          umma_ts(tmem + COL_DK, tmem + COL_DPT + kk * 8, desc_advance(qmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
-        umma_commit(&bars->q_empty[stage]);
+          if (leader) umma_ts(tmem + COL_DK, tmem + COL_DPT + kk * 8, desc_advance(qmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        if (leader) umma_commit(&bars->q_empty[stage]);
         if (it + 1 < total && !issue_dp(it + 1)) { ok = false; break; }
       }
-      if (ok) umma_commit(&bars->acc_done);
-      else {
-        umma_commit(&bars->drain);
+      if (ok) {
+        if (leader) umma_commit(&bars->acc_done);
+      } else {
+        if (leader) umma_commit(&bars->drain);
         const long long t0 = clock64();
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
       }
@@ -580,7 +584,10 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // every lane runs the control flow, so the compiler keeps descriptors and loop state in uniform registers;
+      // one elected lane issues the tcgen05 instructions (see the note on the issue rate in flash_fwd.cu)
+      const bool leader = elect_one();
       constexpr uint32_t IDESC_S = make_idesc_bf16(BIG, BLK, 0, 0);      // S^T, dP^T: both operands K-major
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BIG, HD, 0, 1);     // dV (A in TMEM), dK (A K-major): B MN-major
       constexpr uint32_t IDESC_DQ = make_idesc_bf16(BLK, HD, 1, 1);      // dQ_blk: A = dS MN-major, B = K MN-major
@@ -607,10 +614,10 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
-          umma_ss(tmem + COL_ST, desc_advance(kdesc0, off), desc_advance(qd, off), IDESC_S, kk > 0 ? 1u : 0u);
+          if (leader) umma_ss(tmem + COL_ST, desc_advance(kdesc0, off), desc_advance(qd, off), IDESC_S, kk > 0 ? 1u : 0u);
         }
-        umma_ss(tmem + COL_ST, ones_d, desc_advance(stat_d0, stage * STAT_BYTES), IDESC_S, 1u);
-        umma_commit(&bars->s_full);
+        if (leader) umma_ss(tmem + COL_ST, ones_d, desc_advance(stat_d0, stage * STAT_BYTES), IDESC_S, 1u);
+        if (leader) umma_commit(&bars->s_full);
         return true;
       };
       // dP^T(it) = V dO^T - delta: waits for the dO block (its statistics tile came with the Q block)
@@ -621,10 +628,10 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
           const uint32_t off = (kk >> 2) * BIG_HALF + (kk & 3) * 32;
-          umma_ss(tmem + COL_DPT, desc_advance(vdesc0, off), desc_advance(d_k, off), IDESC_S, kk > 0 ? 1u : 0u);
+          if (leader) umma_ss(tmem + COL_DPT, desc_advance(vdesc0, off), desc_advance(d_k, off), IDESC_S, kk > 0 ? 1u : 0u);
         }
-        umma_ss(tmem + COL_DPT, ones_d, desc_advance(stat_d0, stage * STAT_BYTES + STAT_TILE), IDESC_S, 1u);
-        umma_commit(&bars->dp_full);
+        if (leader) umma_ss(tmem + COL_DPT, ones_d, desc_advance(stat_d0, stage * STAT_BYTES + STAT_TILE), IDESC_S, 1u);
+        if (leader) umma_commit(&bars->dp_full);
         return true;
       };
       if (ok && total > 0) ok = issue_s(0) && issue_dp(0);
@@ -637,23 +644,23 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)      // dV += P^T dO
-          umma_ts(tmem + COL_DV, tmem + COL_ST + kk * 8, desc_advance(d_mn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
-        umma_commit(&bars->d_empty);               // dO(it) is free: the producer fetches dO(it+1)
+          if (leader) umma_ts(tmem + COL_DV, tmem + COL_ST + kk * 8, desc_advance(d_mn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        if (leader) umma_commit(&bars->d_empty);               // dO(it) is free: the producer fetches dO(it+1)
         if (it + 1 < total && !issue_s(it + 1)) { ok = false; break; }
         if (!mbar_wait(&bars->ds_full, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < BIG / 16; ++kk)      // dQ_blk = dS K   (k runs over the 128 kv rows)
-          umma_ss(tmem + COL_DPT, desc_advance(ds_mn, kk * 2048), desc_advance(k_mn, kk * 2048), IDESC_DQ, kk > 0 ? 1u : 0u);
-        umma_commit(&bars->dq_full);
+          if (leader) umma_ss(tmem + COL_DPT, desc_advance(ds_mn, kk * 2048), desc_advance(k_mn, kk * 2048), IDESC_DQ, kk > 0 ? 1u : 0u);
+        if (leader) umma_commit(&bars->dq_full);
         const uint64_t qmn = desc_advance(q_mn0, stage * BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk) {    // dK += dS^T Q   (k runs over the 128 query rows)
           const uint32_t off = (kk >> 2) * BLK_HALF + (kk & 3) * 32;
-          umma_ss(tmem + COL_DK, desc_advance(ds_k, off), desc_advance(qmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+          if (leader) umma_ss(tmem + COL_DK, desc_advance(ds_k, off), desc_advance(qmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
         }
-        umma_commit(&bars->q_empty[stage]);
-        umma_commit(&bars->ds_free);               // the dS^T tile may be overwritten
+        if (leader) umma_commit(&bars->q_empty[stage]);
+        if (leader) umma_commit(&bars->ds_free);               // the dS^T tile may be overwritten
         if (it + 1 < total) {
           // dP^T(it+1) lands where dQ_blk(it) sits: the softmax warps must have drained it
           if (!mbar_wait(&bars->dq_free, par, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
@@ -661,9 +668,10 @@ flash_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           if (!issue_dp(it + 1)) { ok = false; break; }
         }
       }
-      if (ok) umma_commit(&bars->acc_done);
-      else {
-        umma_commit(&bars->drain);
+      if (ok) {
+        if (leader) umma_commit(&bars->acc_done);
+      } else {
+        if (leader) umma_commit(&bars->drain);
         const long long t0 = clock64();
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
       }
@@ -967,7 +975,10 @@ flash_bwd_dq_kernel(const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* _
       }
     }
    } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // every lane runs the control flow, so the compiler keeps descriptors and loop state in uniform registers;
+      // one elected lane issues the tcgen05 instructions (see the note on the issue rate in flash_fwd.cu)
+      const bool leader = elect_one();
       constexpr uint32_t IDESC_S = make_idesc_bf16(BIG, BLK, 0, 0);
       constexpr uint32_t IDESC_ACC = make_idesc_bf16(BIG, HD, 0, 1);
       bool ok = mbar_wait(&bars->a_ready, 0, abort_flag, err, ODY_ERR_TIMEOUT_TMEM_FULL);
@@ -983,8 +994,8 @@ flash_bwd_dq_kernel(const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* _
         const uint64_t kd = desc_advance(k_k0, stage * BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          umma_ts(tmem + COL_S, tmem + COL_QA + kk * 8, desc_advance(kd, (kk >> 2) * BLK_HALF + (kk & 3) * 32), IDESC_S, kk > 0 ? 1u : 0u);
-        umma_commit(&bars->s_full);
+          if (leader) umma_ts(tmem + COL_S, tmem + COL_QA + kk * 8, desc_advance(kd, (kk >> 2) * BLK_HALF + (kk & 3) * 32), IDESC_S, kk > 0 ? 1u : 0u);
+        if (leader) umma_commit(&bars->s_full);
         return true;
       };
       // dP(it) = dO V^T, dO from TMEM
@@ -995,9 +1006,9 @@ flash_bwd_dq_kernel(const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* _
         const uint64_t vd = desc_advance(v_k0, stage * BLK_BYTES);
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          umma_ts(tmem + COL_DP, tmem + COL_DOA + kk * 8, desc_advance(vd, (kk >> 2) * BLK_HALF + (kk & 3) * 32), IDESC_S, kk > 0 ? 1u : 0u);
-        umma_commit(&bars->v_empty[stage]);
-        umma_commit(&bars->dp_full);
+          if (leader) umma_ts(tmem + COL_DP, tmem + COL_DOA + kk * 8, desc_advance(vd, (kk >> 2) * BLK_HALF + (kk & 3) * 32), IDESC_S, kk > 0 ? 1u : 0u);
+        if (leader) umma_commit(&bars->v_empty[stage]);
+        if (leader) umma_commit(&bars->dp_full);
         return true;
       };
       if (ok && total > 0) ok = issue_s(0) && issue_dp(0);
@@ -1018,14 +1029,15 @@ flash_bwd_dq_kernel(const __nv_bfloat16* __restrict__ qg, const __nv_bfloat16* _
         const uint32_t acc0 = it > 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)   // dQ += dS K
-          umma_ts(tmem + COL_DQ, tmem + COL_DP + kk * 8, desc_advance(kmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
-        umma_commit(&bars->k_empty[it % K_STAGES]);
+          if (leader) umma_ts(tmem + COL_DQ, tmem + COL_DP + kk * 8, desc_advance(kmn, kk * 2048), IDESC_ACC, kk > 0 ? 1u : acc0);
+        if (leader) umma_commit(&bars->k_empty[it % K_STAGES]);
         // dP(it+1) overwrites dS(it), which the in-order pipe has consumed with dQ(it) by then
         if (it + 1 < total && !issue_dp(it + 1)) { ok = false; break; }
       }
-      if (ok) umma_commit(&bars->acc_done);
-      else {
-        umma_commit(&bars->drain);
+      if (ok) {
+        if (leader) umma_commit(&bars->acc_done);
+      } else {
+        if (leader) umma_commit(&bars->drain);
         const long long t0 = clock64();
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
       }

@@ -196,17 +196,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     } else if (warp == 1) {
       // ------------------------------------------------------------------ MMA issuer
-      // One issuing thread for both tiles.  Fed back to back a tcgen05.mma of this shape takes 64 cycles (a probe that issues
-      // nothing else: every operand form, with or without tcgen05.ld traffic), but a warp that shares its scheduler with
-      // busy softmax warps gets an instruction out only every 90 - 97 cycles (the same probe with eight arithmetic warps),
-      // which is what the 16 instructions of a tile's chain cost here.  Measured and not kept: one issuing warp per tile
-      // (the tiles fall into step: both compute exponentials, then both wait for the pipe; 758 against 1007 TFLOP/s), and
-      // issuing a tile's chain from its own softmax warp with a token that makes the tiles take turns (893: that warp
-      // still shares its scheduler with the other tile's softmax warp).  The single issuer also keeps the tiles out of
-      // step, which is what lets one tile's MMAs run under the other tile's exponentials.  Pausing the softmax warps so
-      // that the scheduler turns to the issuing warp (nanosleep 0 every 16 / every 4 exponential pairs) brings the probe's
-      // issue rate to 71 cycles but costs the softmax warps more than it gains here: 915 / 727 TFLOP/s.
-      if (lane == 0) {
+      // One issuing warp for both tiles.  Every lane runs the control flow and one elected lane issues the tcgen05
+      // instructions: with warp-uniform control flow the compiler keeps descriptors and loop state in uniform registers and
+      // an MMA costs a few instructions, where the same loop under `if (lane == 0)` is divergent code with many more
+      // instructions per MMA.  That matters because the pipe takes a 128 x 128 x 16 instruction every 64 cycles and the
+      // issuing warp shares its scheduler with softmax warps that rarely stall: measured with a probe
+      // (benchmarks/mma_issue_rate.cu), the single-lane form gets an instruction out every 99 cycles next to dense
+      // arithmetic warps, the elected-lane form every 64.  In this kernel the change is 1007 -> 1085 and 1161 -> 1250
+      // TFLOP/s.  Measured before it and not kept: one issuing warp per tile (the tiles fall into step: both compute
+      // exponentials, then both wait for the pipe; 758 TFLOP/s), a tile's chain issued from its own softmax warp with a
+      // token that makes the tiles take turns (893), and pauses in the softmax warps that hand the scheduler to the
+      // issuing warp (915).  The single issuer also keeps the tiles out of step, which is what lets one tile's MMAs run
+      // under the other tile's exponentials.
+      {
+        const bool leader = elect_one();
         constexpr uint32_t IDESC_QK = make_idesc_bf16(BM, BN, 0, 0);
         constexpr uint32_t IDESC_PV = make_idesc_bf16(BM, HD, 0, 1);
         uint64_t qdesc0 = KS32 ? make_smem_desc_sw32(smem_u32(sQ)) : make_smem_desc(smem_u32(sQ), 16, 1024);
@@ -218,22 +221,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           const uint64_t q = desc_advance(qdesc0, t * TILE_BYTES);
           const uint64_t k = desc_advance(kdesc0, (j & 1) * TILE_BYTES);
           const uint32_t d = tmem + COL_S + t * BN;
-          umma_ss(d, q, k, IDESC_QK, 0u);
+          if (leader) umma_ss(d, q, k, IDESC_QK, 0u);
 #pragma unroll
           for (int kk = 1; kk < HD / 16; ++kk) {
             const uint32_t off = KS32 ? kk * 4096 : (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-            umma_ss(d, desc_advance(q, off), desc_advance(k, off), IDESC_QK, 1u);
+            if (leader) umma_ss(d, desc_advance(q, off), desc_advance(k, off), IDESC_QK, 1u);
           }
-          umma_commit(&bars->s_full[t]);
+          if (leader) umma_commit(&bars->s_full[t]);
         };
         // O_t (+)= P_t V(j)
         auto issue_pv = [&](int t, int j) {
           const uint64_t v = desc_advance(vdesc0, (j & 1) * TILE_BYTES);
           const uint32_t pa = tmem + COL_S + t * BN;
           const uint32_t d = tmem + COL_O + t * HD;
-          umma_ts(d, pa, v, IDESC_PV, j > 0 ? 1u : 0u);
+          if (leader) umma_ts(d, pa, v, IDESC_PV, j > 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 1; kk < BN / 16; ++kk) umma_ts(d, pa + kk * 8, desc_advance(v, kk * 2048), IDESC_PV, 1u);
+          for (int kk = 1; kk < BN / 16; ++kk) if (leader) umma_ts(d, pa + kk * 8, desc_advance(v, kk * 2048), IDESC_PV, 1u);
         };
         ok = mbar_wait(&bars->q_full[0], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL) &&
              mbar_wait(&bars->k_full[0], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
@@ -244,7 +247,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             ok = mbar_wait(&bars->q_full[1], 0, abort_flag, err, ODY_ERR_TIMEOUT_FULL);
             if (ok) issue_qk(1, 0);
           }
-          umma_commit(&bars->k_empty[0]);
+          if (leader) umma_commit(&bars->k_empty[0]);
         }
         for (int j = 0; j < nblk && ok; ++j) {
           // keep the descriptor bases opaque: the compiler would otherwise hold every base + slice offset of the loop
@@ -273,15 +276,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
               issue_qk(t, j + 1);      // its commit on s_full[t] also covers the P V just issued
               ODY_FWD_STAMP(blockIdx.x == 0 && blockIdx.y == 0, j, 11 + t * 2);
             } else {
-              umma_commit(&bars->o_done[t]);
+              if (leader) umma_commit(&bars->o_done[t]);
             }
           }
           if (!ok) break;
-          umma_commit(&bars->v_empty[s]);
-          if (have_k1) umma_commit(&bars->k_empty[s1]);
+          if (leader) umma_commit(&bars->v_empty[s]);
+          if (have_k1 && leader) umma_commit(&bars->k_empty[s1]);
         }
         if (!ok) {
-          umma_commit(&bars->drain);
+          if (leader) umma_commit(&bars->drain);
           const long long t0 = clock64();
           while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
         }
