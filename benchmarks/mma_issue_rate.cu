@@ -9,8 +9,10 @@
 // bounded mbarrier wait.  Variants: both operands from shared memory (SS) or A from TMEM (TS), B K-major or MN-major,
 // one to three accumulators, N = 128 or 256, chains whose A columns the next chain overwrites, two issuing warps, and
 // eight extra warps that stream tcgen05.ld, or run dense FMA + MUFU code (sixteen independent chains per thread), with
-// and without a pause every ~20 instructions.  What it shows: the pipe takes a 128 x 128 x 16 instruction every 64 cycles
-// in every operand form; a lone issuing warp next to dense arithmetic warps gets one out only every ~99 cycles.
+// and without a pause every ~20 instructions; and the issuing loop run by the whole warp with one elected lane issuing
+// (warp-uniform control flow) instead of under `if (lane == 0)`.  What it shows: the pipe takes a 128 x 128 x 16 instruction every 64 cycles
+// in every operand form; a lone issuing warp next to dense arithmetic warps gets one out only every ~99 cycles when the
+// loop runs under `if (lane == 0)`, and every 64 when it runs warp-uniformly.
 #include <cstdio>
 #include <cstdlib>
 #include <cuda_runtime.h>
@@ -23,7 +25,7 @@ using namespace ody;
 struct PBars { uint64_t done; uint64_t done2; uint32_t tmem_base; int abort_flag; };
 
 // KIND 0: SS, B K-major; 1: SS, B MN-major; 2: TS, B K-major; 3: TS, B MN-major.  LD: 8 extra warps stream tcgen05.ld meanwhile.
-template <int KIND, int N, int NACC, bool LD, bool MATH = false, int YIELD = 0>
+template <int KIND, int N, int NACC, bool LD, bool MATH = false, int YIELD = 0, bool UNI = false>
 __global__ void __launch_bounds__(384, 1) probe(int groups, long long* out, int* err) {
   extern __shared__ uint8_t raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
@@ -41,7 +43,26 @@ __global__ void __launch_bounds__(384, 1) probe(int groups, long long* out, int*
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
   volatile int* abort_flag = &bars->abort_flag;
-  if (warp == 0 && lane == 0) {
+  if (UNI && warp == 0) {
+    constexpr uint32_t IDESC = make_idesc_bf16(128, N, 0, 0);
+    const uint32_t acol = NACC * N;
+    const long long t0 = clock64();
+    for (int g = 0; g < groups; ++g) {
+      const uint32_t d = tmem + (g % NACC) * N;
+      const uint64_t bk = make_smem_desc(smem_u32(sB) + (g % NB) * B_BYTES, 16, 1024);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        const uint64_t bd = desc_advance(bk, (kk >> 2) * (B_BYTES / 2) + (kk & 3) * 32);
+        if (elect_one()) umma_ts(d, tmem + acol + kk * 8, bd, IDESC, 1u);
+      }
+    }
+    const long long t1 = clock64();
+    if (elect_one()) umma_commit(&bars->done);
+    __syncwarp();
+    mbar_wait(&bars->done, 0, abort_flag, err, 1);
+    const long long t2 = clock64();
+    if (blockIdx.x == 0 && lane == 0) { out[0] = t1 - t0; out[1] = t2 - t0; }
+  } else if (!UNI && warp == 0 && lane == 0) {
     constexpr uint32_t IDESC = make_idesc_bf16(128, N, 0, (KIND & 1) ? 1 : 0);
     const uint64_t a0 = make_smem_desc(smem_u32(sA), 16, 1024);
     const uint32_t acol = NACC * N;             // A operand columns (TS)
@@ -121,12 +142,12 @@ __global__ void __launch_bounds__(384, 1) probe(int groups, long long* out, int*
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
-template <int KIND, int N, int NACC, bool LD, bool MATH = false, int YIELD = 0>
+template <int KIND, int N, int NACC, bool LD, bool MATH = false, int YIELD = 0, bool UNI = false>
 void run(const char* name, int groups, long long* out, int* err) {
   constexpr int SMEM = 128 * 256 + 3 * N * 256 + 256 + 1024;
-  cudaFuncSetAttribute(probe<KIND, N, NACC, LD, MATH, YIELD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  cudaFuncSetAttribute(probe<KIND, N, NACC, LD, MATH, YIELD, UNI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
   cudaMemset(out, 0, 32);
-  for (int rep = 0; rep < 2; ++rep) probe<KIND, N, NACC, LD, MATH, YIELD><<<148, 384, SMEM>>>(groups, out, err);
+  for (int rep = 0; rep < 2; ++rep) probe<KIND, N, NACC, LD, MATH, YIELD, UNI><<<148, 384, SMEM>>>(groups, out, err);
   cudaError_t e = cudaDeviceSynchronize();
   long long h[4]; int herr = 0;
   cudaMemcpy(h, out, 32, cudaMemcpyDeviceToHost);
@@ -157,6 +178,8 @@ int main() {
   run<2, 128, 3, true, true, 1>("TS  8 math warps, dependent smem load / 20 instr", G, out, err);
   run<2, 128, 3, true, true, 2>("TS  8 math warps, nanosleep(0) / 20 instr", G, out, err);
   run<2, 128, 3, true, true, 3>("TS  8 math warps, bar.warp.sync / 20 instr", G, out, err);
+  run<2, 128, 3, false, false, 0, true>("TS  warp-uniform issue (elect_one), alone", G, out, err);
+  run<2, 128, 3, true, true, 0, true>("TS  warp-uniform issue (elect_one) + 8 math warps", G, out, err);
   run<0, 256, 1, false>("SS  N=256 B K-major, 1 accumulator", G, out, err);
   run<2, 256, 1, false>("TS  N=256 B K-major, 1 accumulator", G, out, err);
   return 0;

@@ -154,7 +154,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {
+      // every lane runs the control flow, so the compiler keeps descriptors and loop state in uniform registers and an MMA
+      // costs a few instructions; one elected lane issues the tcgen05 instructions (benchmarks/mma_issue_rate.cu)
+      const bool leader = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
@@ -172,17 +175,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(&bars->full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint64_t a0 = desc_advance(adesc0, stage * STAGE_BYTES), b0 = desc_advance(bdesc0, stage * STAGE_BYTES);
-          umma_ss(d_tmem, a0, b0, IDESC, kb > 0 ? 1u : 0u);
+          if (leader) umma_ss(d_tmem, a0, b0, IDESC, kb > 0 ? 1u : 0u);
 #pragma unroll
           for (int kk = 1; kk < BK / UMMA_K; ++kk)
-            umma_ss(d_tmem, desc_advance(a0, kk * (A_MN ? 2048 : 32)), desc_advance(b0, kk * (B_MN ? 2048 : 32)), IDESC, 1u);
-          umma_commit(&bars->empty[stage]);        // frees the smem stage once these MMAs have read it
+            if (leader) umma_ss(d_tmem, desc_advance(a0, kk * (A_MN ? 2048 : 32)), desc_advance(b0, kk * (B_MN ? 2048 : 32)), IDESC, 1u);
+          if (leader) umma_commit(&bars->empty[stage]);        // frees the smem stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(&bars->tmem_full[buf]);  // accumulator complete
+        if (ok && leader) umma_commit(&bars->tmem_full[buf]);  // accumulator complete
       }
       if (!ok || *abort_flag) {
-        umma_commit(&bars->drain);
+        if (leader) umma_commit(&bars->drain);
         const long long t0 = clock64();
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
       }

@@ -228,7 +228,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (even CTA only)
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {
+      // every lane runs the control flow, so the compiler keeps descriptors and loop state in uniform registers and an MMA
+      // costs a few instructions; one elected lane issues the tcgen05 instructions (benchmarks/mma_issue_rate.cu)
+      const bool leader = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       int local_tile = 0;
@@ -246,17 +249,17 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (!mbar_wait(&bars->full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint64_t a0 = desc_advance(adesc0, stage * STAGE_BYTES), b0 = desc_advance(bdesc0, stage * STAGE_BYTES);
-          umma2_ss(d_tmem, a0, b0, IDESC, kb > 0 ? 1u : 0u);
+          if (leader) umma2_ss(d_tmem, a0, b0, IDESC, kb > 0 ? 1u : 0u);
 #pragma unroll
           for (int kk = 1; kk < BK / UMMA_K; ++kk)
-            umma2_ss(d_tmem, desc_advance(a0, kk * (A_MN ? 2048 : 32)), desc_advance(b0, kk * (B_MN ? 2048 : 32)), IDESC, 1u);
-          umma2_commit_both(&bars->empty[stage]);      // frees the stage in both CTAs once these MMAs have read it
+            if (leader) umma2_ss(d_tmem, desc_advance(a0, kk * (A_MN ? 2048 : 32)), desc_advance(b0, kk * (B_MN ? 2048 : 32)), IDESC, 1u);
+          if (leader) umma2_commit_both(&bars->empty[stage]);      // frees the stage in both CTAs once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma2_commit_both(&bars->tmem_full[buf]);   // accumulators of both CTAs complete
+        if (ok && leader) umma2_commit_both(&bars->tmem_full[buf]);   // accumulators of both CTAs complete
       }
       if (!ok || *abort_flag) {
-        umma2_commit_local(&bars->drain);
+        if (leader) umma2_commit_local(&bars->drain);
         const long long t0 = clock64();
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
       }

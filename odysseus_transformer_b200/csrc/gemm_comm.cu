@@ -263,7 +263,10 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // every lane runs the control flow, so the compiler keeps descriptors and loop state in uniform registers and an MMA
+      // costs a few instructions; one elected lane issues the tcgen05 instructions (benchmarks/mma_issue_rate.cu)
+      const bool leader = elect_one();
       int stage = 0; uint32_t phase = 0; int local_tile = 0; bool ok = true;
       const uint32_t s0 = smem_u32(smem);
       const uint64_t adesc0 = A_MN ? make_smem_desc(s0, 8192, 1024) : make_smem_desc(s0, 16, 1024);
@@ -278,17 +281,17 @@ gemm_comm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!mbar_wait(&bars->full[stage], phase, abort_flag, err, ODY_ERR_TIMEOUT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint64_t a0 = desc_advance(adesc0, stage * STAGE_BYTES), b0 = desc_advance(bdesc0, stage * STAGE_BYTES);
-          umma_ss(d_tmem, a0, b0, IDESC, kb > 0 ? 1u : 0u);
+          if (leader) umma_ss(d_tmem, a0, b0, IDESC, kb > 0 ? 1u : 0u);
 #pragma unroll
           for (int kk = 1; kk < BK / UMMA_K; ++kk)
-            umma_ss(d_tmem, desc_advance(a0, kk * (A_MN ? 2048 : 32)), desc_advance(b0, kk * (B_MN ? 2048 : 32)), IDESC, 1u);
-          umma_commit(&bars->empty[stage]);
+            if (leader) umma_ss(d_tmem, desc_advance(a0, kk * (A_MN ? 2048 : 32)), desc_advance(b0, kk * (B_MN ? 2048 : 32)), IDESC, 1u);
+          if (leader) umma_commit(&bars->empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(&bars->tmem_full[buf]);
+        if (ok && leader) umma_commit(&bars->tmem_full[buf]);
       }
       if (!ok || *abort_flag) {
-        umma_commit(&bars->drain);
+        if (leader) umma_commit(&bars->drain);
         const long long t0 = clock64();
         while (!mbar_try_wait(&bars->drain, 0) && clock64() - t0 < ODY_SPIN_LIMIT_CYCLES / 8) {}
       }
