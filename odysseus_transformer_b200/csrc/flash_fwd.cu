@@ -294,8 +294,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // ------------------------------------------------------------------ softmax + epilogue (warpgroup t handles tile t)
     // One thread per query row.  The other split that was measured, all eight warps on one tile-block at a time with two
     // threads per row (64 key columns each, partial maxima and sums swapped through shared memory at a 64-thread barrier),
-    // was slower: 901 against 1007 TFLOP/s at 8192 tokens x 32 heads, 1030 against 1161 at 32768 x 4.  The barrier and the
-    // halved independent work per thread cost more than the shorter turn of a block gains.
+    // was slower: 901 against 1007 TFLOP/s at 8192 tokens x 32 heads, 1030 against 1161 at 32768 x 4, and again with the
+    // warp-uniform issue loop, 934 / 1065 against 1085 / 1250.  The exponentials are bound by the special-function unit of
+    // each scheduler, which two warps of the same block share, so the block's turn does not get shorter, and the barrier
+    // and the halved independent work per thread cost on top.
     reg_inc<PUSH ? REGS_MATH_PUSH : REGS_MATH>();
     const int t = (warp - 4) >> 2;                     // 0 = tile A, 1 = tile B
     const int q = warp & 3;                            // TMEM lane quarter
