@@ -263,31 +263,6 @@ def main():
     peak = max_over_ranks(mem["peak_allocated"], dev)
     exposed = exposed_comm_ms(ctx, reset=True)
 
-    # ---------------- on 8 GPUs also the fixed-length point: Llama-2-7B, Odysseus, L = 32768 (same Trainer API, device-resident)
-    extra = None
-    if world == 8 and args.model == "llama2-7b" and mode == "odysseus" and not args.seq_len and not args.layers:
-        del trainer, host_batches
-        torch.cuda.empty_cache()
-        L2 = 32768
-        tr2 = Trainer(cfg, mode, ctx, L2, lr=1e-5, dtype=torch.bfloat16, seed=42)
-        hb2 = [torch.randint(cfg.vocab_size, (1, L2 + 1), generator=gen).pin_memory() for _ in range(nb)]
-        db2 = [tr2.shard_batch(b) for b in hb2]
-        for i in range(args.warmup):
-            tr2.train_step_device(db2[i]["local_input_ids"], db2[i]["local_position_ids"], db2[i]["local_target_ids"])
-        barrier()
-        torch.cuda.reset_peak_memory_stats(dev)
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record()
-        for i in range(args.warmup, nb):
-            tr2.train_step_device(db2[i]["local_input_ids"], db2[i]["local_position_ids"], db2[i]["local_target_ids"])
-        f1.record()
-        barrier()
-        tr2.check_status()
-        ms2 = max_over_ranks(f0.elapsed_time(f1), dev)
-        extra = {"seq_len": L2, "value": args.steps * L2 / (ms2 / 1e3), "unit": "tokens/s", "ms_per_step": ms2 / args.steps,
-                 "peak_mem_gb": max_over_ranks(memory_gb(dev)["peak_allocated"], dev),
-                 "published_8xA100_tok_s": 15302.0, "vs_published": args.steps * L2 / (ms2 / 1e3) / 15302.0}
-
     if rank == 0:
         tok_s = args.steps * L / (ms / 1e3)
         e2e_tok_s = args.steps * L / (e2e_ms / 1e3)
@@ -313,8 +288,6 @@ def main():
             "clocks": clocks,
             "peak_mem_gb": peak, "loss": last_loss, "exposed_comm_ms_per_step": exposed / (args.steps + min(2, args.warmup) + args.steps),
         }
-        if extra is not None:
-            out["config2_32k"] = extra
         print(json.dumps(out))
     if world > 1:
         dist.barrier()
