@@ -49,7 +49,8 @@ def test_saved_activation_model_matches_autograd(mode):
 # (mode, L, GPUs, checkpointing, measured peak allocated GiB) on B200s, Llama-2-7B, fused backend
 MEASURED = [("odysseus", 8192, 1, False, 133.2), ("odysseus", 32768, 4, False, 58.0), ("ulysses", 32768, 4, False, 60.0),
             ("ring", 32768, 4, False, 57.9), ("odysseus", 65536, 4, False, 90.8), ("ulysses", 65536, 4, False, 94.8),
-            ("odysseus", 131072, 4, True, 38.55)]
+            ("odysseus", 131072, 4, True, 38.55), ("odysseus", 131072, 8, False, 78.53), ("ulysses", 65536, 8, False, 47.66),
+            ("tpsp", 65536, 8, False, 45.66), ("ring", 65536, 8, False, 45.64)]
 
 
 @pytest.mark.parametrize("mode,L,n,ckpt,peak", MEASURED)
