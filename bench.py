@@ -91,7 +91,8 @@ def _reference_tree() -> str:
     """``baseline/_ref``: the reference has no setup.py / pyproject.toml, so pip cannot install it; a plain copy of
     its tree is the install.  Made here when missing and the read-only original is reachable."""
     ref = os.path.join(ROOT, "baseline", "_ref")
-    src = "/root/reference"
+    # the reference checkout: next to this repository unless ODY_REFERENCE_SRC says otherwise
+    src = os.environ.get("ODY_REFERENCE_SRC", os.path.join(os.path.dirname(ROOT), "reference"))
     if not os.path.exists(os.path.join(ref, "train.py")) and os.path.isdir(src):
         import shutil
         shutil.copytree(src, ref, dirs_exist_ok=True)
