@@ -59,10 +59,12 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_k(const bf16* __restrict__ x,
 }
 
 // Two rows per loop iteration and one barrier per iteration (the warps' partial dot products go through a
-// double-buffered shared array that every thread sums itself): the kernel is bound by memory latency, so what
-// matters is how many row loads are in flight between barriers.
+// double-buffered shared array that every thread sums itself).  The kernel is bound by memory latency, so what matters
+// is how many row loads are in flight per SM: the rows stay in registers as packed bf16 and are unpacked a second time
+// for the output instead of being kept as fp32, which halves the registers and lets two blocks share an SM (with the
+// fp32 copies it was one block per SM and a third of the copy bandwidth).
 template <int NV>
-__global__ void __launch_bounds__(256) rmsnorm_bwd_k(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+__global__ void __launch_bounds__(256, NV <= 2 ? 2 : 1) rmsnorm_bwd_k(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                                                      const bf16* __restrict__ w, const float* __restrict__ rstd,
                                                      const bf16* __restrict__ ds, bf16* __restrict__ dx,
                                                      float* __restrict__ dw_partial, int64_t rows, int dim) {
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(const bf16* __restrict__ dy
   const float inv_dim = 1.f / (float)dim;
   int par = 0;
   for (int64_t row0 = (int64_t)blockIdx.x * R; row0 < rows; row0 += (int64_t)gridDim.x * R, par ^= 1) {
-    float g[R][NV][8], xh[R][NV][8], rs[R], dot[R];
+    float rs[R], dot[R];
     bf16x8 pa[R][NV], px[R][NV];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -102,15 +104,14 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(const bf16* __restrict__ dy
       for (int i = 0; i < NV; ++i) {
         const int c = (threadIdx.x + i * blockDim.x) * 8;
         if (c < dim && row0 + r < rows) {
-          float a[8];
+          float a[8], xh[8];
           unpack8(pa[r][i], a);
-          unpack8(px[r][i], xh[r][i]);
+          unpack8(px[r][i], xh);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            xh[r][i][j] *= rs[r];
-            acc[i][j] += a[j] * xh[r][i][j];
-            g[r][i][j] = a[j] * wv[i][j];
-            dot[r] += g[r][i][j] * xh[r][i][j];
+            xh[j] *= rs[r];
+            acc[i][j] += a[j] * xh[j];
+            dot[r] += a[j] * wv[i][j] * xh[j];
           }
         }
       }
@@ -127,9 +128,11 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_k(const bf16* __restrict__ dy
       for (int i = 0; i < NV; ++i) {
         const int c = (threadIdx.x + i * blockDim.x) * 8;
         if (c < dim && row < rows) {
-          float o[8];
+          float a[8], xh[8], o[8];
+          unpack8(pa[r][i], a);
+          unpack8(px[r][i], xh);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = (g[r][i][j] - xh[r][i][j] * dot[r]) * rs[r];
+          for (int j = 0; j < 8; ++j) o[j] = (a[j] * wv[i][j] - xh[j] * rs[r] * dot[r]) * rs[r];
           if (ds != nullptr) {
             float s[8];
             unpack8(ld8(ds + row * dim + c), s);
