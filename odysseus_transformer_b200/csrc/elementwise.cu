@@ -504,7 +504,7 @@ extern "C" int ody_rmsnorm_fwd(const void* x, const void* delta, const void* w, 
 
 extern "C" int ody_rmsnorm_bwd_blocks(int64_t rows, int dim) {
   (void)dim;
-  int64_t b = 148 * 4;
+  int64_t b = 148 * 2;       // two resident blocks per SM (112 registers x 256 threads each)
   return (int)(rows < b ? (rows > 0 ? rows : 1) : b);
 }
 
