@@ -70,3 +70,13 @@ def test_what_fits():
     assert fits(estimate_memory(cfg, "odysseus", 262144, 8, grad_checkpoint=True))
     with pytest.raises(ValueError):
         estimate_memory(cfg, "odysseus", 1000, 3)
+
+
+def test_memory_cli_prints_one_json_line(capsys):
+    import json
+    from odysseus_transformer_b200.utils import memory
+    assert memory.main(["--model", "llama2-7b", "--mode", "ulysses", "--seq-length", "65536", "--gpus", "8"]) == 0
+    out = json.loads(capsys.readouterr().out.strip())
+    assert out["fits_180GB"] is True and 40 < out["peak_allocated"] < 55
+    assert memory.main(["--model", "llama2-7b", "--seq-length", "262144", "--gpus", "4"]) == 0
+    assert json.loads(capsys.readouterr().out.strip())["fits_180GB"] is False
