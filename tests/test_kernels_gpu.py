@@ -130,7 +130,7 @@ def test_gemm_accumulate_and_strided_out(lib, gemm_variant):
     assert big[:, N:].abs().max().item() == 0
 
 
-@pytest.mark.parametrize("rows,dim", [(64, 256), (1000, 4096), (33, 1024), (17, 8192)])
+@pytest.mark.parametrize("rows,dim", [(64, 256), (1000, 4096), (33, 1024), (17, 8192), (5, 16384), (601, 4096)])
 def test_rmsnorm(lib, rows, dim):
     from odysseus_transformer_b200.ops import torch_ref as R
     x, d, w = _rand(rows, dim), _rand(rows, dim), _rand(dim) + 1
